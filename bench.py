@@ -1,0 +1,378 @@
+#!/usr/bin/env python
+"""Headline benchmark: MoE dispatch + combine latency on DeepSeek-V3 shapes.
+
+    python bench.py --gpus 1 --steps 200 --warmup 20
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 200 --warmup 20
+
+One *step* is one ``dispatch`` followed by one ``combine`` of an expert-parallel MoE layer
+with EP = number of GPUs: 128 tokens per rank (decode), hidden 7168, 256 experts, top-8,
+fp8-e4m3 dispatch with 56 fp32 scales per token, bf16 combine, identity expert (the
+combine input is a pre-filled bf16 buffer), which is the configuration of the reference's
+benchmarks/bench_all_to_all.py:578-590 behind its published EP8 numbers
+(docs/fabric-lib.md:100-119). ``--tokens 4096`` gives the prefill shape.
+
+Timing: every step is bracketed by CUDA events on the launching stream; an L2 flush
+(a 256 MiB device write) and, with several ranks, a tiny all-reduce that lines the ranks
+up run before the start event, outside the timed interval. The reported value is the
+maximum over ranks of the mean step time. The ``e2e`` entry times the same step through
+the public API including the host->device copy of the step's inputs from pinned memory and
+the device->host read of its result, with the host clock.
+
+Rank 0 prints one JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+PUBLISHED_US = {  # reference EP8 dispatch+combine, pplx-EFA column (docs/fabric-lib.md:109,119)
+    128: 49.7 + 64.2,
+    4096: 1052.4 + 1396.7,
+}
+
+
+def parse_args() -> argparse.Namespace:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["ours", "nccl", "reference"], default="ours")
+    ap.add_argument("--tokens", type=int, default=128, help="tokens per rank (128 decode, 4096 prefill)")
+    ap.add_argument("--hidden", type=int, default=7168)
+    ap.add_argument("--experts", type=int, default=256)
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--combine-mode", choices=["per_route", "pre_reduce"], default="per_route")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the secondary prefill measurement")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def reference_unavailable() -> str | None:
+    """Why the unmodified reference cannot run here (None if it can)."""
+    ref = ROOT / "baseline" / "_ref" / "pplx_garden"
+    if not ref.exists():
+        return "baseline/_ref is empty: the offline pip install of the reference was not done on this machine"
+    if not list(ref.glob("_rust*.so")):
+        return ("reference installed as pure Python only: its native module pplx_garden._rust is a Rust "
+                "crate (cargo/rustc absent) that also needs libibverbs/libfabric, GDRCopy and an RDMA NIC per GPU")
+    return None
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a block runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self._file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self._proc = None
+        try:
+            self._proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(gpu_index)],
+                stdout=self._file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self._proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self._proc is None:
+            return out
+        self._proc.terminate()
+        try:
+            self._proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self._proc.kill()
+        self._file.flush()
+        self._file.seek(0)
+        clocks, max_clocks, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self._file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                max_clocks.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        self._file.close()
+        try:
+            os.unlink(self._file.name)
+        except OSError:
+            pass
+        if clocks:
+            out.update(sm_mhz=statistics.median(clocks), sm_max_mhz=max(max_clocks),
+                       reasons=sorted(reasons), samples=len(clocks))
+        return out
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        why = reference_unavailable()
+        if why is not None:
+            if int(os.environ.get("RANK", "0")) == 0:
+                print(json.dumps({"impl": "reference", "unavailable": why}))
+            return
+        # A runnable reference would be driven here through its own P2PAllToAll.
+        print(json.dumps({"impl": "reference", "unavailable": "reference driver not wired up"}))
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    import pplx_garden  # noqa: F401
+    from pplx_garden.distributed import ProcessGroup
+    from pplx_garden.kernels.nccl_all_to_all import NcclAllToAll
+    from pplx_garden.kernels.p2p_all_to_all import P2PAllToAll
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world and world == 1 and args.gpus > 1:
+        raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    process_group = global_group = None
+    if world > 1:
+        process_group = ProcessGroup.from_env(device)
+        global_group = process_group.create_group()
+
+    def run_shape(tokens: int, steps: int, warmup: int, with_e2e: bool) -> dict:
+        H, E, K = args.hidden, args.experts, args.topk
+        hs = H // 128
+        kw = dict(max_num_tokens=tokens, num_experts=E, expert_padding=1, hidden_dim=H,
+                  hidden_dim_scale=hs, in_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16,
+                  scale_dtype=torch.float32, num_experts_per_token=K, device=device,
+                  global_group=global_group)
+        if args.impl == "ours":
+            a2a = P2PAllToAll(dp_group=None, node_group=None, nets_per_gpu=0, max_private_tokens=None,
+                              combine_mode=args.combine_mode, **kw)
+            rows = a2a.max_recv_rows
+        else:
+            a2a = NcclAllToAll(**kw)
+            rows = tokens * world * min(K, -(-E // world))
+        L = -(-E // world)
+        gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+        pool = 4
+        host = []
+        bias = torch.randn(E, generator=gen) * 0.5 if tokens >= 1024 else torch.zeros(E)
+        for _ in range(pool):
+            x = torch.randn((tokens, H), generator=gen)
+            blocks = x.reshape(tokens, hs, 128)
+            scale = blocks.abs().amax(-1).clamp_min(1e-10) / 448.0
+            xq = (blocks / scale.unsqueeze(-1)).reshape(tokens, H).to(torch.float8_e4m3fn)
+            logits = torch.randn((tokens, E), generator=gen) + bias
+            top = torch.topk(logits, K, dim=-1)
+            w = torch.softmax(top.values, dim=-1)
+            host.append(tuple(t.pin_memory() for t in (xq.view(torch.uint8), scale.contiguous(),
+                                                       top.indices.to(torch.int32).contiguous(), w.contiguous())))
+        dev_inputs = [tuple(t.to(device) for t in h) for h in host]
+
+        def views(tup):
+            xq, sc, idx, w = tup
+            return xq.view(torch.float8_e4m3fn), sc, idx.view(torch.uint32), w
+
+        num = torch.zeros(L, dtype=torch.int32, device=device)
+        ox = torch.zeros((rows, H), dtype=torch.uint8, device=device).view(torch.float8_e4m3fn)
+        osc = torch.zeros((rows, hs), dtype=torch.float32, device=device)
+        out = torch.zeros((tokens, H), dtype=torch.bfloat16, device=device)
+        expert_y = torch.randn((rows, H), device=device).to(torch.bfloat16)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+        dummy = torch.zeros(1, device=device)
+
+        def step(inp) -> None:
+            xq, sc, idx, w = views(inp)
+            a2a.dispatch(num, ox, osc, xq, sc, idx, w)
+            a2a.combine(out, idx, w, expert_y)
+
+        def line_up() -> None:
+            flush.zero_()
+            if world > 1:
+                dist.all_reduce(dummy)
+
+        # correctness of the path that is about to be timed: y = dequant(x) must come back
+        xq, sc, idx, w = views(dev_inputs[0])
+        a2a.dispatch(num, ox, osc, xq, sc, idx, w)
+        y = (ox.to(torch.float32) * osc.repeat_interleave(128, dim=1)).to(torch.bfloat16)
+        a2a.combine(out, idx, w, y)
+        torch.cuda.synchronize()
+        want = xq.to(torch.float32) * sc.repeat_interleave(128, dim=1)
+        err = (out.to(torch.float32) - want).abs().max().item()
+        assert err < 0.1 * want.abs().max().item() + 1e-3, f"dispatch/combine round trip is wrong (max err {err})"
+
+        for i in range(warmup):
+            line_up()
+            step(dev_inputs[i % pool])
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(device_ids=[device.index])
+        sampler = ClockSampler(device.index)
+        torch.cuda.synchronize()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        dstarts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        t_wall = time.perf_counter()
+        for i in range(steps):
+            inp = dev_inputs[i % pool]
+            xq, sc, idx, w = views(inp)
+            line_up()
+            starts[i].record()
+            a2a.dispatch(num, ox, osc, xq, sc, idx, w)
+            dstarts[i].record()
+            a2a.combine(out, idx, w, expert_y)
+            ends[i].record()
+        torch.cuda.synchronize()
+        t_wall = time.perf_counter() - t_wall
+        if world > 1:
+            dist.barrier(device_ids=[device.index])
+        torch.cuda.synchronize()
+        step_us = [s.elapsed_time(e) * 1000 for s, e in zip(starts, ends)]
+        disp_us = [s.elapsed_time(e) * 1000 for s, e in zip(starts, dstarts)]
+        comb_us = [s.elapsed_time(e) * 1000 for s, e in zip(dstarts, ends)]
+
+        # back-to-back (no flush, no line-up): K steps inside one event pair
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier(device_ids=[device.index])
+        b0, b1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        b0.record()
+        for i in range(steps):
+            step(dev_inputs[i % pool])
+        b1.record()
+        torch.cuda.synchronize()
+        b2b_us = b0.elapsed_time(b1) * 1000 / steps
+        clocks = sampler.stop()
+
+        e2e = None
+        if with_e2e:
+            d_in = [torch.empty_like(t, device=device) for t in host[0]]
+            res_num = torch.empty(L, dtype=torch.int32).pin_memory()
+            res_row = torch.empty(H, dtype=torch.bfloat16).pin_memory()
+            h2d = sum(t.numel() * t.element_size() for t in host[0])
+            d2h = res_num.numel() * 4 + res_row.numel() * 2
+            e2e_us = []
+            for i in range(warmup + steps):
+                line_up()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for dst, src in zip(d_in, host[i % pool]):
+                    dst.copy_(src, non_blocking=True)
+                xq, sc, idx, w = views(tuple(d_in))
+                a2a.dispatch(num, ox, osc, xq, sc, idx, w)
+                a2a.combine(out, idx, w, expert_y)
+                res_num.copy_(num, non_blocking=True)
+                res_row.copy_(out[0], non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                if i >= warmup:
+                    e2e_us.append((time.perf_counter() - t0) * 1e6)
+            e2e = {"mean_us": statistics.fmean(e2e_us), "h2d": h2d, "d2h": d2h}
+
+        if args.impl == "ours":
+            a2a.check()
+        result = {
+            "mean_us": statistics.fmean(step_us), "p50_us": statistics.median(step_us),
+            "dispatch_p50_us": statistics.median(disp_us), "combine_p50_us": statistics.median(comb_us),
+            "b2b_us": b2b_us, "wall_s": t_wall, "clocks": clocks, "e2e": e2e,
+        }
+        a2a.destroy()
+        return result
+
+    def reduce_max(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    main_res = run_shape(args.tokens, args.steps, max(args.warmup, 3), not args.no_e2e)
+    value = reduce_max(main_res["mean_us"])
+    extra = {
+        "p50_us_max_rank": reduce_max(main_res["p50_us"]),
+        "dispatch_p50_us_max_rank": reduce_max(main_res["dispatch_p50_us"]),
+        "combine_p50_us_max_rank": reduce_max(main_res["combine_p50_us"]),
+        "back_to_back_us_per_step": reduce_max(main_res["b2b_us"]),
+    }
+    e2e_val = reduce_max(main_res["e2e"]["mean_us"]) if main_res["e2e"] else None
+    other_tokens = 4096 if args.tokens == 128 else 128
+    if not args.no_prefill:
+        other_steps = max(10, min(args.steps, 40)) if other_tokens > 128 else args.steps
+        other = run_shape(other_tokens, other_steps, 3, False)
+        extra[f"tokens{other_tokens}_step_us"] = reduce_max(other["mean_us"])
+        extra[f"tokens{other_tokens}_dispatch_p50_us"] = reduce_max(other["dispatch_p50_us"])
+        extra[f"tokens{other_tokens}_combine_p50_us"] = reduce_max(other["combine_p50_us"])
+        pub = PUBLISHED_US.get(other_tokens)
+        if pub:
+            extra[f"tokens{other_tokens}_vs_published_ep8"] = extra[f"tokens{other_tokens}_step_us"] / pub
+
+    if rank == 0:
+        published = PUBLISHED_US.get(args.tokens)
+        line = {
+            "metric": "EP dispatch+combine latency per step (us), DeepSeek-V3 shape",
+            "value": value,
+            "unit": "us",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": value / 1000.0,
+            "higher_is_better": False,
+            "scaling": "weak",
+            "vs_baseline": (value / published) if published else None,
+            "dtype": "fp8_e4m3 dispatch (1x128 fp32 scales) / bf16 combine",
+            "data": "synthetic",
+            "impl": args.impl,
+            "config": {
+                "model": "DeepSeek-V3 MoE layer communication (identity expert)",
+                "tokens_per_rank": args.tokens,
+                "global_batch": args.tokens * world,
+                "seq_len": 1,
+                "hidden": args.hidden,
+                "experts": args.experts,
+                "topk": args.topk,
+                "parallelism": f"ep{world}",
+                "combine_mode": args.combine_mode,
+                "l2": "flushed between timed steps (256 MiB device write before each start event)",
+                "baseline_note": "vs_baseline divides by the reference's published EP8 dispatch+combine "
+                                 "(113.9 us decode / 2449.1 us prefill), whatever n_gpus is",
+            },
+            "clocks": {k: main_res["clocks"][k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
+            "gpu_launches": 2 * args.steps if args.impl == "ours" else 0,
+            "extra": extra,
+        }
+        if e2e_val is not None:
+            line["e2e"] = {
+                "value": e2e_val,
+                "unit": "us",
+                "h2d_bytes_per_step": main_res["e2e"]["h2d"],
+                "d2h_bytes_per_step": main_res["e2e"]["d2h"],
+                "readback": "per-expert token counts + first combined token row",
+            }
+        print(json.dumps(line))
+
+    if global_group is not None:
+        global_group.destroy()
+    if process_group is not None:
+        process_group.destroy()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,94 @@
+// Host side of one all-to-all context: wire-format/layout arithmetic, the device-local
+// workspace, launch wrappers and the status word.
+//
+// Counterpart of the reference's AllToAllContext (p2p-all-to-all/src/a2a_context.rs:15-488).
+// There is no worker thread to spawn or join: the reference's host proxy
+// (p2p-all-to-all/src/a2a_worker.rs:340-455) has no equivalent because counts, tokens and
+// arrival signals all move as NVLink peer stores issued by the kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <array>
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "a2a_types.h"
+
+namespace pplx {
+
+struct A2AParams {
+  int world = 1;
+  int dp_size = 1;
+  int num_experts = 0;
+  int topk = 0;
+  int max_num_tokens = 0;
+  int hidden_dim = 0;
+  int hidden_dim_scale = 0;
+  int in_elemsize = 2;
+  int out_elemsize = 2;
+  int scale_elemsize = 4;
+  int expert_padding = 1;
+  int combine_mode = kCombinePerRoute;
+  int num_blocks = 0;          // 0: one block per SM (divided among virtual ranks)
+  int64_t wait_limit_ms = 0;   // 0: PPLX_A2A_TIMEOUT_MS or 10 s
+};
+
+// Pure arithmetic (no CUDA): validated config with wire format and symmetric layout.
+A2AConfig a2a_make_config(const A2AParams& p, int num_sms, int virtual_ranks);
+
+struct A2AStatusInfo {
+  uint32_t code = 0, phase = 0, who = 0, detail = 0;
+  std::string message() const;
+};
+
+class A2AContext {
+ public:
+  // `ranks` lists the ranks this process plays (one entry in a real multi-GPU run).
+  // sync_ptrs[i][p] / recv_ptrs[i][p]: rank p's symmetric regions as mapped for ranks[i].
+  A2AContext(const A2AParams& params, int device, const std::vector<int>& ranks,
+             const std::vector<std::vector<uint64_t>>& sync_ptrs,
+             const std::vector<std::vector<uint64_t>>& recv_ptrs);
+  ~A2AContext();
+  A2AContext(const A2AContext&) = delete;
+  A2AContext& operator=(const A2AContext&) = delete;
+
+  const A2AConfig& config() const { return cfg_; }
+  int num_local_ranks() const { return static_cast<int>(ranks_.size()); }
+  int device() const { return device_; }
+
+  void dispatch(const DispatchSendArgs* send, const DispatchRecvArgs* recv, bool do_send,
+                bool do_recv, cudaStream_t stream);
+  void combine(const CombineSendArgs* send, const CombineRecvArgs* recv, bool do_send,
+               bool do_recv, int y_dtype, int out_dtype, cudaStream_t stream);
+
+  // Synchronous read of the status word of local rank `i` (does not wait for the stream).
+  A2AStatusInfo status(int i = 0) const;
+  // True once any kernel of this context reported a failure. Reads a pinned host word:
+  // no stream synchronisation, safe to call after every launch.
+  bool failed() const;
+  // Throws pplx::Error when any local rank recorded a failure.
+  void check() const;
+  // [tokens sent, reserved, max dispatch wait ns, max combine wait ns, ...]
+  std::array<uint64_t, 8> stats(int i = 0) const;
+  std::array<uint32_t, kNumPhases> iterations(int i = 0) const;
+  void set_team_override(int team) { team_override_ = team; }
+
+ private:
+  int pick(int64_t items) const;
+
+  A2AConfig cfg_{};
+  int device_;
+  std::vector<int> ranks_;
+  A2ARankStates states_{};
+  std::vector<void*> allocations_;
+  std::vector<uint32_t*> status_ptrs_;
+  std::vector<uint32_t*> host_flags_;
+  std::vector<unsigned long long*> stats_ptrs_;
+  std::vector<uint32_t*> iters_ptrs_;
+  int64_t last_tokens_ = 0;
+  int team_override_ = 0;
+};
+
+}  // namespace pplx

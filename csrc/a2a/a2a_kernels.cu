@@ -1,0 +1,1005 @@
+// Expert-parallel dispatch / combine kernels for one NVSwitch domain (sm_100a).
+//
+// Four phases, launched separately or fused pairwise (send+recv in one launch):
+//
+//   dispatch_send  tokens -> peer receive regions (16-byte peer stores over NVLink),
+//                  per-expert counts -> peers, arrival signal per destination
+//   dispatch_recv  wait for every source, build the expert-major layout from the
+//                  counts, replicate each record into the rows of its local experts
+//   combine_send   expert outputs -> origin ranks' combine regions, arrival signal
+//   combine_recv   wait, top-k weighted reduction into the caller's tensor
+//
+// They cover what the reference does with four cooperative kernels plus a host proxy
+// thread (p2p-all-to-all/a2a-kernels/src/a2a/a2a_dispatch_send.cu:112-536,
+// a2a_dispatch_recv.cu:16-236, a2a_combine_send.cu:20-235, a2a_combine_recv.cu:20-167,
+// p2p-all-to-all/src/a2a_worker.rs:340-455), but the protocol is different:
+//   * no CPU takes part; counts, payload and signals all travel as peer stores,
+//   * a token crosses NVLink once per destination *rank*, not once per route,
+//   * receive regions are sized for the worst case, so there is no overflow/pull path,
+//   * no grid-wide barrier: a block never waits for another block of its own GPU,
+//   * every wait on a remote flag is bounded in time and reports through a status word.
+//
+// blockIdx.y selects a *virtual rank*: with gridDim.y == 1 the launch serves the one
+// rank of this process; with gridDim.y == R one launch on one GPU plays R ranks whose
+// "peer" pointers all live on that GPU (used to test the multi-rank protocol and to
+// profile it on a single device).
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include <type_traits>
+
+#include "a2a_kernels.h"
+#include "a2a_types.h"
+#include "ptx.cuh"
+
+namespace pplx {
+namespace {
+
+constexpr int kMaxTeams = kA2AThreads / 32;
+
+template <int TEAM>
+struct Team {
+  int id;         // global team index inside this virtual rank
+  int count;      // teams inside this virtual rank
+  int in_block;   // team index inside the block
+  int lane;       // thread index inside the team
+  __device__ __forceinline__ Team() {
+    in_block = threadIdx.x / TEAM;
+    lane = threadIdx.x % TEAM;
+    // consecutive work items land on different SMs
+    id = in_block * gridDim.x + blockIdx.x;
+    count = gridDim.x * (kA2AThreads / TEAM);
+  }
+  __device__ __forceinline__ void sync() const {
+    if constexpr (TEAM == 32) {
+      __syncwarp();
+    } else if constexpr (TEAM == kA2AThreads) {
+      __syncthreads();
+    } else {
+      bar_sync(1 + in_block, TEAM);
+    }
+  }
+};
+
+__device__ __forceinline__ void report(const A2ALocal& ws, uint32_t code, uint32_t phase,
+                                       uint32_t who, uint32_t detail) {
+  if (atomicCAS(&ws.status[0], 0u, code) == 0u) {
+    ws.status[1] = phase;
+    ws.status[2] = who;
+    ws.status[3] = detail;
+    *reinterpret_cast<volatile uint32_t*>(ws.host_flag) = code;
+    __threadfence_system();
+  }
+}
+
+__device__ __forceinline__ uint32_t* flag_ptr(uint8_t* sync_base, int phase_slot, int src) {
+  // phase_slot 0: dispatch arrivals (indexed by source dp group)
+  // phase_slot 1: combine arrivals (indexed by source rank)
+  return reinterpret_cast<uint32_t*>(sync_base) +
+         (phase_slot * kMaxRanks + src) * kFlagStrideWords;
+}
+
+// Bounded wait until a cumulative arrival counter reaches `expected`.
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t expected,
+                                          uint64_t limit_ns, uint64_t* waited_ns) {
+  if (static_cast<int32_t>(ld_acquire_sys(flag) - expected) >= 0) {
+    *waited_ns = 0;
+    return true;
+  }
+  const uint64_t start = globaltimer_ns();
+  for (;;) {
+    #pragma unroll 1
+    for (int i = 0; i < 64; ++i) {
+      if (static_cast<int32_t>(ld_acquire_sys(flag) - expected) >= 0) {
+        *waited_ns = globaltimer_ns() - start;
+        return true;
+      }
+    }
+    if (globaltimer_ns() - start > limit_ns) {
+      *waited_ns = limit_ns;
+      return false;
+    }
+  }
+}
+
+// Marks this block as finished with `phase`; the last block of the launch advances the
+// phase's launch counter and clears the cursors of the *next* launch's parity.
+__device__ __forceinline__ void finish_phase(const A2AConfig& cfg, const A2ALocal& ws, int phase,
+                                             uint32_t iter) {
+  __syncthreads();
+  __shared__ uint32_t s_last;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t old = atom_acq_rel_gpu_add(&ws.done[phase], 1u);
+    s_last = (old == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (s_last) {
+    const uint32_t next_par = (iter + 1) & 1u;
+    if (phase == kPhaseDispatchSend) {
+      if (threadIdx.x < kMaxRanks) ws.send_cursor[next_par * kMaxRanks + threadIdx.x] = 0;
+    } else if (phase == kPhaseDispatchRecv) {
+      const int n = cfg.num_groups * cfg.experts_per_rank;
+      for (int i = threadIdx.x; i < n; i += blockDim.x) ws.place_cursor[next_par * n + i] = 0;
+    }
+    if (threadIdx.x == 0) {
+      ws.done[phase] = 0;
+      ws.iters[phase] = iter + 1;
+    }
+  }
+}
+
+__device__ __forceinline__ uint32_t read_iter(const A2ALocal& ws, int phase) {
+  return *reinterpret_cast<volatile const uint32_t*>(&ws.iters[phase]);
+}
+
+// ---------------------------------------------------------------------------
+// dispatch_send
+// ---------------------------------------------------------------------------
+
+// Quantises 16 consecutive bf16 values (two 16-byte vectors) held by one lane to e4m3;
+// eight neighbouring lanes share one 1x128 block and therefore one scale.
+__device__ __forceinline__ Vec16 quantize16(const Vec16& a, const Vec16& b, float* scale_out) {
+  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+  float2 f[8];
+  float amax = 0.f;
+  #pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[i] = __bfloat1622float2(pa[i]);
+    f[4 + i] = __bfloat1622float2(pb[i]);
+  }
+  #pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fmaxf(fabsf(f[i].x), fabsf(f[i].y)));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+  const float scale = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+  const float inv = 1.0f / scale;
+  *scale_out = scale;
+  Vec16 out;
+  uint32_t* o = reinterpret_cast<uint32_t*>(&out);
+  #pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 lo = make_float2(f[2 * i].x * inv, f[2 * i].y * inv);
+    const float2 hi = make_float2(f[2 * i + 1].x * inv, f[2 * i + 1].y * inv);
+    const uint32_t l = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3);
+    const uint32_t h = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3);
+    o[i] = l | (h << 16);
+  }
+  return out;
+}
+
+template <int TEAM>
+__device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st,
+                                    const DispatchSendArgs& a, uint32_t* dyn_smem) {
+  const A2ALocal& ws = st.local;
+  const Team<TEAM> team;
+  const int world = cfg.world;
+  const int K = cfg.topk;
+  const int L = cfg.experts_per_rank;
+  const int my_group = st.rank / cfg.dp_size;
+  const int my_tp = st.rank % cfg.dp_size;
+  const uint32_t iter = read_iter(ws, kPhaseDispatchSend);
+  const uint32_t par = iter & 1u;
+
+  int T = a.num_tokens;
+  if (a.bound_m != nullptr) T = min(T, *a.bound_m);
+  T = max(0, min(T, cfg.max_num_tokens));
+
+  __shared__ uint32_t s_idx[kMaxTeams][kMaxTopK];
+  __shared__ float s_w[kMaxTeams][kMaxTopK];
+  __shared__ uint32_t s_slot[kMaxTeams][kMaxRanks];
+
+  // ---- the last block counts tokens per expert and pushes the counts ----
+  if (blockIdx.x == gridDim.x - 1) {
+    uint32_t* hist = dyn_smem;                  // [num_experts]
+    uint32_t* nrec = dyn_smem + cfg.num_experts;  // [kMaxRanks]
+    for (int i = threadIdx.x; i < cfg.num_experts + kMaxRanks; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (int t = threadIdx.x; t < T; t += blockDim.x) {
+      uint32_t mask = 0;
+      for (int k = 0; k < K; ++k) {
+        const uint32_t e = a.indices[t * a.indices_stride + k];
+        if (e < static_cast<uint32_t>(cfg.num_experts)) {
+          atomicAdd(&hist[e], 1u);
+          mask |= 1u << (e / L);
+        } else {
+          report(ws, kStatusBadExpertIndex, kPhaseDispatchSend, t, e);
+        }
+      }
+      while (mask) {
+        const int d = __ffs(mask) - 1;
+        mask &= mask - 1;
+        atomicAdd(&nrec[d], 1u);
+      }
+    }
+    __syncthreads();
+    const int per_dst = L + 1;
+    for (int i = threadIdx.x; i < world * per_dst; i += blockDim.x) {
+      const int d = i / per_dst;
+      const int j = i % per_dst;
+      if (d % cfg.dp_size != my_tp) continue;
+      uint32_t v;
+      if (j == 0) {
+        v = nrec[d];
+      } else {
+        const int e = d * L + (j - 1);
+        v = e < cfg.num_experts ? hist[e] : 0u;
+      }
+      uint32_t* dst = reinterpret_cast<uint32_t*>(st.sync[d] + cfg.off_counts) +
+                      my_group * cfg.counts_stride + j;
+      st_stream_u32(dst, v);
+    }
+  }
+
+  // ---- token loop: one team per token ----
+  const uint32_t nvec = cfg.d_payload_bytes / 16;
+  const int hs = cfg.hidden_dim_scale;
+  for (int t = team.id; t < T; t += team.count) {
+    if (team.lane < K) {
+      s_idx[team.in_block][team.lane] = a.indices[t * a.indices_stride + team.lane];
+      s_w[team.in_block][team.lane] = a.weights[t * a.weights_stride + team.lane];
+    }
+    team.sync();
+    if (team.lane < kMaxRanks) {
+      const int d = team.lane;
+      uint32_t slot = kNoSlot;
+      if (d < world && d % cfg.dp_size == my_tp) {
+        bool hit = false;
+        for (int k = 0; k < K; ++k) {
+          const uint32_t e = s_idx[team.in_block][k];
+          hit |= (e < static_cast<uint32_t>(cfg.num_experts)) && (e / L == static_cast<uint32_t>(d));
+        }
+        if (hit) {
+          slot = atom_relaxed_gpu_add(&ws.send_cursor[par * kMaxRanks + d], 1u);
+          if (slot >= static_cast<uint32_t>(cfg.max_num_tokens)) {
+            report(ws, kStatusRecordOverflow, kPhaseDispatchSend, d, slot);
+            slot = kNoSlot;
+          }
+        }
+      }
+      s_slot[team.in_block][d] = slot;
+    }
+    team.sync();
+
+    uint8_t* rec[kMaxRanks];
+    #pragma unroll
+    for (int d = 0; d < kMaxRanks; ++d) {
+      const uint32_t slot = s_slot[team.in_block][d];
+      rec[d] = slot == kNoSlot
+                   ? nullptr
+                   : st.recv[d] + cfg.off_drecv + my_group * cfg.drecv_group_stride +
+                         static_cast<uint64_t>(slot) * cfg.d_stride;
+    }
+
+    // header
+    for (int wi = team.lane; wi < 1 + 2 * K; wi += TEAM) {
+      uint32_t word;
+      if (wi == 0) {
+        word = static_cast<uint32_t>(t);
+      } else if (wi <= K) {
+        word = s_idx[team.in_block][wi - 1];
+      } else {
+        word = __float_as_uint(s_w[team.in_block][wi - 1 - K]);
+      }
+      #pragma unroll
+      for (int d = 0; d < kMaxRanks; ++d) {
+        if (rec[d] != nullptr) st_stream_u32(rec[d] + 4 * wi, word);
+      }
+    }
+
+    const uint8_t* src = a.x + static_cast<uint64_t>(t) * a.x_stride;
+    if (!a.quantize) {
+      constexpr int U = 4;
+      for (uint32_t i0 = team.lane; i0 < nvec; i0 += TEAM * U) {
+        Vec16 v[U];
+        #pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint32_t i = i0 + u * TEAM;
+          if (i < nvec) v[u] = ld_input_v4(src + 16ull * i);
+        }
+        #pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint32_t i = i0 + u * TEAM;
+          if (i < nvec) {
+            #pragma unroll
+            for (int d = 0; d < kMaxRanks; ++d) {
+              if (rec[d] != nullptr) st_stream_v4(rec[d] + cfg.d_header_bytes + 16ull * i, v[u]);
+            }
+          }
+        }
+      }
+      // scales travel packed as fp32 right after the payload
+      if (hs > 0) {
+        const float* xs = reinterpret_cast<const float*>(a.x_scale);
+        for (int j = team.lane; j < hs; j += TEAM) {
+          const float s = xs[t * a.x_scale_stride_token + j * a.x_scale_stride_elem];
+          #pragma unroll
+          for (int d = 0; d < kMaxRanks; ++d) {
+            if (rec[d] != nullptr) {
+              st_stream_u32(rec[d] + cfg.d_header_bytes + cfg.d_payload_bytes + 4 * j,
+                            __float_as_uint(s));
+            }
+          }
+        }
+      }
+    } else {
+      // bf16 in, e4m3 + one fp32 scale per 128 elements out. Lane i converts elements
+      // [16 i, 16 i + 16); lanes 8 j .. 8 j + 7 of a warp share scale j.
+      const uint32_t warp_lane = threadIdx.x & 31u;
+      const uint32_t lane_base = team.lane - warp_lane;
+      for (uint32_t base = lane_base; base < nvec; base += TEAM) {
+        const uint32_t i = base + warp_lane;
+        const bool valid = i < nvec;
+        Vec16 lo = {0, 0, 0, 0}, hi = {0, 0, 0, 0};
+        if (valid) {
+          lo = ld_input_v4(src + 32ull * i);
+          hi = ld_input_v4(src + 32ull * i + 16);
+        }
+        float scale;
+        const Vec16 q = quantize16(lo, hi, &scale);
+        if (valid) {
+          #pragma unroll
+          for (int d = 0; d < kMaxRanks; ++d) {
+            if (rec[d] != nullptr) {
+              st_stream_v4(rec[d] + cfg.d_header_bytes + 16ull * i, q);
+              if ((i & 7u) == 0) {
+                st_stream_u32(rec[d] + cfg.d_header_bytes + cfg.d_payload_bytes + 4 * (i >> 3),
+                              __float_as_uint(scale));
+              }
+            }
+          }
+        }
+      }
+    }
+    team.sync();
+  }
+
+  // ---- arrival signal: one increment per block and destination ----
+  __syncthreads();
+  if (threadIdx.x < world && threadIdx.x % cfg.dp_size == my_tp) {
+    fence_acq_rel_sys();
+    red_release_sys_add(flag_ptr(st.sync[threadIdx.x], 0, my_group), 1u);
+  }
+  if (threadIdx.x == 0 && blockIdx.x == 0) atomicAdd(&ws.stats[0], static_cast<unsigned long long>(T));
+  finish_phase(cfg, ws, kPhaseDispatchSend, iter);
+}
+
+// ---------------------------------------------------------------------------
+// dispatch_recv
+// ---------------------------------------------------------------------------
+
+// Compacts the entries of the team's first warp for which `valid` holds into
+// out_a/out_b (shared memory) and returns their number in *out_n. Must be called by
+// all 32 lanes of that warp.
+__device__ __forceinline__ void compact_warp(bool valid, uint32_t va, uint32_t vb, uint32_t* out_a,
+                                             uint32_t* out_b, uint32_t* out_n) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint32_t mask = __ballot_sync(0xffffffffu, valid);
+  if (valid) {
+    const uint32_t pos = __popc(mask & ((1u << lane) - 1u));
+    out_a[pos] = va;
+    out_b[pos] = vb;
+  }
+  if (lane == 0) *out_n = __popc(mask);
+}
+
+template <int TEAM>
+__device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
+                                    const DispatchRecvArgs& a, uint32_t* dyn_smem) {
+  const A2ALocal& ws = st.local;
+  const Team<TEAM> team;
+  const int G = cfg.num_groups;
+  const int K = cfg.topk;
+  const int L = cfg.experts_per_rank;
+  const int rank = st.rank;
+  const uint32_t iter = read_iter(ws, kPhaseDispatchRecv);
+  const uint32_t par = iter & 1u;
+  const uint32_t expected = (iter + 1) * gridDim.x;
+
+  __shared__ uint32_t s_abort;
+  __shared__ uint32_t s_rec_prefix[kMaxRanks + 1];
+  __shared__ uint32_t s_rows[kMaxTeams][kMaxTopK];
+  __shared__ uint32_t s_unused[kMaxTeams][kMaxTopK];
+  __shared__ uint32_t s_nrows[kMaxTeams];
+
+  if (threadIdx.x == 0) s_abort = ws.status[0] != 0 ? 1u : 0u;
+  __syncthreads();
+  if (threadIdx.x < G) {
+    uint64_t waited;
+    const bool ok = wait_flag(flag_ptr(st.sync[rank], 0, threadIdx.x), expected,
+                              cfg.wait_limit_ns, &waited);
+    if (!ok) {
+      report(ws, kStatusWaitTimeout, kPhaseDispatchRecv, threadIdx.x, expected);
+      s_abort = 1;
+    }
+    if (blockIdx.x == 0) atomicMax(&ws.stats[2], static_cast<unsigned long long>(waited));
+  }
+  __syncthreads();
+  const bool abort = s_abort != 0;  // uniform across the block
+
+  // ---- expert-major layout from the counts (every block computes it privately) ----
+  uint32_t* cnt = dyn_smem;           // [G][L]
+  uint32_t* base = cnt + G * L;       // [G][L]  first row of (group, expert)
+  uint32_t* total = base + G * L;     // [L]
+  uint32_t* pad_off = total + L;      // [L]
+  uint32_t* misc = pad_off + L;       // [0] padded row count
+  const uint32_t* counts = reinterpret_cast<const uint32_t*>(st.sync[rank] + cfg.off_counts);
+  const uint32_t pad = static_cast<uint32_t>(cfg.expert_padding);
+  if (!abort) {
+    for (int i = threadIdx.x; i < G * L; i += blockDim.x) {
+      const int g = i / L, le = i % L;
+      cnt[i] = ld_relaxed_sys(counts + g * cfg.counts_stride + 1 + le);
+    }
+    if (threadIdx.x == 0) {
+      uint32_t acc = 0;
+      for (int g = 0; g < G; ++g) {
+        s_rec_prefix[g] = acc;
+        acc += min(ld_relaxed_sys(counts + g * cfg.counts_stride),
+                   static_cast<uint32_t>(cfg.max_num_tokens));
+      }
+      for (int g = G; g <= kMaxRanks; ++g) s_rec_prefix[g] = acc;
+    }
+    __syncthreads();
+    for (int le = threadIdx.x; le < L; le += blockDim.x) {
+      uint32_t sum = 0;
+      for (int g = 0; g < G; ++g) sum += cnt[g * L + le];
+      total[le] = sum;
+    }
+    __syncthreads();
+    // exclusive scan of the padded totals by warp 0
+    if (threadIdx.x < 32) {
+      const int per = (L + 31) / 32;
+      const int lo = threadIdx.x * per;
+      const int hi = min(lo + per, L);
+      uint32_t sum = 0;
+      for (int j = lo; j < hi; ++j) sum += (total[j] + pad - 1) / pad * pad;
+      uint32_t incl = sum;
+      #pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (threadIdx.x >= o) incl += n;
+      }
+      uint32_t run = incl - sum;
+      for (int j = lo; j < hi; ++j) {
+        pad_off[j] = run;
+        run += (total[j] + pad - 1) / pad * pad;
+      }
+      if (threadIdx.x == 31) misc[0] = incl;
+    }
+    __syncthreads();
+    for (int le = threadIdx.x; le < L; le += blockDim.x) {
+      uint32_t run = pad_off[le];
+      for (int g = 0; g < G; ++g) {
+        base[g * L + le] = run;
+        run += cnt[g * L + le];
+      }
+    }
+    __syncthreads();
+
+    const uint32_t padded_rows = misc[0];
+    const uint32_t row_cap = a.out_rows ? min(a.out_rows, cfg.max_recv_rows) : cfg.max_recv_rows;
+    if (blockIdx.x == 0) {
+      for (int le = threadIdx.x; le < L; le += blockDim.x) {
+        a.out_num_tokens[le] = static_cast<int32_t>(total[le]);
+        ws.expert_meta[2 + le] = total[le];
+        ws.expert_meta[2 + L + le] = pad_off[le];
+        // rows that only exist as padding carry no source
+        const uint32_t end = pad_off[le] + (total[le] + pad - 1) / pad * pad;
+        for (uint32_t r = pad_off[le] + total[le]; r < end && r < cfg.max_recv_rows; ++r) {
+          ws.row_src[r] = kNoSlot;
+        }
+      }
+      if (threadIdx.x == 0) {
+        ws.expert_meta[0] = min(padded_rows, row_cap);
+        ws.expert_meta[1] = s_rec_prefix[G];
+        if (padded_rows > row_cap) {
+          report(ws, kStatusRowOverflow, kPhaseDispatchRecv, padded_rows, row_cap);
+        }
+      }
+    }
+
+    // ---- record loop: one team per record ----
+    const uint32_t nvec = cfg.d_payload_bytes / 16;
+    const int hs = cfg.hidden_dim_scale;
+    const uint32_t total_recs = s_rec_prefix[G];
+    const uint8_t* drecv = st.recv[rank] + cfg.off_drecv;
+    for (uint32_t r = team.id; r < total_recs; r += team.count) {
+      int g = 0;
+      #pragma unroll
+      for (int j = 1; j < kMaxRanks; ++j) {
+        if (j < G && r >= s_rec_prefix[j]) g = j;
+      }
+      const uint32_t ri = r - s_rec_prefix[g];
+      const uint8_t* rec =
+          drecv + g * cfg.drecv_group_stride + static_cast<uint64_t>(ri) * cfg.d_stride;
+      const uint32_t* hdr = reinterpret_cast<const uint32_t*>(rec);
+      if (team.lane < 32) {
+        const int k = team.lane;
+        uint32_t row = kNoSlot;
+        if (k < K) {
+          const uint32_t e = ld_relaxed_sys(hdr + 1 + k);
+          const uint32_t t = ld_relaxed_sys(hdr);
+          if (e < static_cast<uint32_t>(cfg.num_experts) && e / L == static_cast<uint32_t>(rank)) {
+            const int le = e - rank * L;
+            row = base[g * L + le] +
+                  atom_relaxed_gpu_add(&ws.place_cursor[par * (G * L) + g * L + le], 1u);
+            if (row < row_cap) {
+              ws.row_src[row] = g;
+              ws.row_tk[row] = t * K + k;
+            } else {
+              row = kNoSlot;
+            }
+          }
+          if (cfg.combine_mode == kCombinePreReduce) {
+            ws.rec_rows[static_cast<uint64_t>(r) * K + k] = row;
+            ws.rec_weights[static_cast<uint64_t>(r) * K + k] =
+                __uint_as_float(ld_relaxed_sys(hdr + 1 + K + k));
+            if (k == 0) {
+              ws.rec_token[2 * r] = t;
+              ws.rec_token[2 * r + 1] = g;
+            }
+          }
+        }
+        compact_warp(row != kNoSlot, row, 0u, s_rows[team.in_block], s_unused[team.in_block],
+                     &s_nrows[team.in_block]);
+      }
+      team.sync();
+
+      const uint32_t nrows = s_nrows[team.in_block];
+      constexpr int U = 4;
+      for (uint32_t i0 = team.lane; i0 < nvec; i0 += TEAM * U) {
+        Vec16 v[U];
+        #pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint32_t i = i0 + u * TEAM;
+          if (i < nvec) v[u] = ld_stream_v4(rec + cfg.d_header_bytes + 16ull * i);
+        }
+        for (uint32_t j = 0; j < nrows; ++j) {
+          uint8_t* dst = a.out_x + static_cast<uint64_t>(s_rows[team.in_block][j]) * a.out_x_stride;
+          #pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint32_t i = i0 + u * TEAM;
+            if (i < nvec) st_stream_v4(dst + 16ull * i, v[u]);
+          }
+        }
+      }
+      if (hs > 0 && a.out_x_scale != nullptr) {
+        float* os = reinterpret_cast<float*>(a.out_x_scale);
+        for (int j = team.lane; j < hs; j += TEAM) {
+          const uint32_t bits = ld_relaxed_sys(
+              reinterpret_cast<const uint32_t*>(rec + cfg.d_header_bytes + cfg.d_payload_bytes) + j);
+          for (uint32_t q = 0; q < nrows; ++q) {
+            os[static_cast<int64_t>(s_rows[team.in_block][q]) * a.out_x_scale_stride_token +
+               j * a.out_x_scale_stride_elem] = __uint_as_float(bits);
+          }
+        }
+      }
+      team.sync();
+    }
+  }
+  finish_phase(cfg, ws, kPhaseDispatchRecv, iter);
+}
+
+// ---------------------------------------------------------------------------
+// combine_send
+// ---------------------------------------------------------------------------
+
+template <typename T>
+struct Elem8;  // 8 consecutive elements as fp32
+
+template <>
+struct Elem8<__nv_bfloat16> {
+  static constexpr int kBytes = 16;
+  __device__ static __forceinline__ void load(const uint8_t* p, float (&f)[8], bool stream) {
+    const Vec16 v = stream ? ld_stream_v4(p) : ld_input_v4(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __bfloat1622float2(h[i]);
+      f[2 * i] = x.x;
+      f[2 * i + 1] = x.y;
+    }
+  }
+  __device__ static __forceinline__ void store(uint8_t* p, const float (&f)[8]) {
+    Vec16 v;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    st_stream_v4(p, v);
+  }
+};
+
+template <>
+struct Elem8<__half> {
+  static constexpr int kBytes = 16;
+  __device__ static __forceinline__ void load(const uint8_t* p, float (&f)[8], bool stream) {
+    const Vec16 v = stream ? ld_stream_v4(p) : ld_input_v4(p);
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 x = __half22float2(h[i]);
+      f[2 * i] = x.x;
+      f[2 * i + 1] = x.y;
+    }
+  }
+  __device__ static __forceinline__ void store(uint8_t* p, const float (&f)[8]) {
+    Vec16 v;
+    __half2* h = reinterpret_cast<__half2*>(&v);
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    st_stream_v4(p, v);
+  }
+};
+
+template <>
+struct Elem8<float> {
+  static constexpr int kBytes = 32;
+  __device__ static __forceinline__ void load(const uint8_t* p, float (&f)[8], bool stream) {
+    const Vec16 a = stream ? ld_stream_v4(p) : ld_input_v4(p);
+    const Vec16 b = stream ? ld_stream_v4(p + 16) : ld_input_v4(p + 16);
+    f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y);
+    f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
+    f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y);
+    f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
+  }
+  __device__ static __forceinline__ void store(uint8_t* p, const float (&f)[8]) {
+    Vec16 a, b;
+    a.x = __float_as_uint(f[0]); a.y = __float_as_uint(f[1]);
+    a.z = __float_as_uint(f[2]); a.w = __float_as_uint(f[3]);
+    b.x = __float_as_uint(f[4]); b.y = __float_as_uint(f[5]);
+    b.z = __float_as_uint(f[6]); b.w = __float_as_uint(f[7]);
+    st_stream_v4(p, a);
+    st_stream_v4(p + 16, b);
+  }
+};
+
+// acc += sum_j w[j] * rows[j][granule], eight independent 16/32-byte loads in flight.
+template <typename Y>
+__device__ __forceinline__ void weighted_gather8(float (&acc)[8], const uint8_t* base,
+                                                 uint64_t row_stride, const uint32_t* rows,
+                                                 const uint32_t* weights_bits, uint32_t n,
+                                                 uint64_t byte_off, bool stream) {
+  for (uint32_t j0 = 0; j0 < n; j0 += 8) {
+    float f[8][8];
+    #pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (j0 + u < n) {
+        Elem8<Y>::load(base + static_cast<uint64_t>(rows[j0 + u]) * row_stride + byte_off, f[u],
+                       stream);
+      }
+    }
+    #pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (j0 + u < n) {
+        const float w = __uint_as_float(weights_bits[j0 + u]);
+        #pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] = fmaf(w, f[u][q], acc[q]);
+      }
+    }
+  }
+}
+
+// Per-route mode: plain byte copy of each valid expert row to every member of the
+// origin dp group. Pre-reduce mode: weighted partial sum per received record.
+template <int TEAM, typename Y>
+__device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
+                                   const CombineSendArgs& a) {
+  const A2ALocal& ws = st.local;
+  const Team<TEAM> team;
+  const int K = cfg.topk;
+  const uint32_t iter = read_iter(ws, kPhaseCombineSend);
+
+  __shared__ uint32_t s_healthy;
+  __shared__ uint32_t s_rows[kMaxTeams][kMaxTopK];
+  __shared__ uint32_t s_wbits[kMaxTeams][kMaxTopK];
+  __shared__ uint32_t s_n[kMaxTeams];
+  if (threadIdx.x == 0) s_healthy = ws.status[0] == 0 ? 1u : 0u;
+  __syncthreads();
+  const bool healthy = s_healthy != 0;
+
+  if (healthy && cfg.combine_mode == kCombinePerRoute) {
+    const uint32_t rows = ws.expert_meta[0];
+    const uint32_t nvec = cfg.c_stride / 16;
+    for (uint32_t row = team.id; row < rows; row += team.count) {
+      const uint32_t g = ws.row_src[row];
+      if (g == kNoSlot) continue;
+      const uint32_t tk = ws.row_tk[row];
+      const uint8_t* src = a.expert_y + static_cast<uint64_t>(row) * a.expert_y_stride;
+      uint8_t* dst[kMaxRanks];
+      #pragma unroll
+      for (int m = 0; m < kMaxRanks; ++m) {
+        dst[m] = m < cfg.dp_size ? st.recv[g * cfg.dp_size + m] + cfg.off_crecv +
+                                       static_cast<uint64_t>(tk) * cfg.c_stride
+                                 : nullptr;
+      }
+      constexpr int U = 4;
+      for (uint32_t i0 = team.lane; i0 < nvec; i0 += TEAM * U) {
+        Vec16 v[U];
+        #pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint32_t i = i0 + u * TEAM;
+          if (i < nvec) v[u] = ld_input_v4(src + 16ull * i);
+        }
+        #pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint32_t i = i0 + u * TEAM;
+          if (i < nvec) {
+            #pragma unroll
+            for (int m = 0; m < kMaxRanks; ++m) {
+              if (dst[m] != nullptr) st_stream_v4(dst[m] + 16ull * i, v[u]);
+            }
+          }
+        }
+      }
+    }
+  } else if (healthy) {
+    const uint32_t recs = ws.expert_meta[1];
+    const uint32_t ngran = cfg.hidden_dim / 8;
+    for (uint32_t r = team.id; r < recs; r += team.count) {
+      const uint32_t t = ws.rec_token[2 * r];
+      const uint32_t g = ws.rec_token[2 * r + 1];
+      if (team.lane < 32) {
+        const int k = team.lane;
+        uint32_t row = kNoSlot, wb = 0;
+        if (k < K) {
+          row = ws.rec_rows[static_cast<uint64_t>(r) * K + k];
+          wb = __float_as_uint(ws.rec_weights[static_cast<uint64_t>(r) * K + k]);
+        }
+        compact_warp(row != kNoSlot, row, wb, s_rows[team.in_block], s_wbits[team.in_block],
+                     &s_n[team.in_block]);
+      }
+      team.sync();
+      const uint32_t n = s_n[team.in_block];
+      const uint64_t slot = static_cast<uint64_t>(t) * cfg.world + st.rank;
+      for (uint32_t i = team.lane; i < ngran; i += TEAM) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        weighted_gather8<Y>(acc, a.expert_y, a.expert_y_stride, s_rows[team.in_block],
+                            s_wbits[team.in_block], n, static_cast<uint64_t>(i) * Elem8<Y>::kBytes,
+                            false);
+        for (int m = 0; m < cfg.dp_size; ++m) {
+          Elem8<Y>::store(st.recv[g * cfg.dp_size + m] + cfg.off_crecv + slot * cfg.c_stride +
+                              static_cast<uint64_t>(i) * Elem8<Y>::kBytes,
+                          acc);
+        }
+      }
+      team.sync();
+    }
+  }
+
+  __syncthreads();
+  if (threadIdx.x < cfg.world) {
+    fence_acq_rel_sys();
+    red_release_sys_add(flag_ptr(st.sync[threadIdx.x], 1, st.rank), 1u);
+  }
+  finish_phase(cfg, ws, kPhaseCombineSend, iter);
+}
+
+// ---------------------------------------------------------------------------
+// combine_recv
+// ---------------------------------------------------------------------------
+
+template <int TEAM, typename Y, typename O>
+__device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
+                                   const CombineRecvArgs& a) {
+  const A2ALocal& ws = st.local;
+  const Team<TEAM> team;
+  const int K = cfg.topk;
+  const int L = cfg.experts_per_rank;
+  const uint32_t iter = read_iter(ws, kPhaseCombineRecv);
+  const uint32_t expected = (iter + 1) * gridDim.x;
+
+  __shared__ uint32_t s_abort;
+  __shared__ uint32_t s_slot[kMaxTeams][kMaxTopK];
+  __shared__ uint32_t s_wbits[kMaxTeams][kMaxTopK];
+  __shared__ uint32_t s_n[kMaxTeams];
+  if (threadIdx.x == 0) s_abort = ws.status[0] != 0 ? 1u : 0u;
+  __syncthreads();
+  if (threadIdx.x < cfg.world) {
+    uint64_t waited;
+    const bool ok = wait_flag(flag_ptr(st.sync[st.rank], 1, threadIdx.x), expected,
+                              cfg.wait_limit_ns, &waited);
+    if (!ok) {
+      report(ws, kStatusWaitTimeout, kPhaseCombineRecv, threadIdx.x, expected);
+      s_abort = 1;
+    }
+    if (blockIdx.x == 0) atomicMax(&ws.stats[3], static_cast<unsigned long long>(waited));
+  }
+  __syncthreads();
+
+  int T = a.num_tokens;
+  if (a.bound_m != nullptr) T = min(T, *a.bound_m);
+  T = max(0, min(T, cfg.max_num_tokens));
+
+  if (s_abort == 0) {
+    const uint8_t* crecv = st.recv[st.rank] + cfg.off_crecv;
+    const uint32_t ngran = cfg.hidden_dim / 8;
+    for (int t = team.id; t < T; t += team.count) {
+      if (team.lane < 32) {
+        const int k = team.lane;
+        bool valid = false;
+        uint32_t slot = 0, wb = 0;
+        if (k < K) {
+          const uint32_t e = a.indices[t * a.indices_stride + k];
+          if (e < static_cast<uint32_t>(cfg.num_experts)) {
+            if (cfg.combine_mode == kCombinePerRoute) {
+              valid = true;
+              slot = static_cast<uint32_t>(t) * K + k;
+              wb = __float_as_uint(a.weights[t * a.weights_stride + k]);
+            } else {
+              // one partial per distinct destination rank; weights were applied remotely
+              const uint32_t d = e / L;
+              bool first = true;
+              for (int q = 0; q < k; ++q) {
+                const uint32_t eq = a.indices[t * a.indices_stride + q];
+                first &= !(eq < static_cast<uint32_t>(cfg.num_experts) && eq / L == d);
+              }
+              valid = first;
+              slot = static_cast<uint32_t>(t) * cfg.world + d;
+              wb = __float_as_uint(1.0f);
+            }
+          }
+        }
+        compact_warp(valid, slot, wb, s_slot[team.in_block], s_wbits[team.in_block],
+                     &s_n[team.in_block]);
+      }
+      team.sync();
+      const uint32_t n = s_n[team.in_block];
+      uint8_t* out_row = a.out_tokens + static_cast<uint64_t>(t) * a.out_tokens_stride * sizeof(O);
+      for (uint32_t i = team.lane; i < ngran; i += TEAM) {
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (a.accumulate) {
+          Elem8<O>::load(out_row + static_cast<uint64_t>(i) * Elem8<O>::kBytes, acc, true);
+        }
+        weighted_gather8<Y>(acc, crecv, cfg.c_stride, s_slot[team.in_block],
+                            s_wbits[team.in_block], n, static_cast<uint64_t>(i) * Elem8<Y>::kBytes,
+                            true);
+        Elem8<O>::store(out_row + static_cast<uint64_t>(i) * Elem8<O>::kBytes, acc);
+      }
+      team.sync();
+    }
+  }
+  finish_phase(cfg, ws, kPhaseCombineRecv, iter);
+}
+
+// ---------------------------------------------------------------------------
+// kernels
+// ---------------------------------------------------------------------------
+
+template <int TEAM>
+__global__ void __launch_bounds__(kA2AThreads, 1)
+dispatch_kernel(const __grid_constant__ A2AConfig cfg, const __grid_constant__ A2ARankStates states,
+                const __grid_constant__ PerRank<DispatchSendArgs> send,
+                const __grid_constant__ PerRank<DispatchRecvArgs> recv, int do_send, int do_recv) {
+  extern __shared__ __align__(16) uint32_t dyn_smem[];
+  const A2ARankState& st = states.r[blockIdx.y];
+  if (do_send) dispatch_send_phase<TEAM>(cfg, st, send.r[blockIdx.y], dyn_smem);
+  if (do_send && do_recv) __syncthreads();
+  if (do_recv) dispatch_recv_phase<TEAM>(cfg, st, recv.r[blockIdx.y], dyn_smem);
+}
+
+template <int TEAM, typename Y>
+__global__ void __launch_bounds__(kA2AThreads, 1)
+combine_send_kernel(const __grid_constant__ A2AConfig cfg,
+                    const __grid_constant__ A2ARankStates states,
+                    const __grid_constant__ PerRank<CombineSendArgs> send) {
+  combine_send_phase<TEAM, Y>(cfg, states.r[blockIdx.y], send.r[blockIdx.y]);
+}
+
+template <int TEAM, typename Y, typename O>
+__global__ void __launch_bounds__(kA2AThreads, 1)
+combine_recv_kernel(const __grid_constant__ A2AConfig cfg,
+                    const __grid_constant__ A2ARankStates states,
+                    const __grid_constant__ PerRank<CombineRecvArgs> recv) {
+  combine_recv_phase<TEAM, Y, O>(cfg, states.r[blockIdx.y], recv.r[blockIdx.y]);
+}
+
+template <int TEAM, typename Y, typename O>
+__global__ void __launch_bounds__(kA2AThreads, 1)
+combine_kernel(const __grid_constant__ A2AConfig cfg, const __grid_constant__ A2ARankStates states,
+               const __grid_constant__ PerRank<CombineSendArgs> send,
+               const __grid_constant__ PerRank<CombineRecvArgs> recv) {
+  combine_send_phase<TEAM, Y>(cfg, states.r[blockIdx.y], send.r[blockIdx.y]);
+  __syncthreads();
+  combine_recv_phase<TEAM, Y, O>(cfg, states.r[blockIdx.y], recv.r[blockIdx.y]);
+}
+
+size_t dispatch_smem_bytes(const A2AConfig& cfg) {
+  const size_t send = (cfg.num_experts + kMaxRanks) * sizeof(uint32_t);
+  const size_t gl = static_cast<size_t>(cfg.num_groups) * cfg.experts_per_rank;
+  const size_t recv = (2 * gl + 2 * cfg.experts_per_rank + 32) * sizeof(uint32_t);
+  return send > recv ? send : recv;
+}
+
+template <typename F>
+cudaError_t with_team(int team, F&& f) {
+  switch (team) {
+    case 32: return f(std::integral_constant<int, 32>{});
+    case 128: return f(std::integral_constant<int, 128>{});
+    case 512: return f(std::integral_constant<int, 512>{});
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+template <typename F>
+cudaError_t with_dtype(int dtype, F&& f) {
+  switch (dtype) {
+    case kDtypeBF16: return f(static_cast<__nv_bfloat16*>(nullptr));
+    case kDtypeF16: return f(static_cast<__half*>(nullptr));
+    case kDtypeF32: return f(static_cast<float*>(nullptr));
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+template <typename Kern, typename... Args>
+cudaError_t launch(Kern kern, dim3 grid, size_t smem, cudaStream_t stream, bool cooperative,
+                   Args... args) {
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+  }
+  void* params[] = {const_cast<void*>(static_cast<const void*>(&args))...};
+  if (cooperative) {
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kern), grid,
+                                       dim3(kA2AThreads), params, smem, stream);
+  }
+  return cudaLaunchKernel(reinterpret_cast<const void*>(kern), grid, dim3(kA2AThreads), params,
+                          smem, stream);
+}
+
+}  // namespace
+
+int a2a_pick_team(const A2AConfig& cfg, int64_t work_items) {
+  // Largest team that still gives every work item its own team in the first wave.
+  const int64_t warps = static_cast<int64_t>(cfg.num_blocks) * (kA2AThreads / 32);
+  int team_warps = 16;
+  while (team_warps > 1 && warps / team_warps < work_items) team_warps >>= 2;
+  return team_warps * 32;
+}
+
+cudaError_t a2a_launch_dispatch(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
+                                const PerRank<DispatchSendArgs>& send,
+                                const PerRank<DispatchRecvArgs>& recv, bool do_send, bool do_recv,
+                                int team, cudaStream_t stream) {
+  const dim3 grid(cfg.num_blocks, nranks);
+  const size_t smem = dispatch_smem_bytes(cfg);
+  // One launch that plays several ranks contains blocks that wait for one another:
+  // co-residency must be guaranteed (or the launch refused) by the driver.
+  const bool cooperative = nranks > 1 && do_send && do_recv;
+  return with_team(team, [&](auto t) {
+    constexpr int TEAM = decltype(t)::value;
+    return launch(dispatch_kernel<TEAM>, grid, smem, stream, cooperative, cfg, states, send, recv,
+                  static_cast<int>(do_send), static_cast<int>(do_recv));
+  });
+}
+
+cudaError_t a2a_launch_combine(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
+                               const PerRank<CombineSendArgs>& send,
+                               const PerRank<CombineRecvArgs>& recv, bool do_send, bool do_recv,
+                               int y_dtype, int out_dtype, int team, cudaStream_t stream) {
+  const dim3 grid(cfg.num_blocks, nranks);
+  return with_team(team, [&](auto t) {
+    constexpr int TEAM = decltype(t)::value;
+    return with_dtype(y_dtype, [&](auto* yp) {
+      using Y = std::remove_pointer_t<decltype(yp)>;
+      if (do_send && !do_recv) {
+        return launch(combine_send_kernel<TEAM, Y>, grid, 0, stream, false, cfg, states, send);
+      }
+      return with_dtype(out_dtype, [&](auto* op) {
+        using O = std::remove_pointer_t<decltype(op)>;
+        if (do_send) {
+          return launch(combine_kernel<TEAM, Y, O>, grid, 0, stream, nranks > 1, cfg, states, send,
+                        recv);
+        }
+        return launch(combine_recv_kernel<TEAM, Y, O>, grid, 0, stream, false, cfg, states, recv);
+      });
+    });
+  });
+}
+
+}  // namespace pplx

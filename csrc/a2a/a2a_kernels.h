@@ -1,0 +1,26 @@
+// Launchers of the dispatch / combine kernels (implemented in a2a_kernels.cu).
+// Counterpart of the reference's p2p-all-to-all/a2a-kernels/src/a2a/a2a_kernels.h:17-141,
+// with structs instead of ~30 positional pointers per call.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include "a2a_types.h"
+
+namespace pplx {
+
+// Threads that cooperate on one token/record (32, 128 or 512) for `work_items` items.
+int a2a_pick_team(const A2AConfig& cfg, int64_t work_items);
+
+// `nranks` > 1 plays that many virtual ranks in one launch on the current device.
+cudaError_t a2a_launch_dispatch(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
+                                const PerRank<DispatchSendArgs>& send,
+                                const PerRank<DispatchRecvArgs>& recv, bool do_send, bool do_recv,
+                                int team, cudaStream_t stream);
+
+cudaError_t a2a_launch_combine(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
+                               const PerRank<CombineSendArgs>& send,
+                               const PerRank<CombineRecvArgs>& recv, bool do_send, bool do_recv,
+                               int y_dtype, int out_dtype, int team, cudaStream_t stream);
+
+}  // namespace pplx

@@ -1,0 +1,184 @@
+// Plain-data description of one expert-parallel all-to-all context.
+//
+// The protocol is device-only: every rank owns a *symmetric* region (same layout
+// on every rank, mapped into every peer over NVLink) made of
+//
+//   flags    one 128-byte line per (phase, source): cumulative arrival counters
+//   counts   per source dp-group: {#records, per-local-expert token counts}
+//   drecv    dispatch records, one fixed-capacity region per source dp-group
+//   crecv    combine records, indexed by the origin's (token, k) or (token, rank)
+//
+// A dispatch record is sent once per (token, destination rank) and replicated to
+// the experts of that rank on arrival:
+//
+//   [ header | payload (hidden * in_elemsize, 16-byte padded) | scales ]
+//   header words: [0] token index at the source, [1..K] expert ids, [1+K..2K]
+//   fp32 routing weights; padded to 16 bytes.
+//
+// The reference sends one copy per route and keeps a 16-byte reserved trailer
+// instead (p2p-all-to-all/a2a-kernels/src/a2a/a2a_dispatch_send.cu:586-588,
+// p2p-all-to-all/src/a2a_worker.rs:317-325).
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+namespace pplx {
+
+constexpr int kMaxRanks = 8;          // one NVSwitch domain
+constexpr int kMaxTopK = 16;
+constexpr int kMaxVirtualRanks = 8;   // ranks emulated by one launch on one GPU
+constexpr int kA2AThreads = 512;
+constexpr uint32_t kNoSlot = 0xffffffffu;
+constexpr int kFlagStrideWords = 32;  // 128 bytes per flag
+
+// Indices into the per-context launch counters.
+enum A2APhase : int {
+  kPhaseDispatchSend = 0,
+  kPhaseDispatchRecv = 1,
+  kPhaseCombineSend = 2,
+  kPhaseCombineRecv = 3,
+  kNumPhases = 4,
+};
+
+// Values of status[0]. status[1] = phase, status[2] = peer/group, status[3] = detail.
+enum A2AStatus : uint32_t {
+  kStatusOk = 0,
+  kStatusWaitTimeout = 1,     // a bounded wait on an arrival flag ran out
+  kStatusRowOverflow = 2,     // more expert rows than the output tensor holds
+  kStatusBadExpertIndex = 3,  // indices[t][k] >= num_experts
+  kStatusRecordOverflow = 4,  // more records than a source region holds
+};
+
+enum A2ACombineMode : int {
+  kCombinePerRoute = 0,   // one record per (token, k); weights applied at the origin
+  kCombinePreReduce = 1,  // expert rank applies the dispatch-time weights and sends
+                          // one partial sum per (token, expert rank)
+};
+
+struct A2AConfig {
+  int world;             // ranks in the NVLink domain
+  int dp_size;           // ranks that hold identical tokens (TP replication factor)
+  int num_groups;        // world / dp_size
+  int num_experts;
+  int experts_per_rank;  // ceil(num_experts / world)
+  int topk;
+  int max_num_tokens;    // per dp group and per call
+  int hidden_dim;
+  int hidden_dim_scale;  // 0 when there are no scales
+  int in_elemsize;
+  int out_elemsize;      // element size of combine records (expert_y)
+  int expert_padding;
+  int combine_mode;
+  int num_blocks;        // grid.x of every a2a kernel (arrival counters depend on it)
+
+  // wire format
+  uint32_t d_header_bytes;
+  uint32_t d_payload_bytes;
+  uint32_t d_scale_bytes;
+  uint32_t d_stride;       // bytes per dispatch record
+  uint32_t c_stride;       // bytes per combine record
+  uint32_t c_records_per_token;  // topk (per-route) or world (pre-reduce)
+  uint32_t counts_stride;  // u32 words per source group in the counts table
+  uint32_t max_recv_rows;  // capacity of the row tables (expert-major rows)
+
+  // symmetric layout, byte offsets
+  uint64_t sync_bytes;
+  uint64_t off_counts;          // inside the sync region
+  uint64_t recv_bytes;
+  uint64_t off_drecv;           // inside the recv region
+  uint64_t drecv_group_stride;
+  uint64_t off_crecv;
+
+  uint64_t wait_limit_ns;
+};
+
+// Device-local (not peer visible) workspace of one rank.
+struct A2ALocal {
+  uint32_t* iters;         // [kNumPhases] completed launches per phase
+  uint32_t* done;          // [kNumPhases] blocks that finished the current launch
+  uint32_t* send_cursor;   // [2][kMaxRanks] next record slot per destination
+  uint32_t* place_cursor;  // [2][num_groups * experts_per_rank]
+  uint32_t* row_src;       // [max_recv_rows] source dp group of a row, kNoSlot = padding
+  uint32_t* row_tk;        // [max_recv_rows] token * topk + k at the source
+  uint32_t* expert_meta;   // [0] padded row count, [1] record count,
+                           // [2 .. 2+L) totals, [2+L .. 2+2L) padded offsets
+  uint32_t* rec_rows;      // pre-reduce: [num_groups * max_num_tokens][topk] row or kNoSlot
+  float* rec_weights;      // pre-reduce: same shape, routing weight
+  uint32_t* rec_token;     // pre-reduce: [num_groups * max_num_tokens] token index
+  uint32_t* status;        // [4]
+  uint32_t* host_flag;     // pinned host word (device-mapped): failure code, readable by the
+                           // host without synchronising the stream
+  unsigned long long* stats;  // [8] counters: records sent, rows placed, max wait ns...
+};
+
+struct A2ARankState {
+  int rank;
+  int pad_;
+  A2ALocal local;
+  uint8_t* sync[kMaxRanks];  // every rank's sync region as mapped here
+  uint8_t* recv[kMaxRanks];  // every rank's recv region as mapped here
+};
+
+struct A2ARankStates {
+  A2ARankState r[kMaxVirtualRanks];
+};
+
+struct DispatchSendArgs {
+  const uint8_t* x;
+  uint64_t x_stride;  // bytes
+  const uint8_t* x_scale;
+  int64_t x_scale_stride_elem;   // in elements
+  int64_t x_scale_stride_token;  // in elements
+  const uint32_t* indices;
+  uint64_t indices_stride;  // elements
+  const float* weights;
+  uint64_t weights_stride;  // elements
+  const int32_t* bound_m;
+  int32_t num_tokens;
+  int32_t quantize;  // 1: x is bf16 and is quantised to e4m3 with 1x128 scales on the fly
+};
+
+struct DispatchRecvArgs {
+  int32_t* out_num_tokens;
+  uint8_t* out_x;
+  uint64_t out_x_stride;  // bytes
+  uint8_t* out_x_scale;
+  int64_t out_x_scale_stride_elem;
+  int64_t out_x_scale_stride_token;
+  uint32_t out_rows;  // rows available in out_x (0 = unknown: trust max_recv_rows)
+  uint32_t pad_;
+};
+
+struct CombineSendArgs {
+  const uint8_t* expert_y;
+  uint64_t expert_y_stride;  // bytes
+};
+
+struct CombineRecvArgs {
+  uint8_t* out_tokens;
+  uint64_t out_tokens_stride;  // elements
+  const uint32_t* indices;
+  uint64_t indices_stride;
+  const float* weights;
+  uint64_t weights_stride;
+  const int32_t* bound_m;
+  int32_t num_tokens;
+  int32_t accumulate;
+};
+
+template <typename T>
+struct PerRank {
+  T r[kMaxVirtualRanks];
+};
+
+// Scalar types understood by the combine kernel (values match torch's ScalarType).
+enum A2ADtype : int {
+  kDtypeF16 = 5,
+  kDtypeF32 = 6,
+  kDtypeBF16 = 15,
+};
+
+static inline uint64_t round_up_u64(uint64_t a, uint64_t b) { return (a + b - 1) / b * b; }
+
+}  // namespace pplx

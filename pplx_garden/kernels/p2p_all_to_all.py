@@ -1,0 +1,358 @@
+"""Expert-parallel dispatch / combine over NVLink peer memory.
+
+``P2PAllToAll`` keeps the constructor and the ``dispatch`` / ``combine`` / ``destroy``
+signatures of the reference's python/pplx_garden/kernels/p2p_all_to_all.py:50-534, so
+serving code written against it runs unchanged. What happens underneath differs:
+
+* every rank allocates two CUDA-VMM regions (flags + counts, and the receive buffers),
+  exports them as POSIX file descriptors and maps every peer's regions, as the reference
+  does for its NVLink path (`:205-261`); there is no send buffer, no RDMA registration
+  and no host proxy thread, because the kernels push counts, tokens and arrival signals
+  directly into the peers' memory;
+* receive regions are sized for the worst case (each source token reaches a rank at most
+  once), so ``max_private_tokens`` has nothing left to tune and is accepted for
+  compatibility only; ``nets_per_gpu`` likewise;
+* a world larger than one NVSwitch domain (8 GPUs) needs an RDMA transport and is
+  rejected here.
+
+Extensions (keyword-only, all optional): ``combine_mode="pre_reduce"`` makes the expert
+ranks apply the routing weights given at dispatch time and send one partial sum per
+(token, expert rank) instead of one row per route; passing bf16 ``dp_x`` to a context
+whose ``in_dtype`` is ``float8_e4m3fn`` with ``hidden_dim_scale = hidden_dim // 128`` and
+``dp_x_scale=None`` quantises on the fly (one fp32 scale per 1x128 block).
+"""
+
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from pplx_garden.distributed import ParallelGroup
+from pplx_garden.kernels.all_to_all import AllToAllKernel
+from pplx_garden.native.cumem import (
+    CUMemAllocHandle,
+    CUMemExportHandle,
+    CUMemHandleKind,
+    CUMemMapping,
+)
+from pplx_garden.native.p2p_all_to_all import AllToAllContext
+from pplx_garden.utils import logging_utils
+from pplx_garden.utils.math import ceil_div
+
+logger = logging_utils.get_logger(__name__)
+
+_NVLINK_DOMAIN = 8
+
+
+@dataclass
+class _RankRegions:
+    sync_handle: CUMemExportHandle
+    recv_handle: CUMemExportHandle
+
+
+@dataclass
+class _PeerMappings:
+    sync: CUMemMapping
+    recv: CUMemMapping
+
+
+class P2PAllToAll(AllToAllKernel):
+    def __init__(
+        self,
+        *,
+        max_num_tokens: int,
+        num_experts: int,
+        expert_padding: int,
+        hidden_dim: int,
+        hidden_dim_scale: Optional[int],
+        in_dtype: torch.dtype,
+        out_dtype: torch.dtype,
+        scale_dtype: Optional[torch.dtype],
+        num_experts_per_token: int,
+        nets_per_gpu: int = 0,
+        max_private_tokens: Optional[int] = None,
+        device: torch.device,
+        dp_group: Optional[ParallelGroup],
+        node_group: Optional[ParallelGroup] = None,
+        global_group: Optional[ParallelGroup],
+        combine_mode: str = "per_route",
+        num_blocks: int = 0,
+        wait_limit_ms: int = 0,
+    ) -> None:
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise ValueError("P2PAllToAll needs a CUDA device")
+        if device.index is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        if (hidden_dim_scale is None) != (scale_dtype is None):
+            raise ValueError("hidden_dim_scale and scale_dtype must be given together")
+        if scale_dtype is not None and scale_dtype != torch.float32:
+            raise ValueError("only float32 scales are supported")
+
+        self._hidden_dim = hidden_dim
+        self._hidden_dim_scale = hidden_dim_scale
+        self._num_experts_per_token = num_experts_per_token
+        self._in_dtype = in_dtype
+        self._out_dtype = out_dtype
+        self._scale_dtype = scale_dtype
+        self._device = device
+        self._global_group = global_group
+        self._dp_size = dp_group.size if dp_group is not None else 1
+
+        rank = global_group.rank if global_group is not None else 0
+        world_size = global_group.size if global_group is not None else 1
+        if world_size > _NVLINK_DOMAIN:
+            raise NotImplementedError(
+                f"world size {world_size} exceeds one NVLink domain ({_NVLINK_DOMAIN} GPUs); "
+                "the inter-node path needs an RDMA NIC, which this build does not drive"
+            )
+        if node_group is not None and node_group.size != world_size:
+            logger.info(
+                "node_group of %d ranks inside a world of %d: all ranks share one NVSwitch "
+                "domain here, so all traffic uses NVLink", node_group.size, world_size)
+        self._rank = rank
+        self._world_size = world_size
+        self._num_local_experts = ceil_div(num_experts, world_size)
+        self._max_num_tokens = max_num_tokens
+        self._all_to_all: Optional[AllToAllContext] = None
+
+        props = torch.cuda.get_device_properties(device)
+        layout = AllToAllContext.layout(
+            hidden_dim=hidden_dim,
+            hidden_dim_scale=hidden_dim_scale,
+            in_elemsize=in_dtype.itemsize,
+            out_elemsize=out_dtype.itemsize,
+            scale_elemsize=scale_dtype.itemsize if scale_dtype else None,
+            max_num_tokens=max_num_tokens,
+            num_experts=num_experts,
+            expert_padding=expert_padding,
+            num_experts_per_token=num_experts_per_token,
+            dp_size=self._dp_size,
+            world_size=world_size,
+            combine_mode=combine_mode,
+            num_blocks=num_blocks,
+            num_sms=props.multi_processor_count,
+        )
+        self._layout = layout
+        self.max_recv_rows: int = layout["max_recv_rows"]
+
+        torch.cuda.set_device(device)
+        handle_kind = CUMemHandleKind.FileDescriptor
+        self._sync_handle = CUMemAllocHandle(layout["sync_bytes"], device, handle_kind)
+        self._recv_handle = CUMemAllocHandle(layout["recv_bytes"], device, handle_kind)
+        sync_mapping = self._sync_handle.map(device)
+        recv_mapping = self._recv_handle.map(device)
+        sync_mapping.to_tensor((sync_mapping.size,), torch.uint8).zero_()
+        torch.cuda.synchronize(device)
+
+        self._mappings: list[_PeerMappings] = []
+        if world_size > 1:
+            assert global_group is not None
+            mine = _RankRegions(self._sync_handle.export(), self._recv_handle.export())
+            everyone = global_group.all_gather_object(mine)
+            for peer, regions in enumerate(everyone):
+                if peer == rank:
+                    self._mappings.append(_PeerMappings(sync_mapping, recv_mapping))
+                else:
+                    self._mappings.append(
+                        _PeerMappings(
+                            regions.sync_handle.bind(device).map(device),
+                            regions.recv_handle.bind(device).map(device),
+                        )
+                    )
+            # Every peer has imported our descriptors: the exporter may now close them.
+            global_group.barrier()
+            del mine, everyone
+        else:
+            self._mappings.append(_PeerMappings(sync_mapping, recv_mapping))
+
+        self._all_to_all = AllToAllContext.create(
+            hidden_dim=hidden_dim,
+            hidden_dim_scale=hidden_dim_scale,
+            in_elemsize=in_dtype.itemsize,
+            out_elemsize=out_dtype.itemsize,
+            out_dtype=out_dtype,
+            scale_elemsize=scale_dtype.itemsize if scale_dtype else None,
+            max_num_tokens=max_num_tokens,
+            max_private_tokens=max_private_tokens,
+            num_experts=num_experts,
+            expert_padding=expert_padding,
+            num_experts_per_token=num_experts_per_token,
+            rank=rank,
+            dp_size=self._dp_size,
+            node_size=world_size,
+            world_size=world_size,
+            sync_ptrs=[m.sync.data_ptr() for m in self._mappings],
+            recv_ptrs=[m.recv.data_ptr() for m in self._mappings],
+            device=device.index,
+            combine_mode=combine_mode,
+            num_blocks=num_blocks,
+            wait_limit_ms=wait_limit_ms,
+        )
+        self._check_every = int(os.environ.get("PPLX_A2A_CHECK_EVERY", "0"))
+        self._calls = 0
+
+        # No rank may signal a peer whose flags are not zeroed yet.
+        if global_group is not None:
+            global_group.barrier()
+
+    # ------------------------------------------------------------------
+    @property
+    def num_local_experts(self) -> int:
+        return self._num_local_experts
+
+    @property
+    def context(self) -> AllToAllContext:
+        assert self._all_to_all is not None
+        return self._all_to_all
+
+    def check(self) -> None:
+        """Raise if a kernel of this context reported a failure (e.g. a wait that timed out).
+        Cheap: reads a pinned host word, does not synchronise the stream."""
+        assert self._all_to_all is not None
+        if self._all_to_all.failed():
+            self._all_to_all.check()
+
+    # ------------------------------------------------------------------
+    def dispatch(
+        self,
+        out_expert_num_tokens: torch.Tensor,
+        out_expert_x: torch.Tensor,
+        out_expert_x_scale: Optional[torch.Tensor],
+        dp_x: torch.Tensor,
+        dp_x_scale: Optional[torch.Tensor],
+        indices: torch.Tensor,
+        weights: torch.Tensor,
+        bound_m: Optional[torch.Tensor] = None,
+        do_send: bool = True,
+        do_recv: bool = True,
+    ) -> None:
+        a2a = self._all_to_all
+        assert a2a is not None
+        assert do_send or do_recv
+        num_tokens = dp_x.shape[0]
+        K = self._num_experts_per_token
+        H = self._hidden_dim
+
+        assert out_expert_num_tokens.shape == (self._num_local_experts,)
+        assert out_expert_num_tokens.dtype == torch.int32 and out_expert_num_tokens.stride(0) == 1
+        assert out_expert_x.dim() == 2 and out_expert_x.shape[1] == H
+        assert out_expert_x.stride(1) == 1 and out_expert_x.dtype == self._in_dtype
+        out_rows = out_expert_x.shape[0]
+        out_x_stride = out_expert_x.stride(0) * out_expert_x.element_size()
+
+        if out_expert_x_scale is not None:
+            assert out_expert_x_scale.dtype == self._scale_dtype
+            out_scale = (out_expert_x_scale.data_ptr(), out_expert_x_scale.stride(1),
+                         out_expert_x_scale.stride(0))
+        else:
+            out_scale = (None, None, None)
+
+        assert dp_x.shape == (num_tokens, H) and dp_x.stride(1) == 1
+        quantize = False
+        if dp_x.dtype != self._in_dtype:
+            # fused quantisation: bf16 in, e4m3 + 1x128 fp32 scales on the wire
+            assert dp_x.dtype == torch.bfloat16 and self._in_dtype == torch.float8_e4m3fn, (
+                f"dp_x is {dp_x.dtype}, the context was built for {self._in_dtype}")
+            assert dp_x_scale is None and self._hidden_dim_scale == H // 128
+            assert out_expert_x_scale is not None
+            quantize = True
+        if dp_x_scale is not None:
+            assert self._scale_dtype is not None and self._hidden_dim_scale is not None
+            assert out_expert_x_scale is not None
+            assert dp_x_scale.dtype == self._scale_dtype
+            in_scale = (dp_x_scale.data_ptr(), dp_x_scale.stride(1), dp_x_scale.stride(0))
+        else:
+            assert quantize or (self._scale_dtype is None and self._hidden_dim_scale is None)
+            in_scale = (None, None, None)
+
+        assert indices.shape == (num_tokens, K) and indices.stride(1) == 1
+        assert indices.dtype == torch.uint32
+        assert weights.shape == (num_tokens, K) and weights.stride(1) == 1
+        assert weights.dtype == torch.float32
+        if bound_m is not None:
+            assert bound_m.numel() == 1 and bound_m.dtype == torch.int32
+            bound_m_ptr = bound_m.data_ptr()
+        else:
+            bound_m_ptr = None
+
+        stream = torch.cuda.current_stream().cuda_stream
+        send = (num_tokens, dp_x.data_ptr(), dp_x.stride(0) * dp_x.element_size(), *in_scale,
+                indices.data_ptr(), indices.stride(0), weights.data_ptr(), weights.stride(0),
+                bound_m_ptr)
+        recv = (out_expert_num_tokens.data_ptr(), out_expert_x.data_ptr(), out_x_stride, *out_scale)
+        if do_send and do_recv:
+            a2a.dispatch(*send, *recv, stream, out_rows, quantize)
+        elif do_send:
+            a2a.dispatch_send(*send, stream, quantize)
+        else:
+            a2a.dispatch_recv(*recv, stream, out_rows)
+
+    # ------------------------------------------------------------------
+    def combine(
+        self,
+        out_tokens: torch.Tensor,
+        indices: torch.Tensor,
+        weights: torch.Tensor,
+        expert_y: torch.Tensor,
+        bound_m: Optional[torch.Tensor] = None,
+        do_send: bool = True,
+        do_recv: bool = True,
+        accumulate: bool = False,
+    ) -> None:
+        a2a = self._all_to_all
+        assert a2a is not None
+        assert do_send or do_recv
+        assert not accumulate or self._dp_size == 1, "accumulate is not supported with dp_size > 1"
+        K = self._num_experts_per_token
+        H = self._hidden_dim
+        num_tokens = indices.shape[0]
+
+        assert out_tokens.shape == (num_tokens, H) and out_tokens.stride(1) == 1
+        assert out_tokens.dtype == self._out_dtype
+        assert indices.shape == (num_tokens, K) and indices.stride(1) == 1
+        assert indices.dtype == torch.uint32
+        assert weights.shape == (num_tokens, K) and weights.stride(1) == 1
+        assert weights.dtype == torch.float32
+        assert expert_y.dim() == 2 and expert_y.shape[1] == H and expert_y.stride(1) == 1
+        assert expert_y.element_size() == self._out_dtype.itemsize, (
+            "expert_y must have the element size of out_dtype")
+        if bound_m is not None:
+            assert bound_m.numel() == 1 and bound_m.dtype == torch.int32
+            bound_m_ptr = bound_m.data_ptr()
+        else:
+            bound_m_ptr = None
+
+        stream = torch.cuda.current_stream().cuda_stream
+        y_ptr = expert_y.data_ptr()
+        y_stride = expert_y.stride(0) * expert_y.element_size()
+        recv = (out_tokens.data_ptr(), out_tokens.stride(0), indices.data_ptr(), indices.stride(0),
+                weights.data_ptr(), weights.stride(0), bound_m_ptr, accumulate, stream)
+        if do_send and do_recv:
+            a2a.combine(y_ptr, y_stride, num_tokens, expert_y.dtype, *recv)
+        elif do_send:
+            a2a.combine_send(y_ptr, y_stride, stream, expert_y.dtype)
+        else:
+            a2a.combine_recv(num_tokens, expert_y.shape[0], expert_y.dtype, *recv)
+
+    # ------------------------------------------------------------------
+    def destroy(self) -> None:
+        """Tear down. Collective: every rank must call it."""
+        if self._all_to_all is None:
+            return
+        torch.cuda.synchronize(self._device)
+        # No peer may still be writing into our regions when they are unmapped.
+        if self._global_group is not None:
+            self._global_group.barrier()
+        self._all_to_all.destroy()
+        self._all_to_all = None
+        for m in self._mappings:
+            m.sync.unmap()
+            m.recv.unmap()
+        self._mappings.clear()
+        del self._sync_handle, self._recv_handle
+        if self._global_group is not None:
+            self._global_group.barrier()

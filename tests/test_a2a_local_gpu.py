@@ -1,0 +1,292 @@
+"""Multi-rank dispatch/combine on ONE GPU: every rank is a slice of one launch.
+Shapes follow the reference's parametrisation table
+(tests/p2p_all_to_all/test_p2p_all_to_all.py:240-557) plus cases for the split phases,
+bound_m, accumulate, repeated iterations, pre-reduced combine and fused quantisation."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import pytest
+import torch
+
+from pplx_garden.kernels import oracle
+from tests.a2a_data import act, make_rank_data
+
+pytestmark = pytest.mark.gpu
+
+
+@dataclass
+class Cfg:
+    world: int
+    dp_size: int = 1
+    tokens: int = 128
+    experts: int = 16
+    hidden: int = 128
+    hidden_scale: Optional[int] = None
+    topk: int = 2
+    in_dtype: torch.dtype = torch.float32
+    out_dtype: torch.dtype = torch.float32
+    padding: int = 1
+    combine_mode: str = "per_route"
+
+
+CONFIGS = {
+    "W1-FP32": Cfg(world=1),
+    "W2-FP32": Cfg(world=2),
+    "W2-BF16": Cfg(world=2, in_dtype=torch.bfloat16, out_dtype=torch.bfloat16),
+    "W2-BF16-PADDED": Cfg(world=2, tokens=8, hidden=16, in_dtype=torch.bfloat16,
+                          out_dtype=torch.bfloat16, padding=16),
+    "W2-SCALES": Cfg(world=2, tokens=2, hidden_scale=16, in_dtype=torch.bfloat16,
+                     out_dtype=torch.bfloat16),
+    "W4-FP32-K8": Cfg(world=4, experts=128, topk=8),
+    "W4-BF16-H7168": Cfg(world=4, experts=256, hidden=7168, topk=8, in_dtype=torch.bfloat16,
+                         out_dtype=torch.bfloat16),
+    "W4-DP2-TINY": Cfg(world=4, dp_size=2, tokens=1, experts=4, hidden=8, topk=1,
+                       in_dtype=torch.bfloat16, out_dtype=torch.bfloat16),
+    "W4-DP2": Cfg(world=4, dp_size=2, tokens=64, experts=32, hidden=256, topk=4,
+                  in_dtype=torch.bfloat16, out_dtype=torch.bfloat16),
+    "W8-BF16": Cfg(world=8, experts=128, hidden=7168, topk=8, in_dtype=torch.bfloat16,
+                   out_dtype=torch.bfloat16),
+    "W8-FP8": Cfg(world=8, tokens=256, experts=128, hidden=7168, hidden_scale=56, topk=8,
+                  in_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16),
+    "W8-UNEVEN-EXPERTS": Cfg(world=8, tokens=32, experts=60, hidden=256, topk=6,
+                             in_dtype=torch.bfloat16, out_dtype=torch.bfloat16, padding=4),
+    "W8-PRE-REDUCE": Cfg(world=8, experts=64, hidden=1024, topk=8, in_dtype=torch.bfloat16,
+                         out_dtype=torch.bfloat16, combine_mode="pre_reduce"),
+    "W2-PRE-REDUCE-FP32": Cfg(world=2, combine_mode="pre_reduce"),
+    "W8-F16-OUT": Cfg(world=8, tokens=16, experts=64, hidden=512, topk=4,
+                      in_dtype=torch.bfloat16, out_dtype=torch.float16),
+}
+
+
+def _make_group(cfg: Cfg, device, **kw):
+    from pplx_garden.kernels.local_all_to_all import LocalAllToAllGroup
+
+    return LocalAllToAllGroup(
+        world_size=cfg.world, dp_size=cfg.dp_size, max_num_tokens=cfg.tokens,
+        num_experts=cfg.experts, expert_padding=cfg.padding, hidden_dim=cfg.hidden,
+        hidden_dim_scale=cfg.hidden_scale, in_dtype=cfg.in_dtype, out_dtype=cfg.out_dtype,
+        scale_dtype=torch.float32 if cfg.hidden_scale else None,
+        num_experts_per_token=cfg.topk, device=device, combine_mode=cfg.combine_mode,
+        wait_limit_ms=2000, **kw)
+
+
+def _inputs(cfg: Cfg, device, seed_offset: int = 0):
+    groups = cfg.world // cfg.dp_size
+    data = [make_rank_data(seed=g + seed_offset, num_experts=cfg.experts, topk=cfg.topk,
+                           num_tokens=cfg.tokens, hidden_dim=cfg.hidden,
+                           hidden_dim_scale=cfg.hidden_scale,
+                           in_dtype=torch.float32 if cfg.in_dtype == torch.float8_e4m3fn else cfg.in_dtype,
+                           device=device) for g in range(groups)]
+    if cfg.in_dtype == torch.float8_e4m3fn:
+        for d in data:
+            d.dp_x = d.dp_x.clamp(-400, 400).to(torch.float8_e4m3fn)
+    return data
+
+
+def _outputs(cfg: Cfg, group, device):
+    L = group.num_local_experts
+    rows = group.max_recv_rows
+    W = cfg.world
+    num = [torch.full((L,), -1, dtype=torch.int32, device=device) for _ in range(W)]
+    ox = [torch.zeros((rows, cfg.hidden), dtype=torch.float32, device=device).to(cfg.in_dtype)
+          for _ in range(W)]
+    os_ = None
+    if cfg.hidden_scale:
+        os_ = [torch.zeros((rows, cfg.hidden_scale), dtype=torch.float32, device=device)
+               for _ in range(W)]
+    out = [torch.zeros((cfg.tokens, cfg.hidden), dtype=cfg.out_dtype, device=device)
+           for _ in range(W)]
+    return num, ox, os_, out
+
+
+def _run_once(cfg: Cfg, group, data, device, *, split=False, bound=None, accumulate=False,
+              out_prev=None):
+    W = cfg.world
+    per_rank = [data[r // cfg.dp_size] for r in range(W)]
+    num, ox, os_, out = _outputs(cfg, group, device)
+    if out_prev is not None:
+        for o, p in zip(out, out_prev):
+            o.copy_(p)
+    xs = [d.dp_x for d in per_rank]
+    scales = [d.dp_x_scale for d in per_rank] if cfg.hidden_scale else None
+    idx = [d.indices for d in per_rank]
+    wts = [d.weights for d in per_rank]
+    bm = None
+    if bound is not None:
+        bm = [torch.tensor([bound], dtype=torch.int32, device=device) for _ in range(W)]
+    if split:
+        group.dispatch(num, ox, os_, xs, scales, idx, wts, bm, do_send=True, do_recv=False)
+        group.dispatch(num, ox, os_, xs, scales, idx, wts, bm, do_send=False, do_recv=True)
+    else:
+        group.dispatch(num, ox, os_, xs, scales, idx, wts, bm)
+    ys = [act(ox[r], None if os_ is None else os_[r]).to(cfg.out_dtype) for r in range(W)]
+    if split:
+        group.combine(out, idx, wts, ys, bm, do_send=True, do_recv=False, accumulate=accumulate)
+        group.combine(out, idx, wts, ys, bm, do_send=False, do_recv=True, accumulate=accumulate)
+    else:
+        group.combine(out, idx, wts, ys, bm, accumulate=accumulate)
+    torch.cuda.synchronize()
+    group.check()
+    return num, ox, os_, out
+
+
+def _verify(cfg: Cfg, data, num, ox, os_, out, *, bound=None, out_prev=None):
+    groups = cfg.world // cfg.dp_size
+    n_tok = None if bound is None else [bound] * groups
+    for r in range(cfg.world):
+        exp = oracle.expected_dispatch(
+            r, cfg.world, cfg.experts, cfg.padding,
+            [d.dp_x.cpu() for d in data],
+            [d.dp_x_scale.cpu() for d in data] if cfg.hidden_scale else None,
+            [d.indices.cpu() for d in data], n_tok)
+        oracle.check_dispatch(exp, num[r], ox[r], None if os_ is None else os_[r])
+        d = data[r // cfg.dp_size]
+        T = cfg.tokens if bound is None else bound
+        want = act(d.dp_x[:T].cpu().to(torch.float32) if cfg.hidden_scale is None else d.dp_x[:T].cpu(),
+                   None if d.dp_x_scale is None else d.dp_x_scale[:T].cpu())
+        want = want.to(cfg.out_dtype).to(torch.float32)
+        if out_prev is not None:
+            want = want + out_prev[r][:T].cpu().to(torch.float32)
+        got = out[r][:T].cpu().to(torch.float32)
+        tol = dict(rtol=2e-2, atol=2e-2) if cfg.out_dtype != torch.float32 else dict(rtol=1e-5, atol=1e-5)
+        if cfg.hidden_scale:
+            tol = dict(rtol=3e-2, atol=0.5)
+        torch.testing.assert_close(got, want, **tol, msg=lambda m, r=r: f"rank {r} combine: {m}")
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_dispatch_combine(name: str) -> None:
+    cfg = CONFIGS[name]
+    device = torch.device("cuda", 0)
+    group = _make_group(cfg, device)
+    try:
+        data = _inputs(cfg, device)
+        num, ox, os_, out = _run_once(cfg, group, data, device)
+        _verify(cfg, data, num, ox, os_, out)
+    finally:
+        group.destroy()
+
+
+def test_repeated_iterations_and_split_phases() -> None:
+    """Flags are cumulative and cursors double-buffered: many iterations with new routing
+    each time, alternating fused and split launches, must all be exact."""
+    cfg = Cfg(world=4, tokens=48, experts=32, hidden=512, topk=4, in_dtype=torch.bfloat16,
+              out_dtype=torch.bfloat16, padding=8)
+    device = torch.device("cuda", 0)
+    group = _make_group(cfg, device)
+    try:
+        for it in range(6):
+            data = _inputs(cfg, device, seed_offset=100 * it)
+            num, ox, os_, out = _run_once(cfg, group, data, device, split=bool(it % 2))
+            _verify(cfg, data, num, ox, os_, out)
+        iters = group.context.iterations(0)
+        assert list(iters) == [6, 6, 6, 6]
+    finally:
+        group.destroy()
+
+
+def test_bound_m_and_accumulate() -> None:
+    cfg = Cfg(world=2, tokens=64, experts=16, hidden=256, topk=4)
+    device = torch.device("cuda", 0)
+    group = _make_group(cfg, device)
+    try:
+        data = _inputs(cfg, device)
+        num, ox, os_, out = _run_once(cfg, group, data, device, bound=17)
+        _verify(cfg, data, num, ox, os_, out, bound=17)
+        for r in range(cfg.world):
+            assert torch.count_nonzero(out[r][17:]) == 0, "rows past bound_m must stay untouched"
+        prev = [torch.randn((cfg.tokens, cfg.hidden), device=device) for _ in range(cfg.world)]
+        num, ox, os_, out = _run_once(cfg, group, data, device, accumulate=True, out_prev=prev)
+        _verify(cfg, data, num, ox, os_, out, out_prev=prev)
+    finally:
+        group.destroy()
+
+
+def test_zero_tokens() -> None:
+    cfg = Cfg(world=2, tokens=4, experts=8, hidden=64, topk=2)
+    device = torch.device("cuda", 0)
+    group = _make_group(cfg, device)
+    try:
+        data = _inputs(cfg, device)
+        num, ox, os_, out = _run_once(cfg, group, data, device, bound=0)
+        for r in range(cfg.world):
+            assert num[r].sum().item() == 0
+    finally:
+        group.destroy()
+
+
+def test_fused_quantisation_matches_reference_quantiser() -> None:
+    """bf16 tokens in, e4m3 + one fp32 scale per 1x128 block at the experts."""
+    cfg = Cfg(world=4, tokens=32, experts=32, hidden=1024, hidden_scale=8, topk=4,
+              in_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16)
+    device = torch.device("cuda", 0)
+    group = _make_group(cfg, device)
+    try:
+        groups = cfg.world
+        raw = [make_rank_data(seed=g, num_experts=cfg.experts, topk=cfg.topk, num_tokens=cfg.tokens,
+                              hidden_dim=cfg.hidden, hidden_dim_scale=None, in_dtype=torch.bfloat16,
+                              device=device) for g in range(groups)]
+        num, ox, os_, out = _outputs(cfg, group, device)
+        group.dispatch(num, ox, os_, [d.dp_x for d in raw], None, [d.indices for d in raw],
+                       [d.weights for d in raw])
+        torch.cuda.synchronize()
+        group.check()
+        quant = [oracle.quantize_1x128(d.dp_x.cpu().to(torch.float32)) for d in raw]
+        for r in range(cfg.world):
+            exp = oracle.expected_dispatch(
+                r, cfg.world, cfg.experts, cfg.padding,
+                [q[0].to(torch.float32) for q in quant], [q[1] for q in quant],
+                [d.indices.cpu() for d in raw])
+            torch.testing.assert_close(num[r].cpu(), exp.num_tokens, rtol=0, atol=0)
+            # de-quantised rows must agree with the float reference quantiser
+            for le, (start, want, ws) in enumerate(zip(exp.block_start, exp.rows, exp.scales)):
+                n = want.shape[0]
+                got = ox[r][start:start + n].cpu().to(torch.float32)
+                gs = os_[r][start:start + n].cpu()
+                deq_got = got * gs.repeat_interleave(128, dim=1)
+                deq_want = want * ws.repeat_interleave(128, dim=1)
+                key_g = deq_got.sum(dim=1).argsort()
+                key_w = deq_want.sum(dim=1).argsort()
+                torch.testing.assert_close(deq_got[key_g], deq_want[key_w], rtol=0.07, atol=1e-3)
+        ys = [(ox[r].to(torch.float32) * os_[r].repeat_interleave(128, dim=1) * 2).to(cfg.out_dtype)
+              for r in range(cfg.world)]
+        group.combine(out, [d.indices for d in raw], [d.weights for d in raw], ys)
+        torch.cuda.synchronize()
+        group.check()
+        for r in range(cfg.world):
+            want = raw[r].dp_x.cpu().to(torch.float32) * 2
+            torch.testing.assert_close(out[r].cpu().to(torch.float32), want, rtol=0.08, atol=0.08)
+    finally:
+        group.destroy()
+
+
+def test_wait_timeout_reports_status_without_hanging() -> None:
+    """A receive whose sources never signalled must give up after the configured limit,
+    leave the context marked failed and keep the CUDA context usable."""
+    cfg = Cfg(world=2, tokens=4, experts=8, hidden=64, topk=2)
+    device = torch.device("cuda", 0)
+    from pplx_garden.kernels.local_all_to_all import LocalAllToAllGroup
+
+    group = LocalAllToAllGroup(
+        world_size=cfg.world, max_num_tokens=cfg.tokens, num_experts=cfg.experts,
+        expert_padding=1, hidden_dim=cfg.hidden, hidden_dim_scale=None, in_dtype=torch.float32,
+        out_dtype=torch.float32, scale_dtype=None, num_experts_per_token=cfg.topk, device=device,
+        wait_limit_ms=200)
+    try:
+        num, ox, os_, out = _outputs(cfg, group, device)
+        # recv without any send: the arrival flags stay at zero
+        with pytest.raises((TimeoutError, RuntimeError)):
+            group.context.dispatch_multi(None, [
+                (num[r].data_ptr(), ox[r].data_ptr(), ox[r].stride(0) * 4, None, None, None,
+                 ox[r].shape[0]) for r in range(cfg.world)], torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            group.check()
+        code, phase, who, detail, message = group.context.status(0)
+        assert code == 1 and phase == 1, message
+        # the device is still healthy
+        assert torch.ones(8, device=device).sum().item() == 8
+    finally:
+        group.destroy()
