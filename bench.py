@@ -13,8 +13,9 @@ benchmarks/bench_all_to_all.py:578-590 behind its published EP8 numbers
 (docs/fabric-lib.md:100-119). ``--tokens 4096`` gives the prefill shape.
 
 Timing: every step is bracketed by CUDA events on the launching stream; an L2 flush
-(a 256 MiB device write) and, with several ranks, a tiny all-reduce that lines the ranks
-up run before the start event, outside the timed interval. The reported value is the
+(a 256 MiB device write followed by a read of the same buffer) and, with several ranks, a
+tiny all-reduce that lines the ranks up run before the start event, outside the timed
+interval. The reported value is the
 maximum over ranks of the mean step time. The ``e2e`` entry times the same step through
 the public API including the host->device copy of the step's inputs from pinned memory and
 the device->host read of its result, with the host clock.
@@ -72,25 +73,84 @@ def reference_unavailable() -> str | None:
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a block runs."""
+    """Samples SM clock and throttle reasons of one GPU while a block runs. Reads only:
+    NVML queries from a background thread every few milliseconds (nvidia-smi as a
+    fallback), never a setting."""
 
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int) -> None:
-        self._file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
-        self._proc = None
-        try:
-            self._proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(gpu_index)],
-                stdout=self._file, stderr=subprocess.DEVNULL)
-        except OSError:
-            self._proc = None
+    def __init__(self, gpu_index: int, period_s: float = 0.005) -> None:
+        import threading
 
-    def stop(self) -> dict:
+        self._clocks: list[float] = []
+        self._max = None
+        self._reasons: set[str] = set()
+        self._stop = threading.Event()
+        self._thread = None
+        self._proc = None
+        self._file = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            # NVML enumerates physical devices; honour CUDA_VISIBLE_DEVICES when it lists indices
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = gpu_index
+            if visible:
+                try:
+                    phys = int(visible.split(",")[gpu_index])
+                except (ValueError, IndexError):
+                    phys = gpu_index
+            handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self._max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            masks = {
+                "hw_slowdown": pynvml.nvmlClocksThrottleReasonHwSlowdown,
+                "hw_thermal_slowdown": pynvml.nvmlClocksThrottleReasonHwThermalSlowdown,
+                "sw_thermal_slowdown": pynvml.nvmlClocksThrottleReasonSwThermalSlowdown,
+                "sw_power_cap": pynvml.nvmlClocksThrottleReasonSwPowerCap,
+            }
+
+            def loop() -> None:
+                while not self._stop.is_set():
+                    try:
+                        self._clocks.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                        bits = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                        for name, mask in masks.items():
+                            if bits & mask:
+                                self._reasons.add(name)
+                    except Exception:
+                        pass
+                    self._stop.wait(period_s)
+
+            self._thread = threading.Thread(target=loop, daemon=True)
+            self._thread.start()
+        except Exception:
+            self._thread = None
+            self._file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            try:
+                self._proc = subprocess.Popen(
+                    ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                     "-lms", "20", "-i", str(gpu_index)],
+                    stdout=self._file, stderr=subprocess.DEVNULL)
+            except OSError:
+                self._proc = None
+
+    def mark(self) -> int:
+        """Number of samples so far (to select the ones taken inside an interval)."""
+        return len(self._clocks)
+
+    def stop(self, first: int = 0, last: int | None = None) -> dict:
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+            clocks = self._clocks[first:last] or self._clocks
+            if clocks:
+                out.update(sm_mhz=statistics.median(clocks), sm_max_mhz=self._max,
+                           reasons=sorted(self._reasons), samples=len(clocks))
+            return out
         if self._proc is None:
             return out
         self._proc.terminate()
@@ -198,6 +258,8 @@ def main() -> None:
         out = torch.zeros((tokens, H), dtype=torch.bfloat16, device=device)
         expert_y = torch.randn((rows, H), device=device).to(torch.bfloat16)
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+        flush_words = flush.view(torch.int32)
+        flush_sum = torch.zeros((), dtype=torch.int64, device=device)
         dummy = torch.zeros(1, device=device)
 
         def step(inp) -> None:
@@ -206,7 +268,9 @@ def main() -> None:
             a2a.combine(out, idx, w, expert_y)
 
         def line_up() -> None:
+            # cold L2 without a cache full of dirty lines: write 256 MiB, then read it back
             flush.zero_()
+            torch.sum(flush_words, out=flush_sum)
             if world > 1:
                 dist.all_reduce(dummy)
 
@@ -220,14 +284,16 @@ def main() -> None:
         err = (out.to(torch.float32) - want).abs().max().item()
         assert err < 0.1 * want.abs().max().item() + 1e-3, f"dispatch/combine round trip is wrong (max err {err})"
 
+        # nvidia-smi needs a moment to start: sample from the warm-up on
+        sampler = ClockSampler(device.index)
         for i in range(warmup):
             line_up()
             step(dev_inputs[i % pool])
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier(device_ids=[device.index])
-        sampler = ClockSampler(device.index)
         torch.cuda.synchronize()
+        first_sample = sampler.mark()
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         dstarts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
@@ -261,7 +327,7 @@ def main() -> None:
         b1.record()
         torch.cuda.synchronize()
         b2b_us = b0.elapsed_time(b1) * 1000 / steps
-        clocks = sampler.stop()
+        clocks = sampler.stop(first_sample, sampler.mark())
 
         e2e = None
         if with_e2e:
@@ -350,7 +416,7 @@ def main() -> None:
                 "topk": args.topk,
                 "parallelism": f"ep{world}",
                 "combine_mode": args.combine_mode,
-                "l2": "flushed between timed steps (256 MiB device write before each start event)",
+                "l2": "flushed between timed steps (256 MiB device write, then read, before each start event)",
                 "baseline_note": "vs_baseline divides by the reference's published EP8 dispatch+combine "
                                  "(113.9 us decode / 2449.1 us prefill), whatever n_gpus is",
             },

@@ -78,7 +78,7 @@ def write_ninja(verbose: bool) -> Path:
     BUILD.mkdir(exist_ok=True)
     py_inc = sysconfig.get_paths()["include"]
     ext_suffix = sysconfig.get_config_var("EXT_SUFFIX")
-    common_inc = [f"-I{CSRC}", f"-I{CUDA_HOME}/include"]
+    common_inc = ["-Icsrc", f"-I{CUDA_HOME}/include"]
     defines = []
     if _has_header("infiniband/verbs.h"):
         defines.append("-DPPLX_HAVE_VERBS=1")
@@ -123,8 +123,11 @@ def write_ninja(verbose: bool) -> Path:
         objs = []
         for src in paths:
             rel = src.relative_to(CSRC)
-            obj = BUILD / tag / rel.with_suffix(rel.suffix + ".o")
-            obj.parent.mkdir(parents=True, exist_ok=True)
+            obj_abs = BUILD / tag / rel.with_suffix(rel.suffix + ".o")
+            obj_abs.parent.mkdir(parents=True, exist_ok=True)
+            # relative paths: the tree may be copied to another location with its build/
+            obj = obj_abs.relative_to(ROOT)
+            src = src.relative_to(ROOT)
             if src.suffix == ".cu":
                 lines.append(f"build {obj}: nvcc {src}")
             else:
@@ -136,7 +139,7 @@ def write_ninja(verbose: bool) -> Path:
 
     targets = []
     ext_objs = compile_group(groups["ext"], "ext")
-    ext_out = ROOT / "pplx_garden" / f"_native{ext_suffix}"
+    ext_out = Path("pplx_garden") / f"_native{ext_suffix}"
     lines.append(f"build {ext_out}: link_shared {' '.join(ext_objs)}")
     targets.append(str(ext_out))
 
@@ -145,14 +148,14 @@ def write_ninja(verbose: bool) -> Path:
 
     if groups["noalloc"]:
         objs = compile_group(groups["noalloc"], "noalloc")
-        out = ROOT / "pplx_garden" / "libpplx_noalloc.so"
+        out = Path("pplx_garden") / "libpplx_noalloc.so"
         lines.append(f"build {out}: link_shared {' '.join(objs)}")
         targets.append(str(out))
     for key, name in (("fabric_debug", "pplx-fabric-debug"), ("unigram_cli", "pplx-unigram-encode")):
         if groups[key]:
             objs = compile_group(groups[key], key)
-            out = ROOT / "bin" / name
-            out.parent.mkdir(exist_ok=True)
+            out = Path("bin") / name
+            (ROOT / "bin").mkdir(exist_ok=True)
             lines.append(f"build {out}: link_exe {' '.join(objs + core_objs)}")
             targets.append(str(out))
     lines.append(f"default {' '.join(targets)}")

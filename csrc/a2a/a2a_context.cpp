@@ -135,6 +135,8 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
                  "virtual ranks x blocks must fit the GPU at one block per SM");
   }
 
+  const char* trace_env = std::getenv("PPLX_A2A_TRACE");
+  cfg_.trace = (trace_env != nullptr && std::atoi(trace_env) != 0) ? 1 : 0;
   const char* team_env = std::getenv("PPLX_A2A_TEAM");
   if (team_env != nullptr) team_override_ = std::atoi(team_env);
 
@@ -164,9 +166,8 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
       off += (bytes + 255) / 256 * 256;
       return at;
     };
-    const size_t o_iters = take(sizeof(uint32_t) * kNumPhases);
-    const size_t o_done = take(sizeof(uint32_t) * kNumPhases);
-    const size_t o_send_cursor = take(sizeof(uint32_t) * 2 * kMaxRanks);
+    const size_t o_epochs = take(sizeof(uint32_t) * 2);
+    const size_t o_done = take(sizeof(uint32_t) * 2);
     const size_t o_place_cursor = take(sizeof(uint32_t) * 2 * GL);
     const size_t o_row_src = take(sizeof(uint32_t) * rows);
     const size_t o_row_tk = take(sizeof(uint32_t) * rows);
@@ -176,14 +177,14 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
     const size_t o_rec_tok = take(pre ? sizeof(uint32_t) * 2 * recs : 4);
     const size_t o_status = take(sizeof(uint32_t) * 4);
     const size_t o_stats = take(sizeof(unsigned long long) * 8);
+    const size_t o_trace = take(sizeof(unsigned long long) * kTraceSlots);
     void* base = nullptr;
     PPLX_CUDA_CHECK(cudaMalloc(&base, off));
     allocations_.push_back(base);
     PPLX_CUDA_CHECK(cudaMemset(base, 0, off));
     uint8_t* b = static_cast<uint8_t*>(base);
-    st.local.iters = reinterpret_cast<uint32_t*>(b + o_iters);
+    st.local.epochs = reinterpret_cast<uint32_t*>(b + o_epochs);
     st.local.done = reinterpret_cast<uint32_t*>(b + o_done);
-    st.local.send_cursor = reinterpret_cast<uint32_t*>(b + o_send_cursor);
     st.local.place_cursor = reinterpret_cast<uint32_t*>(b + o_place_cursor);
     st.local.row_src = reinterpret_cast<uint32_t*>(b + o_row_src);
     st.local.row_tk = reinterpret_cast<uint32_t*>(b + o_row_tk);
@@ -193,6 +194,8 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
     st.local.rec_token = reinterpret_cast<uint32_t*>(b + o_rec_tok);
     st.local.status = reinterpret_cast<uint32_t*>(b + o_status);
     st.local.stats = reinterpret_cast<unsigned long long*>(b + o_stats);
+    st.local.trace = reinterpret_cast<unsigned long long*>(b + o_trace);
+    trace_ptrs_.push_back(st.local.trace);
     uint32_t* host_flag = nullptr;
     PPLX_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&host_flag), 64, cudaHostAllocMapped));
     std::memset(host_flag, 0, 64);
@@ -202,7 +205,7 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
     host_flags_.push_back(host_flag);
     status_ptrs_.push_back(st.local.status);
     stats_ptrs_.push_back(st.local.stats);
-    iters_ptrs_.push_back(st.local.iters);
+    iters_ptrs_.push_back(st.local.epochs);
   }
   PPLX_CUDA_CHECK(cudaDeviceSynchronize());
   PPLX_INFO("a2a context: world=%d dp=%d experts=%d topk=%d hidden=%d record=%uB/%uB blocks=%d "
@@ -223,14 +226,29 @@ bool A2AContext::failed() const {
   return false;
 }
 
-int A2AContext::pick(int64_t items) const {
+void A2AContext::advance_phase(int first, int last) {
+  // The device protocol counts arrivals cumulatively and tags records with the dispatch
+  // number, so the four phases must be issued in order, each exactly once per layer.
+  static const char* names[] = {"dispatch_send", "dispatch_recv", "combine_send", "combine_recv"};
+  if (first != next_phase_) {
+    throw Error(ErrorKind::kInvalidArgument,
+                std::string("all-to-all phases out of order: got ") + names[first] +
+                    " but the next phase of this context is " + names[next_phase_] +
+                    " (sequence: dispatch_send, dispatch_recv, combine_send, combine_recv)");
+  }
+  next_phase_ = (last + 1) % kNumPhases;
+}
+
+int A2AContext::pick(int64_t items, int64_t vectors_per_item) const {
   if (team_override_ == 32 || team_override_ == 128 || team_override_ == 512) return team_override_;
-  return a2a_pick_team(cfg_, std::max<int64_t>(items, 1));
+  return a2a_pick_team(cfg_, std::max<int64_t>(items, 1), std::max<int64_t>(vectors_per_item, 1));
 }
 
 void A2AContext::dispatch(const DispatchSendArgs* send, const DispatchRecvArgs* recv, bool do_send,
                           bool do_recv, cudaStream_t stream) {
   PPLX_REQUIRE(do_send || do_recv, "dispatch: nothing to do");
+  advance_phase(do_send ? kPhaseDispatchSend : kPhaseDispatchRecv,
+                do_recv ? kPhaseDispatchRecv : kPhaseDispatchSend);
   NvtxRange range(do_send && do_recv ? "a2a_dispatch" : do_send ? "a2a_dispatch_send" : "a2a_dispatch_recv");
   PerRank<DispatchSendArgs> s{};
   PerRank<DispatchRecvArgs> r{};
@@ -259,13 +277,17 @@ void A2AContext::dispatch(const DispatchSendArgs* send, const DispatchRecvArgs* 
     }
   }
   PPLX_CUDA_CHECK(cudaSetDevice(device_));
+  // send: one item per token; recv: one item per (source group, token) slot
   const int64_t items = do_recv ? last_tokens_ * cfg_.num_groups : last_tokens_;
-  PPLX_CUDA_CHECK(a2a_launch_dispatch(cfg_, states_, n, s, r, do_send, do_recv, pick(items), stream));
+  PPLX_CUDA_CHECK(a2a_launch_dispatch(cfg_, states_, n, s, r, do_send, do_recv,
+                                      pick(items, cfg_.d_payload_bytes / 16), stream));
 }
 
 void A2AContext::combine(const CombineSendArgs* send, const CombineRecvArgs* recv, bool do_send,
                          bool do_recv, int y_dtype, int out_dtype, cudaStream_t stream) {
   PPLX_REQUIRE(do_send || do_recv, "combine: nothing to do");
+  advance_phase(do_send ? kPhaseCombineSend : kPhaseCombineRecv,
+                do_recv ? kPhaseCombineRecv : kPhaseCombineSend);
   NvtxRange range(do_send && do_recv ? "a2a_combine" : do_send ? "a2a_combine_send" : "a2a_combine_recv");
   PerRank<CombineSendArgs> s{};
   PerRank<CombineRecvArgs> r{};
@@ -289,9 +311,21 @@ void A2AContext::combine(const CombineSendArgs* send, const CombineRecvArgs* rec
   PPLX_REQUIRE(y_size == cfg_.out_elemsize,
                "combine: expert_y element size differs from the context's out dtype");
   PPLX_CUDA_CHECK(cudaSetDevice(device_));
-  const int64_t items = do_send ? tokens * cfg_.num_groups : tokens;
+  // send: one item per expert row (per-route) or per received record (pre-reduce);
+  // recv: one item per token whose reduction reads several records per output vector.
+  int64_t items, vectors;
+  if (do_send) {
+    const int64_t per_token = cfg_.combine_mode == kCombinePreReduce
+                                  ? std::min<int64_t>(cfg_.topk, cfg_.world)
+                                  : cfg_.topk;
+    items = tokens * cfg_.num_groups * per_token / cfg_.world + 1;
+    vectors = cfg_.c_stride / 16;
+  } else {
+    items = tokens;
+    vectors = static_cast<int64_t>(cfg_.hidden_dim / 8) * 8;
+  }
   PPLX_CUDA_CHECK(a2a_launch_combine(cfg_, states_, n, s, r, do_send, do_recv, y_dtype, out_dtype,
-                                     pick(items), stream));
+                                     pick(items, vectors), stream));
 }
 
 A2AStatusInfo A2AContext::status(int i) const {
@@ -321,9 +355,15 @@ std::array<uint64_t, 8> A2AContext::stats(int i) const {
   return out;
 }
 
-std::array<uint32_t, kNumPhases> A2AContext::iterations(int i) const {
-  std::array<uint32_t, kNumPhases> out{};
-  PPLX_CUDA_CHECK(cudaMemcpy(out.data(), iters_ptrs_.at(i), sizeof(uint32_t) * kNumPhases, cudaMemcpyDeviceToHost));
+std::array<uint32_t, 2> A2AContext::iterations(int i) const {
+  std::array<uint32_t, 2> out{};
+  PPLX_CUDA_CHECK(cudaMemcpy(out.data(), iters_ptrs_.at(i), sizeof(uint32_t) * 2, cudaMemcpyDeviceToHost));
+  return out;
+}
+
+std::array<uint64_t, kTraceSlots> A2AContext::trace(int i) const {
+  std::array<uint64_t, kTraceSlots> out{};
+  PPLX_CUDA_CHECK(cudaMemcpy(out.data(), trace_ptrs_.at(i), sizeof(uint64_t) * kTraceSlots, cudaMemcpyDeviceToHost));
   return out;
 }
 

@@ -72,11 +72,18 @@ class A2AContext {
   void check() const;
   // [tokens sent, reserved, max dispatch wait ns, max combine wait ns, ...]
   std::array<uint64_t, 8> stats(int i = 0) const;
-  std::array<uint32_t, kNumPhases> iterations(int i = 0) const;
+  // [completed dispatches, completed combines]
+  std::array<uint32_t, 2> iterations(int i = 0) const;
+  // Timeline of the last launches (globaltimer ns; see A2ATrace), filled when the context
+  // was created with PPLX_A2A_TRACE=1.
+  std::array<uint64_t, kTraceSlots> trace(int i = 0) const;
   void set_team_override(int team) { team_override_ = team; }
+  // Test hook: pretend the phases before `phase` were already issued.
+  void debug_set_next_phase(int phase) { next_phase_ = phase; }
 
  private:
-  int pick(int64_t items) const;
+  int pick(int64_t items, int64_t vectors_per_item) const;
+  void advance_phase(int first, int last);
 
   A2AConfig cfg_{};
   int device_;
@@ -87,6 +94,8 @@ class A2AContext {
   std::vector<uint32_t*> host_flags_;
   std::vector<unsigned long long*> stats_ptrs_;
   std::vector<uint32_t*> iters_ptrs_;
+  std::vector<unsigned long long*> trace_ptrs_;
+  int next_phase_ = kPhaseDispatchSend;
   int64_t last_tokens_ = 0;
   int team_override_ = 0;
 };

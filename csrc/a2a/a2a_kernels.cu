@@ -29,6 +29,7 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
+#include <cstdint>
 #include <type_traits>
 
 #include "a2a_kernels.h"
@@ -39,6 +40,9 @@ namespace pplx {
 namespace {
 
 constexpr int kMaxTeams = kA2AThreads / 32;
+// 16-byte vectors each thread keeps in flight in the copy loops: 512 threads x 8 x 16 B
+// = 64 KiB per SM, about what it takes to cover HBM / NVLink latency at full rate.
+constexpr int kCopyUnroll = 8;
 
 template <int TEAM>
 struct Team {
@@ -105,35 +109,40 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t expecte
   }
 }
 
-// Marks this block as finished with `phase`; the last block of the launch advances the
-// phase's launch counter and clears the cursors of the *next* launch's parity.
-__device__ __forceinline__ void finish_phase(const A2AConfig& cfg, const A2ALocal& ws, int phase,
-                                             uint32_t iter) {
+// Marks this block as finished with a *recv* phase (which = 0 dispatch, 1 combine). The
+// last block of the launch advances the epoch and clears the placement cursors that the
+// dispatch after next will use. Every block read the epoch before it got here, so the
+// increment cannot be observed by a block of the same launch.
+__device__ __forceinline__ void finish_recv(const A2AConfig& cfg, const A2ALocal& ws, int which,
+                                            uint32_t epoch, int trace_slot) {
   __syncthreads();
   __shared__ uint32_t s_last;
   if (threadIdx.x == 0) {
     __threadfence();
-    const uint32_t old = atom_acq_rel_gpu_add(&ws.done[phase], 1u);
+    const uint32_t old = atom_acq_rel_gpu_add(&ws.done[which], 1u);
     s_last = (old == gridDim.x - 1) ? 1u : 0u;
   }
   __syncthreads();
   if (s_last) {
-    const uint32_t next_par = (iter + 1) & 1u;
-    if (phase == kPhaseDispatchSend) {
-      if (threadIdx.x < kMaxRanks) ws.send_cursor[next_par * kMaxRanks + threadIdx.x] = 0;
-    } else if (phase == kPhaseDispatchRecv) {
+    if (which == 0) {
       const int n = cfg.num_groups * cfg.experts_per_rank;
+      const uint32_t next_par = (epoch + 1) & 1u;
       for (int i = threadIdx.x; i < n; i += blockDim.x) ws.place_cursor[next_par * n + i] = 0;
     }
     if (threadIdx.x == 0) {
-      ws.done[phase] = 0;
-      ws.iters[phase] = iter + 1;
+      ws.done[which] = 0;
+      ws.epochs[which] = epoch + 1;
+      if (cfg.trace) ws.trace[trace_slot] = globaltimer_ns();
     }
   }
 }
 
-__device__ __forceinline__ uint32_t read_iter(const A2ALocal& ws, int phase) {
-  return *reinterpret_cast<volatile const uint32_t*>(&ws.iters[phase]);
+__device__ __forceinline__ uint32_t read_epoch(const A2ALocal& ws, int which) {
+  return *reinterpret_cast<volatile const uint32_t*>(&ws.epochs[which]);
+}
+
+__device__ __forceinline__ void trace_mark(const A2AConfig& cfg, const A2ALocal& ws, int slot) {
+  if (cfg.trace && blockIdx.x == 0 && threadIdx.x == 0) ws.trace[slot] = globaltimer_ns();
 }
 
 // ---------------------------------------------------------------------------
@@ -183,8 +192,8 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
   const int L = cfg.experts_per_rank;
   const int my_group = st.rank / cfg.dp_size;
   const int my_tp = st.rank % cfg.dp_size;
-  const uint32_t iter = read_iter(ws, kPhaseDispatchSend);
-  const uint32_t par = iter & 1u;
+  const uint32_t tag = read_epoch(ws, 0) + 1;
+  trace_mark(cfg, ws, kTraceSendStart);
 
   int T = a.num_tokens;
   if (a.bound_m != nullptr) T = min(T, *a.bound_m);
@@ -192,29 +201,19 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
 
   __shared__ uint32_t s_idx[kMaxTeams][kMaxTopK];
   __shared__ float s_w[kMaxTeams][kMaxTopK];
-  __shared__ uint32_t s_slot[kMaxTeams][kMaxRanks];
 
-  // ---- the last block counts tokens per expert and pushes the counts ----
+  // ---- the last block counts routes per expert and pushes the counts ----
   if (blockIdx.x == gridDim.x - 1) {
-    uint32_t* hist = dyn_smem;                  // [num_experts]
-    uint32_t* nrec = dyn_smem + cfg.num_experts;  // [kMaxRanks]
-    for (int i = threadIdx.x; i < cfg.num_experts + kMaxRanks; i += blockDim.x) hist[i] = 0;
+    uint32_t* hist = dyn_smem;  // [num_experts]
+    for (int i = threadIdx.x; i < cfg.num_experts; i += blockDim.x) hist[i] = 0;
     __syncthreads();
-    for (int t = threadIdx.x; t < T; t += blockDim.x) {
-      uint32_t mask = 0;
-      for (int k = 0; k < K; ++k) {
-        const uint32_t e = a.indices[t * a.indices_stride + k];
-        if (e < static_cast<uint32_t>(cfg.num_experts)) {
-          atomicAdd(&hist[e], 1u);
-          mask |= 1u << (e / L);
-        } else {
-          report(ws, kStatusBadExpertIndex, kPhaseDispatchSend, t, e);
-        }
-      }
-      while (mask) {
-        const int d = __ffs(mask) - 1;
-        mask &= mask - 1;
-        atomicAdd(&nrec[d], 1u);
+    for (int i = threadIdx.x; i < T * K; i += blockDim.x) {
+      const int t = i / K, k = i - t * K;
+      const uint32_t e = a.indices[t * a.indices_stride + k];
+      if (e < static_cast<uint32_t>(cfg.num_experts)) {
+        atomicAdd(&hist[e], 1u);
+      } else {
+        report(ws, kStatusBadExpertIndex, kPhaseDispatchSend, t, e);
       }
     }
     __syncthreads();
@@ -225,7 +224,7 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
       if (d % cfg.dp_size != my_tp) continue;
       uint32_t v;
       if (j == 0) {
-        v = nrec[d];
+        v = static_cast<uint32_t>(T);
       } else {
         const int e = d * L + (j - 1);
         v = e < cfg.num_experts ? hist[e] : 0u;
@@ -236,51 +235,45 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
     }
   }
 
-  // ---- token loop: one team per token ----
+  // ---- token loop: one team per token; the record of token t goes to slot t ----
   const uint32_t nvec = cfg.d_payload_bytes / 16;
   const int hs = cfg.hidden_dim_scale;
+  constexpr int U = kCopyUnroll;
   for (int t = team.id; t < T; t += team.count) {
+    const uint8_t* src = a.x + static_cast<uint64_t>(t) * a.x_stride;
+    // payload loads do not depend on the routing: issue them first
+    Vec16 v[U];
+    if (!a.quantize) {
+      #pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint32_t i = team.lane + u * TEAM;
+        if (i < nvec) v[u] = ld_input_v4(src + 16ull * i);
+      }
+    }
     if (team.lane < K) {
       s_idx[team.in_block][team.lane] = a.indices[t * a.indices_stride + team.lane];
       s_w[team.in_block][team.lane] = a.weights[t * a.weights_stride + team.lane];
     }
     team.sync();
-    if (team.lane < kMaxRanks) {
-      const int d = team.lane;
-      uint32_t slot = kNoSlot;
-      if (d < world && d % cfg.dp_size == my_tp) {
-        bool hit = false;
-        for (int k = 0; k < K; ++k) {
-          const uint32_t e = s_idx[team.in_block][k];
-          hit |= (e < static_cast<uint32_t>(cfg.num_experts)) && (e / L == static_cast<uint32_t>(d));
-        }
-        if (hit) {
-          slot = atom_relaxed_gpu_add(&ws.send_cursor[par * kMaxRanks + d], 1u);
-          if (slot >= static_cast<uint32_t>(cfg.max_num_tokens)) {
-            report(ws, kStatusRecordOverflow, kPhaseDispatchSend, d, slot);
-            slot = kNoSlot;
-          }
-        }
-      }
-      s_slot[team.in_block][d] = slot;
+    uint32_t dst_mask = 0;
+    for (int k = 0; k < K; ++k) {
+      const uint32_t e = s_idx[team.in_block][k];
+      if (e < static_cast<uint32_t>(cfg.num_experts)) dst_mask |= 1u << (e / L);
     }
-    team.sync();
-
     uint8_t* rec[kMaxRanks];
     #pragma unroll
     for (int d = 0; d < kMaxRanks; ++d) {
-      const uint32_t slot = s_slot[team.in_block][d];
-      rec[d] = slot == kNoSlot
-                   ? nullptr
-                   : st.recv[d] + cfg.off_drecv + my_group * cfg.drecv_group_stride +
-                         static_cast<uint64_t>(slot) * cfg.d_stride;
+      const bool hit = d < world && ((dst_mask >> d) & 1u) && (d % cfg.dp_size == my_tp);
+      rec[d] = hit ? st.recv[d] + cfg.off_drecv + my_group * cfg.drecv_group_stride +
+                         static_cast<uint64_t>(t) * cfg.d_stride
+                   : nullptr;
     }
 
     // header
     for (int wi = team.lane; wi < 1 + 2 * K; wi += TEAM) {
       uint32_t word;
       if (wi == 0) {
-        word = static_cast<uint32_t>(t);
+        word = tag;
       } else if (wi <= K) {
         word = s_idx[team.in_block][wi - 1];
       } else {
@@ -292,15 +285,14 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
       }
     }
 
-    const uint8_t* src = a.x + static_cast<uint64_t>(t) * a.x_stride;
     if (!a.quantize) {
-      constexpr int U = 4;
       for (uint32_t i0 = team.lane; i0 < nvec; i0 += TEAM * U) {
-        Vec16 v[U];
-        #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const uint32_t i = i0 + u * TEAM;
-          if (i < nvec) v[u] = ld_input_v4(src + 16ull * i);
+        if (i0 != team.lane) {
+          #pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint32_t i = i0 + u * TEAM;
+            if (i < nvec) v[u] = ld_input_v4(src + 16ull * i);
+          }
         }
         #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -358,6 +350,7 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
     }
     team.sync();
   }
+  trace_mark(cfg, ws, kTraceSendLoopDone);
 
   // ---- arrival signal: one increment per block and destination ----
   __syncthreads();
@@ -366,7 +359,7 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
     red_release_sys_add(flag_ptr(st.sync[threadIdx.x], 0, my_group), 1u);
   }
   if (threadIdx.x == 0 && blockIdx.x == 0) atomicAdd(&ws.stats[0], static_cast<unsigned long long>(T));
-  finish_phase(cfg, ws, kPhaseDispatchSend, iter);
+  trace_mark(cfg, ws, kTraceSendSignalled);
 }
 
 // ---------------------------------------------------------------------------
@@ -397,12 +390,14 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
   const int K = cfg.topk;
   const int L = cfg.experts_per_rank;
   const int rank = st.rank;
-  const uint32_t iter = read_iter(ws, kPhaseDispatchRecv);
-  const uint32_t par = iter & 1u;
-  const uint32_t expected = (iter + 1) * gridDim.x;
+  const uint32_t epoch = read_epoch(ws, 0);
+  const uint32_t tag = epoch + 1;
+  const uint32_t par = epoch & 1u;
+  const uint32_t expected = tag * gridDim.x;
+  trace_mark(cfg, ws, kTraceRecvStart);
 
   __shared__ uint32_t s_abort;
-  __shared__ uint32_t s_rec_prefix[kMaxRanks + 1];
+  __shared__ uint32_t s_slot_prefix[kMaxRanks + 1];
   __shared__ uint32_t s_rows[kMaxTeams][kMaxTopK];
   __shared__ uint32_t s_unused[kMaxTeams][kMaxTopK];
   __shared__ uint32_t s_nrows[kMaxTeams];
@@ -421,6 +416,7 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
   }
   __syncthreads();
   const bool abort = s_abort != 0;  // uniform across the block
+  trace_mark(cfg, ws, kTraceRecvWaitDone);
 
   // ---- expert-major layout from the counts (every block computes it privately) ----
   uint32_t* cnt = dyn_smem;           // [G][L]
@@ -438,26 +434,26 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
     if (threadIdx.x == 0) {
       uint32_t acc = 0;
       for (int g = 0; g < G; ++g) {
-        s_rec_prefix[g] = acc;
+        s_slot_prefix[g] = acc;
         acc += min(ld_relaxed_sys(counts + g * cfg.counts_stride),
                    static_cast<uint32_t>(cfg.max_num_tokens));
       }
-      for (int g = G; g <= kMaxRanks; ++g) s_rec_prefix[g] = acc;
+      for (int g = G; g <= kMaxRanks; ++g) s_slot_prefix[g] = acc;
     }
     __syncthreads();
-    for (int le = threadIdx.x; le < L; le += blockDim.x) {
-      uint32_t sum = 0;
-      for (int g = 0; g < G; ++g) sum += cnt[g * L + le];
-      total[le] = sum;
-    }
-    __syncthreads();
-    // exclusive scan of the padded totals by warp 0
+    // Warp 0 owns the layout: lane j covers a contiguous chunk of experts, sums the groups,
+    // scans the padded totals across lanes and writes every (group, expert) base row.
     if (threadIdx.x < 32) {
       const int per = (L + 31) / 32;
       const int lo = threadIdx.x * per;
       const int hi = min(lo + per, L);
       uint32_t sum = 0;
-      for (int j = lo; j < hi; ++j) sum += (total[j] + pad - 1) / pad * pad;
+      for (int j = lo; j < hi; ++j) {
+        uint32_t tot = 0;
+        for (int g = 0; g < G; ++g) tot += cnt[g * L + j];
+        total[j] = tot;
+        sum += (tot + pad - 1) / pad * pad;
+      }
       uint32_t incl = sum;
       #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -467,19 +463,17 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
       uint32_t run = incl - sum;
       for (int j = lo; j < hi; ++j) {
         pad_off[j] = run;
+        uint32_t row = run;
+        for (int g = 0; g < G; ++g) {
+          base[g * L + j] = row;
+          row += cnt[g * L + j];
+        }
         run += (total[j] + pad - 1) / pad * pad;
       }
       if (threadIdx.x == 31) misc[0] = incl;
     }
     __syncthreads();
-    for (int le = threadIdx.x; le < L; le += blockDim.x) {
-      uint32_t run = pad_off[le];
-      for (int g = 0; g < G; ++g) {
-        base[g * L + le] = run;
-        run += cnt[g * L + le];
-      }
-    }
-    __syncthreads();
+    trace_mark(cfg, ws, kTraceRecvLayoutDone);
 
     const uint32_t padded_rows = misc[0];
     const uint32_t row_cap = a.out_rows ? min(a.out_rows, cfg.max_recv_rows) : cfg.max_recv_rows;
@@ -496,35 +490,48 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
       }
       if (threadIdx.x == 0) {
         ws.expert_meta[0] = min(padded_rows, row_cap);
-        ws.expert_meta[1] = s_rec_prefix[G];
+        ws.expert_meta[1] = s_slot_prefix[G];
         if (padded_rows > row_cap) {
           report(ws, kStatusRowOverflow, kPhaseDispatchRecv, padded_rows, row_cap);
         }
       }
     }
 
-    // ---- record loop: one team per record ----
+    // ---- slot loop: one team per (source group, source token) ----
     const uint32_t nvec = cfg.d_payload_bytes / 16;
     const int hs = cfg.hidden_dim_scale;
-    const uint32_t total_recs = s_rec_prefix[G];
+    const uint32_t total_slots = s_slot_prefix[G];
     const uint8_t* drecv = st.recv[rank] + cfg.off_drecv;
-    for (uint32_t r = team.id; r < total_recs; r += team.count) {
+    constexpr int U = kCopyUnroll;
+    // Wide teams have few slots each: fetch the payload together with the header
+    // instead of after it (a slot that turns out to be stale costs one wasted read).
+    constexpr bool kSpeculate = TEAM >= 128;
+    for (uint32_t s = team.id; s < total_slots; s += team.count) {
       int g = 0;
       #pragma unroll
       for (int j = 1; j < kMaxRanks; ++j) {
-        if (j < G && r >= s_rec_prefix[j]) g = j;
+        if (j < G && s >= s_slot_prefix[j]) g = j;
       }
-      const uint32_t ri = r - s_rec_prefix[g];
+      const uint32_t t = s - s_slot_prefix[g];
       const uint8_t* rec =
-          drecv + g * cfg.drecv_group_stride + static_cast<uint64_t>(ri) * cfg.d_stride;
+          drecv + g * cfg.drecv_group_stride + static_cast<uint64_t>(t) * cfg.d_stride;
       const uint32_t* hdr = reinterpret_cast<const uint32_t*>(rec);
+      Vec16 v[U];
+      if (kSpeculate) {
+        #pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const uint32_t i = team.lane + u * TEAM;
+          if (i < nvec) v[u] = ld_stream_v4(rec + cfg.d_header_bytes + 16ull * i);
+        }
+      }
       if (team.lane < 32) {
         const int k = team.lane;
         uint32_t row = kNoSlot;
         if (k < K) {
           const uint32_t e = ld_relaxed_sys(hdr + 1 + k);
-          const uint32_t t = ld_relaxed_sys(hdr);
-          if (e < static_cast<uint32_t>(cfg.num_experts) && e / L == static_cast<uint32_t>(rank)) {
+          const bool fresh = ld_relaxed_sys(hdr) == tag;
+          if (fresh && e < static_cast<uint32_t>(cfg.num_experts) &&
+              e / L == static_cast<uint32_t>(rank)) {
             const int le = e - rank * L;
             row = base[g * L + le] +
                   atom_relaxed_gpu_add(&ws.place_cursor[par * (G * L) + g * L + le], 1u);
@@ -536,12 +543,12 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
             }
           }
           if (cfg.combine_mode == kCombinePreReduce) {
-            ws.rec_rows[static_cast<uint64_t>(r) * K + k] = row;
-            ws.rec_weights[static_cast<uint64_t>(r) * K + k] =
+            ws.rec_rows[static_cast<uint64_t>(s) * K + k] = row;
+            ws.rec_weights[static_cast<uint64_t>(s) * K + k] =
                 __uint_as_float(ld_relaxed_sys(hdr + 1 + K + k));
             if (k == 0) {
-              ws.rec_token[2 * r] = t;
-              ws.rec_token[2 * r + 1] = g;
+              ws.rec_token[2 * s] = t;
+              ws.rec_token[2 * s + 1] = g;
             }
           }
         }
@@ -551,38 +558,42 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
       team.sync();
 
       const uint32_t nrows = s_nrows[team.in_block];
-      constexpr int U = 4;
-      for (uint32_t i0 = team.lane; i0 < nvec; i0 += TEAM * U) {
-        Vec16 v[U];
-        #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const uint32_t i = i0 + u * TEAM;
-          if (i < nvec) v[u] = ld_stream_v4(rec + cfg.d_header_bytes + 16ull * i);
-        }
-        for (uint32_t j = 0; j < nrows; ++j) {
-          uint8_t* dst = a.out_x + static_cast<uint64_t>(s_rows[team.in_block][j]) * a.out_x_stride;
-          #pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const uint32_t i = i0 + u * TEAM;
-            if (i < nvec) st_stream_v4(dst + 16ull * i, v[u]);
+      if (nrows != 0) {
+        for (uint32_t i0 = team.lane; i0 < nvec; i0 += TEAM * U) {
+          if (!kSpeculate || i0 != static_cast<uint32_t>(team.lane)) {
+            #pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const uint32_t i = i0 + u * TEAM;
+              if (i < nvec) v[u] = ld_stream_v4(rec + cfg.d_header_bytes + 16ull * i);
+            }
+          }
+          for (uint32_t j = 0; j < nrows; ++j) {
+            uint8_t* dst =
+                a.out_x + static_cast<uint64_t>(s_rows[team.in_block][j]) * a.out_x_stride;
+            #pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const uint32_t i = i0 + u * TEAM;
+              if (i < nvec) st_stream_v4(dst + 16ull * i, v[u]);
+            }
           }
         }
-      }
-      if (hs > 0 && a.out_x_scale != nullptr) {
-        float* os = reinterpret_cast<float*>(a.out_x_scale);
-        for (int j = team.lane; j < hs; j += TEAM) {
-          const uint32_t bits = ld_relaxed_sys(
-              reinterpret_cast<const uint32_t*>(rec + cfg.d_header_bytes + cfg.d_payload_bytes) + j);
-          for (uint32_t q = 0; q < nrows; ++q) {
-            os[static_cast<int64_t>(s_rows[team.in_block][q]) * a.out_x_scale_stride_token +
-               j * a.out_x_scale_stride_elem] = __uint_as_float(bits);
+        if (hs > 0 && a.out_x_scale != nullptr) {
+          float* os = reinterpret_cast<float*>(a.out_x_scale);
+          for (int j = team.lane; j < hs; j += TEAM) {
+            const uint32_t bits = ld_relaxed_sys(
+                reinterpret_cast<const uint32_t*>(rec + cfg.d_header_bytes + cfg.d_payload_bytes) + j);
+            for (uint32_t q = 0; q < nrows; ++q) {
+              os[static_cast<int64_t>(s_rows[team.in_block][q]) * a.out_x_scale_stride_token +
+                 j * a.out_x_scale_stride_elem] = __uint_as_float(bits);
+            }
           }
         }
       }
       team.sync();
     }
   }
-  finish_phase(cfg, ws, kPhaseDispatchRecv, iter);
+  trace_mark(cfg, ws, kTraceRecvLoopDone);
+  finish_recv(cfg, ws, 0, epoch, kTraceRecvAllDone);
 }
 
 // ---------------------------------------------------------------------------
@@ -692,7 +703,7 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
   const A2ALocal& ws = st.local;
   const Team<TEAM> team;
   const int K = cfg.topk;
-  const uint32_t iter = read_iter(ws, kPhaseCombineSend);
+  trace_mark(cfg, ws, kTraceCSendStart);
 
   __shared__ uint32_t s_healthy;
   __shared__ uint32_t s_rows[kMaxTeams][kMaxTopK];
@@ -705,11 +716,19 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
   if (healthy && cfg.combine_mode == kCombinePerRoute) {
     const uint32_t rows = ws.expert_meta[0];
     const uint32_t nvec = cfg.c_stride / 16;
+    constexpr int U = kCopyUnroll;
     for (uint32_t row = team.id; row < rows; row += team.count) {
-      const uint32_t g = ws.row_src[row];
-      if (g == kNoSlot) continue;
-      const uint32_t tk = ws.row_tk[row];
       const uint8_t* src = a.expert_y + static_cast<uint64_t>(row) * a.expert_y_stride;
+      // the row's bytes do not depend on where it goes: fetch them with its destination
+      Vec16 v[U];
+      #pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const uint32_t i = team.lane + u * TEAM;
+        if (i < nvec) v[u] = ld_input_v4(src + 16ull * i);
+      }
+      const uint32_t g = ws.row_src[row];
+      const uint32_t tk = ws.row_tk[row];
+      if (g == kNoSlot) continue;
       uint8_t* dst[kMaxRanks];
       #pragma unroll
       for (int m = 0; m < kMaxRanks; ++m) {
@@ -717,13 +736,13 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
                                        static_cast<uint64_t>(tk) * cfg.c_stride
                                  : nullptr;
       }
-      constexpr int U = 4;
       for (uint32_t i0 = team.lane; i0 < nvec; i0 += TEAM * U) {
-        Vec16 v[U];
-        #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const uint32_t i = i0 + u * TEAM;
-          if (i < nvec) v[u] = ld_input_v4(src + 16ull * i);
+        if (i0 != static_cast<uint32_t>(team.lane)) {
+          #pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint32_t i = i0 + u * TEAM;
+            if (i < nvec) v[u] = ld_input_v4(src + 16ull * i);
+          }
         }
         #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -755,50 +774,97 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
       }
       team.sync();
       const uint32_t n = s_n[team.in_block];
-      const uint64_t slot = static_cast<uint64_t>(t) * cfg.world + st.rank;
-      for (uint32_t i = team.lane; i < ngran; i += TEAM) {
-        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        weighted_gather8<Y>(acc, a.expert_y, a.expert_y_stride, s_rows[team.in_block],
-                            s_wbits[team.in_block], n, static_cast<uint64_t>(i) * Elem8<Y>::kBytes,
-                            false);
-        for (int m = 0; m < cfg.dp_size; ++m) {
-          Elem8<Y>::store(st.recv[g * cfg.dp_size + m] + cfg.off_crecv + slot * cfg.c_stride +
-                              static_cast<uint64_t>(i) * Elem8<Y>::kBytes,
-                          acc);
+      if (n != 0) {
+        const uint64_t slot = static_cast<uint64_t>(t) * cfg.world + st.rank;
+        for (uint32_t i = team.lane; i < ngran; i += TEAM) {
+          float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          weighted_gather8<Y>(acc, a.expert_y, a.expert_y_stride, s_rows[team.in_block],
+                              s_wbits[team.in_block], n,
+                              static_cast<uint64_t>(i) * Elem8<Y>::kBytes, false);
+          for (int m = 0; m < cfg.dp_size; ++m) {
+            Elem8<Y>::store(st.recv[g * cfg.dp_size + m] + cfg.off_crecv + slot * cfg.c_stride +
+                                static_cast<uint64_t>(i) * Elem8<Y>::kBytes,
+                            acc);
+          }
         }
       }
       team.sync();
     }
   }
+  trace_mark(cfg, ws, kTraceCSendLoopDone);
 
   __syncthreads();
   if (threadIdx.x < cfg.world) {
     fence_acq_rel_sys();
     red_release_sys_add(flag_ptr(st.sync[threadIdx.x], 1, st.rank), 1u);
   }
-  finish_phase(cfg, ws, kPhaseCombineSend, iter);
+  trace_mark(cfg, ws, kTraceCSendSignalled);
 }
 
 // ---------------------------------------------------------------------------
 // combine_recv
 // ---------------------------------------------------------------------------
 
+// Source slots (and weights) of token t, compacted into shared memory by the first warp
+// of the team.
+__device__ __forceinline__ void combine_sources(const A2AConfig& cfg, const CombineRecvArgs& a,
+                                                int t, uint32_t* out_slot, uint32_t* out_wbits,
+                                                uint32_t* out_n) {
+  const int K = cfg.topk;
+  const int L = cfg.experts_per_rank;
+  const int k = threadIdx.x & 31;
+  bool valid = false;
+  uint32_t slot = 0, wb = 0;
+  if (k < K) {
+    const uint32_t e = a.indices[t * a.indices_stride + k];
+    if (e < static_cast<uint32_t>(cfg.num_experts)) {
+      if (cfg.combine_mode == kCombinePerRoute) {
+        valid = true;
+        slot = static_cast<uint32_t>(t) * K + k;
+        wb = __float_as_uint(a.weights[t * a.weights_stride + k]);
+      } else {
+        // one partial per distinct destination rank; weights were applied remotely
+        const uint32_t d = e / L;
+        bool first = true;
+        for (int q = 0; q < k; ++q) {
+          const uint32_t eq = a.indices[t * a.indices_stride + q];
+          first &= !(eq < static_cast<uint32_t>(cfg.num_experts) && eq / L == d);
+        }
+        valid = first;
+        slot = static_cast<uint32_t>(t) * cfg.world + d;
+        wb = __float_as_uint(1.0f);
+      }
+    }
+  }
+  compact_warp(valid, slot, wb, out_slot, out_wbits, out_n);
+}
+
 template <int TEAM, typename Y, typename O>
 __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
                                    const CombineRecvArgs& a) {
   const A2ALocal& ws = st.local;
   const Team<TEAM> team;
-  const int K = cfg.topk;
-  const int L = cfg.experts_per_rank;
-  const uint32_t iter = read_iter(ws, kPhaseCombineRecv);
-  const uint32_t expected = (iter + 1) * gridDim.x;
+  const uint32_t epoch = read_epoch(ws, 1);
+  const uint32_t expected = (epoch + 1) * gridDim.x;
+  trace_mark(cfg, ws, kTraceCRecvStart);
 
   __shared__ uint32_t s_abort;
   __shared__ uint32_t s_slot[kMaxTeams][kMaxTopK];
   __shared__ uint32_t s_wbits[kMaxTeams][kMaxTopK];
   __shared__ uint32_t s_n[kMaxTeams];
+
+  int T = a.num_tokens;
+  if (a.bound_m != nullptr) T = min(T, *a.bound_m);
+  T = max(0, min(T, cfg.max_num_tokens));
+
   if (threadIdx.x == 0) s_abort = ws.status[0] != 0 ? 1u : 0u;
   __syncthreads();
+  // The routing of the first token is local input: read it while the flags are polled.
+  const int t_first = team.id;
+  if (team.lane < 32 && t_first < T) {
+    combine_sources(cfg, a, t_first, s_slot[team.in_block], s_wbits[team.in_block],
+                    &s_n[team.in_block]);
+  }
   if (threadIdx.x < cfg.world) {
     uint64_t waited;
     const bool ok = wait_flag(flag_ptr(st.sync[st.rank], 1, threadIdx.x), expected,
@@ -810,44 +876,19 @@ __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
     if (blockIdx.x == 0) atomicMax(&ws.stats[3], static_cast<unsigned long long>(waited));
   }
   __syncthreads();
-
-  int T = a.num_tokens;
-  if (a.bound_m != nullptr) T = min(T, *a.bound_m);
-  T = max(0, min(T, cfg.max_num_tokens));
+  trace_mark(cfg, ws, kTraceCRecvWaitDone);
 
   if (s_abort == 0) {
     const uint8_t* crecv = st.recv[st.rank] + cfg.off_crecv;
     const uint32_t ngran = cfg.hidden_dim / 8;
-    for (int t = team.id; t < T; t += team.count) {
-      if (team.lane < 32) {
-        const int k = team.lane;
-        bool valid = false;
-        uint32_t slot = 0, wb = 0;
-        if (k < K) {
-          const uint32_t e = a.indices[t * a.indices_stride + k];
-          if (e < static_cast<uint32_t>(cfg.num_experts)) {
-            if (cfg.combine_mode == kCombinePerRoute) {
-              valid = true;
-              slot = static_cast<uint32_t>(t) * K + k;
-              wb = __float_as_uint(a.weights[t * a.weights_stride + k]);
-            } else {
-              // one partial per distinct destination rank; weights were applied remotely
-              const uint32_t d = e / L;
-              bool first = true;
-              for (int q = 0; q < k; ++q) {
-                const uint32_t eq = a.indices[t * a.indices_stride + q];
-                first &= !(eq < static_cast<uint32_t>(cfg.num_experts) && eq / L == d);
-              }
-              valid = first;
-              slot = static_cast<uint32_t>(t) * cfg.world + d;
-              wb = __float_as_uint(1.0f);
-            }
-          }
+    for (int t = t_first; t < T; t += team.count) {
+      if (t != t_first) {
+        if (team.lane < 32) {
+          combine_sources(cfg, a, t, s_slot[team.in_block], s_wbits[team.in_block],
+                          &s_n[team.in_block]);
         }
-        compact_warp(valid, slot, wb, s_slot[team.in_block], s_wbits[team.in_block],
-                     &s_n[team.in_block]);
+        team.sync();
       }
-      team.sync();
       const uint32_t n = s_n[team.in_block];
       uint8_t* out_row = a.out_tokens + static_cast<uint64_t>(t) * a.out_tokens_stride * sizeof(O);
       for (uint32_t i = team.lane; i < ngran; i += TEAM) {
@@ -863,7 +904,8 @@ __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
       team.sync();
     }
   }
-  finish_phase(cfg, ws, kPhaseCombineRecv, iter);
+  trace_mark(cfg, ws, kTraceCRecvLoopDone);
+  finish_recv(cfg, ws, 1, epoch, kTraceCRecvAllDone);
 }
 
 // ---------------------------------------------------------------------------
@@ -909,7 +951,7 @@ combine_kernel(const __grid_constant__ A2AConfig cfg, const __grid_constant__ A2
 }
 
 size_t dispatch_smem_bytes(const A2AConfig& cfg) {
-  const size_t send = (cfg.num_experts + kMaxRanks) * sizeof(uint32_t);
+  const size_t send = cfg.num_experts * sizeof(uint32_t);
   const size_t gl = static_cast<size_t>(cfg.num_groups) * cfg.experts_per_rank;
   const size_t recv = (2 * gl + 2 * cfg.experts_per_rank + 32) * sizeof(uint32_t);
   return send > recv ? send : recv;
@@ -954,12 +996,25 @@ cudaError_t launch(Kern kern, dim3 grid, size_t smem, cudaStream_t stream, bool 
 
 }  // namespace
 
-int a2a_pick_team(const A2AConfig& cfg, int64_t work_items) {
-  // Largest team that still gives every work item its own team in the first wave.
+int a2a_pick_team(const A2AConfig& cfg, int64_t work_items, int64_t vectors_per_item) {
+  // A team handles its items one after the other and each item in batches of
+  // TEAM x kCopyUnroll vectors; both are latency-bound round trips. Pick the team size
+  // with the fewest sequential round trips (ties go to the wider team).
   const int64_t warps = static_cast<int64_t>(cfg.num_blocks) * (kA2AThreads / 32);
-  int team_warps = 16;
-  while (team_warps > 1 && warps / team_warps < work_items) team_warps >>= 2;
-  return team_warps * 32;
+  int best_team = 512;
+  int64_t best_cost = INT64_MAX;
+  for (int team : {512, 128, 32}) {
+    const int64_t teams = warps / (team / 32);
+    const int64_t rounds = (work_items + teams - 1) / teams;
+    const int64_t per_batch = static_cast<int64_t>(team) * kCopyUnroll;
+    const int64_t batches = (vectors_per_item + per_batch - 1) / per_batch;
+    const int64_t cost = rounds * batches;
+    if (cost < best_cost) {
+      best_cost = cost;
+      best_team = team;
+    }
+  }
+  return best_team;
 }
 
 cudaError_t a2a_launch_dispatch(const A2AConfig& cfg, const A2ARankStates& states, int nranks,

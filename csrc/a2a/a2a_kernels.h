@@ -9,8 +9,9 @@
 
 namespace pplx {
 
-// Threads that cooperate on one token/record (32, 128 or 512) for `work_items` items.
-int a2a_pick_team(const A2AConfig& cfg, int64_t work_items);
+// Threads that cooperate on one token/record (32, 128 or 512) when `work_items` items of
+// `vectors_per_item` 16-byte vectors each are spread over the grid.
+int a2a_pick_team(const A2AConfig& cfg, int64_t work_items, int64_t vectors_per_item);
 
 // `nranks` > 1 plays that many virtual ranks in one launch on the current device.
 cudaError_t a2a_launch_dispatch(const A2AConfig& cfg, const A2ARankStates& states, int nranks,

@@ -12,8 +12,11 @@
 // the experts of that rank on arrival:
 //
 //   [ header | payload (hidden * in_elemsize, 16-byte padded) | scales ]
-//   header words: [0] token index at the source, [1..K] expert ids, [1+K..2K]
+//   header words: [0] epoch tag (dispatch number + 1), [1..K] expert ids, [1+K..2K]
 //   fp32 routing weights; padded to 16 bytes.
+// The record of source token t always lives in slot t of its source's region, so the
+// sender needs no slot allocation; the tag tells the receiver which slots were written
+// by the current dispatch (regions are zero-filled once, tags start at 1).
 //
 // The reference sends one copy per route and keeps a 16-byte reserved trailer
 // instead (p2p-all-to-all/a2a-kernels/src/a2a/a2a_dispatch_send.cu:586-588,
@@ -32,13 +35,23 @@ constexpr int kA2AThreads = 512;
 constexpr uint32_t kNoSlot = 0xffffffffu;
 constexpr int kFlagStrideWords = 32;  // 128 bytes per flag
 
-// Indices into the per-context launch counters.
 enum A2APhase : int {
   kPhaseDispatchSend = 0,
   kPhaseDispatchRecv = 1,
   kPhaseCombineSend = 2,
   kPhaseCombineRecv = 3,
   kNumPhases = 4,
+};
+
+// Slots of the optional timeline (globaltimer ns, written by block 0 / the last block).
+enum A2ATrace : int {
+  kTraceSendStart = 0, kTraceSendLoopDone = 1, kTraceSendSignalled = 2,
+  kTraceRecvStart = 3, kTraceRecvWaitDone = 4, kTraceRecvLayoutDone = 5,
+  kTraceRecvLoopDone = 6, kTraceRecvAllDone = 7,
+  kTraceCSendStart = 8, kTraceCSendLoopDone = 9, kTraceCSendSignalled = 10,
+  kTraceCRecvStart = 11, kTraceCRecvWaitDone = 12, kTraceCRecvLoopDone = 13,
+  kTraceCRecvAllDone = 14,
+  kTraceSlots = 16,
 };
 
 // Values of status[0]. status[1] = phase, status[2] = peer/group, status[3] = detail.
@@ -71,6 +84,7 @@ struct A2AConfig {
   int expert_padding;
   int combine_mode;
   int num_blocks;        // grid.x of every a2a kernel (arrival counters depend on it)
+  int trace;             // 1: kernels record a coarse timeline into A2ALocal::trace
 
   // wire format
   uint32_t d_header_bytes;
@@ -95,10 +109,10 @@ struct A2AConfig {
 
 // Device-local (not peer visible) workspace of one rank.
 struct A2ALocal {
-  uint32_t* iters;         // [kNumPhases] completed launches per phase
-  uint32_t* done;          // [kNumPhases] blocks that finished the current launch
-  uint32_t* send_cursor;   // [2][kMaxRanks] next record slot per destination
-  uint32_t* place_cursor;  // [2][num_groups * experts_per_rank]
+  uint32_t* epochs;        // [0] completed dispatches, [1] completed combines; advanced by
+                           // the last block of the respective *recv* phase
+  uint32_t* done;          // [2] blocks that finished the current recv phase
+  uint32_t* place_cursor;  // [2][num_groups * experts_per_rank], indexed by epoch parity
   uint32_t* row_src;       // [max_recv_rows] source dp group of a row, kNoSlot = padding
   uint32_t* row_tk;        // [max_recv_rows] token * topk + k at the source
   uint32_t* expert_meta;   // [0] padded row count, [1] record count,
@@ -109,7 +123,8 @@ struct A2ALocal {
   uint32_t* status;        // [4]
   uint32_t* host_flag;     // pinned host word (device-mapped): failure code, readable by the
                            // host without synchronising the stream
-  unsigned long long* stats;  // [8] counters: records sent, rows placed, max wait ns...
+  unsigned long long* stats;  // [8] counters: tokens sent, -, max dispatch/combine wait ns
+  unsigned long long* trace;  // [kTraceSlots] see A2ATrace
 };
 
 struct A2ARankState {

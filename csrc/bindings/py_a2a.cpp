@@ -416,6 +416,8 @@ void bind_a2a(py::module_& m) {
       .def("stats", [](const PyA2A& s, int i) { return s.ctx->stats(i); }, py::arg("local_rank") = 0)
       .def("iterations", [](const PyA2A& s, int i) { return s.ctx->iterations(i); },
            py::arg("local_rank") = 0)
+      .def("trace", [](const PyA2A& s, int i) { return s.ctx->trace(i); }, py::arg("local_rank") = 0)
+      .def("_set_next_phase", [](PyA2A& s, int phase) { s.ctx->debug_set_next_phase(phase); })
       .def("set_team", [](PyA2A& s, int team) { s.ctx->set_team_override(team); })
       .def("destroy", [](PyA2A& s) { s.ctx.reset(); });
 }

@@ -2,5 +2,4 @@
 #include <pybind11/pybind11.h>
 namespace py = pybind11;
 void bind_fabric(py::module_&) {}
-void bind_unigram(py::module_&) {}
 void bind_ops(py::module_&) {}

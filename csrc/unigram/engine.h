@@ -1,0 +1,114 @@
+// Unigram (SentencePiece-style) tokenizer encoder for HuggingFace tokenizer.json files.
+//
+// Pipeline: precompiled-charsmap normalisation (with space-run collapse) -> special token
+// split -> per text segment: Metaspace -> Viterbi over the vocabulary trie, with one-code-
+// point UNK fallback (score = min vocab score - 10) and fusion of adjacent UNKs.
+// Same behaviour as the reference's pplx-unigram (pplx-unigram/src/engine.rs:46-165,
+// special_tokens.rs:28-127, metaspace.rs:41-59, config.rs:8-127); its public surface
+// (`Engine`, `EncodeState`, `Segment`, `Error`: pplx-unigram/src/lib.rs:10-35) maps to
+// the classes below. An immutable Engine can be shared by any number of threads, each
+// with its own EncodeState; encode_batch() does that with a pool of worker threads.
+#pragma once
+
+#include <cstdint>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <string_view>
+#include <vector>
+
+#include "precompiled.h"
+#include "trie.h"
+
+namespace pplx::unigram {
+
+using TokenId = uint32_t;
+
+enum class ErrorKind { kIo, kInvalidConfig, kUnsupportedConfig, kEncodeFailed };
+
+class UnigramError : public std::runtime_error {
+ public:
+  UnigramError(ErrorKind kind, const std::string& what) : std::runtime_error(what), kind_(kind) {}
+  ErrorKind kind() const { return kind_; }
+
+ private:
+  ErrorKind kind_;
+};
+
+struct Segment {
+  size_t start = 0;
+  size_t end = 0;
+  bool special = false;
+  TokenId special_id = 0;
+};
+
+struct SpecialToken {
+  TokenId id = 0;
+  std::string content;
+  bool single_word = false;
+  bool lstrip = false;
+  bool rstrip = false;
+};
+
+// Scratch buffers of one encoding thread; grow to the longest input seen and are reused.
+struct EncodeState {
+  std::vector<TokenId> tokens;  // result of the last encode()
+  std::string normalized;
+  std::string prep;
+  std::vector<Segment> segments;
+  std::vector<double> best_score;
+  std::vector<uint32_t> best_start;
+  std::vector<TokenId> best_id;
+  std::vector<TokenId> backtrack;
+};
+
+class SpecialTokenMatcher {
+ public:
+  SpecialTokenMatcher() = default;
+  explicit SpecialTokenMatcher(std::vector<SpecialToken> tokens);
+  // Splits `text` into text and special segments (earliest match first; on a tie the
+  // longest content wins).
+  void split(std::string_view text, std::vector<Segment>* out) const;
+  bool empty() const { return tokens_.empty(); }
+
+ private:
+  std::vector<SpecialToken> tokens_;
+};
+
+class Engine {
+ public:
+  static std::shared_ptr<Engine> from_hf_json_path(const std::string& path);
+  static std::shared_ptr<Engine> from_hf_json_bytes(std::string_view bytes);
+
+  size_t vocab_size() const { return vocab_size_; }
+  TokenId unk_id() const { return unk_id_; }
+  bool trie_on_huge_pages() const { return trie_.huge_pages(); }
+  size_t trie_nodes() const { return trie_.size(); }
+
+  // Encodes valid UTF-8 `text`; the ids are left in state->tokens.
+  void encode(std::string_view text, EncodeState* state) const;
+
+  // Encodes many texts with `num_threads` threads (0: hardware concurrency).
+  std::vector<std::vector<TokenId>> encode_batch(const std::vector<std::string_view>& texts,
+                                                 int num_threads) const;
+
+  // Exposed for tests.
+  void normalize(std::string_view text, std::string* out) const { normalizer_.normalize_into(text, out); }
+  const SpecialTokenMatcher& special_matcher() const { return special_; }
+
+ private:
+  Engine() = default;
+  void encode_segment(std::string_view text, EncodeState* state) const;
+  void viterbi(const uint8_t* prep, size_t n, EncodeState* state) const;
+
+  PrecompiledNormalizer normalizer_;
+  SpecialTokenMatcher special_;
+  VocabTrie trie_;
+  std::string replacement_;  // UTF-8 of the metaspace replacement character
+  bool add_prefix_space_ = true;
+  TokenId unk_id_ = 0;
+  double unk_score_ = 0.0;
+  size_t vocab_size_ = 0;
+};
+
+}  // namespace pplx::unigram

@@ -77,7 +77,8 @@ class LocalAllToAllGroup:
         # 128-byte alignment the kernels ask of the symmetric regions.
         self._sync = [torch.zeros(self.layout["sync_bytes"], dtype=torch.uint8, device=device)
                       for _ in range(world_size)]
-        self._recv = [torch.empty(self.layout["recv_bytes"], dtype=torch.uint8, device=device)
+        # record headers carry an epoch tag: the receive regions must start zeroed
+        self._recv = [torch.zeros(self.layout["recv_bytes"], dtype=torch.uint8, device=device)
                       for _ in range(world_size)]
         torch.cuda.synchronize(device)
         sync_ptrs = [t.data_ptr() for t in self._sync]

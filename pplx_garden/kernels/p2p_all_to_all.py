@@ -146,6 +146,8 @@ class P2PAllToAll(AllToAllKernel):
         sync_mapping = self._sync_handle.map(device)
         recv_mapping = self._recv_handle.map(device)
         sync_mapping.to_tensor((sync_mapping.size,), torch.uint8).zero_()
+        # record headers carry an epoch tag: the receive regions must start zeroed
+        recv_mapping.to_tensor((recv_mapping.size,), torch.uint8).zero_()
         torch.cuda.synchronize(device)
 
         self._mappings: list[_PeerMappings] = []
