@@ -270,7 +270,7 @@ def main() -> None:
         def line_up() -> None:
             # cold L2 without a cache full of dirty lines: write 256 MiB, then read it back
             flush.zero_()
-            torch.sum(flush_words, out=flush_sum)
+            torch.sum(flush_words, dim=0, out=flush_sum)
             if world > 1:
                 dist.all_reduce(dummy)
 

@@ -278,9 +278,10 @@ void A2AContext::dispatch(const DispatchSendArgs* send, const DispatchRecvArgs* 
   }
   PPLX_CUDA_CHECK(cudaSetDevice(device_));
   // send: one item per token; recv: one item per (source group, token) slot
-  const int64_t items = do_recv ? last_tokens_ * cfg_.num_groups : last_tokens_;
-  PPLX_CUDA_CHECK(a2a_launch_dispatch(cfg_, states_, n, s, r, do_send, do_recv,
-                                      pick(items, cfg_.d_payload_bytes / 16), stream));
+  const int64_t vectors = cfg_.d_payload_bytes / 16;
+  const int send_team = do_send ? pick(last_tokens_, vectors) : 0;
+  const int recv_team = do_recv ? pick(last_tokens_ * cfg_.num_groups, vectors) : 0;
+  PPLX_CUDA_CHECK(a2a_launch_dispatch(cfg_, states_, n, s, r, send_team, recv_team, stream));
 }
 
 void A2AContext::combine(const CombineSendArgs* send, const CombineRecvArgs* recv, bool do_send,
@@ -312,20 +313,17 @@ void A2AContext::combine(const CombineSendArgs* send, const CombineRecvArgs* rec
                "combine: expert_y element size differs from the context's out dtype");
   PPLX_CUDA_CHECK(cudaSetDevice(device_));
   // send: one item per expert row (per-route) or per received record (pre-reduce);
-  // recv: one item per token whose reduction reads several records per output vector.
-  int64_t items, vectors;
+  // recv: one item per token, whose reduction reads up to eight records per output vector.
+  int send_team = 0, recv_team = 0;
   if (do_send) {
     const int64_t per_token = cfg_.combine_mode == kCombinePreReduce
                                   ? std::min<int64_t>(cfg_.topk, cfg_.world)
                                   : cfg_.topk;
-    items = tokens * cfg_.num_groups * per_token / cfg_.world + 1;
-    vectors = cfg_.c_stride / 16;
-  } else {
-    items = tokens;
-    vectors = static_cast<int64_t>(cfg_.hidden_dim / 8) * 8;
+    send_team = pick(tokens * cfg_.num_groups * per_token / cfg_.world + 1, cfg_.c_stride / 16);
   }
-  PPLX_CUDA_CHECK(a2a_launch_combine(cfg_, states_, n, s, r, do_send, do_recv, y_dtype, out_dtype,
-                                     pick(items, vectors), stream));
+  if (do_recv) recv_team = pick(tokens, static_cast<int64_t>(cfg_.hidden_dim / 8) * 8);
+  PPLX_CUDA_CHECK(a2a_launch_combine(cfg_, states_, n, s, r, send_team, recv_team, y_dtype,
+                                     out_dtype, stream));
 }
 
 A2AStatusInfo A2AContext::status(int i) const {

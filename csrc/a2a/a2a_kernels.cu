@@ -44,26 +44,26 @@ constexpr int kMaxTeams = kA2AThreads / 32;
 // = 64 KiB per SM, about what it takes to cover HBM / NVLink latency at full rate.
 constexpr int kCopyUnroll = 8;
 
-template <int TEAM>
+// A team is a power-of-two group of 32..512 consecutive threads of a block that works on
+// one token / record / row at a time. Its size is a launch parameter, chosen per phase.
 struct Team {
+  int size;
   int id;         // global team index inside this virtual rank
   int count;      // teams inside this virtual rank
   int in_block;   // team index inside the block
   int lane;       // thread index inside the team
-  __device__ __forceinline__ Team() {
-    in_block = threadIdx.x / TEAM;
-    lane = threadIdx.x % TEAM;
+  __device__ __forceinline__ explicit Team(int team_size) : size(team_size) {
+    in_block = threadIdx.x / size;
+    lane = threadIdx.x % size;
     // consecutive work items land on different SMs
     id = in_block * gridDim.x + blockIdx.x;
-    count = gridDim.x * (kA2AThreads / TEAM);
+    count = gridDim.x * (kA2AThreads / size);
   }
   __device__ __forceinline__ void sync() const {
-    if constexpr (TEAM == 32) {
+    if (size == 32) {
       __syncwarp();
-    } else if constexpr (TEAM == kA2AThreads) {
-      __syncthreads();
     } else {
-      bar_sync(1 + in_block, TEAM);
+      bar_sync(1 + in_block, size);
     }
   }
 };
@@ -182,11 +182,10 @@ __device__ __forceinline__ Vec16 quantize16(const Vec16& a, const Vec16& b, floa
   return out;
 }
 
-template <int TEAM>
 __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st,
-                                    const DispatchSendArgs& a, uint32_t* dyn_smem) {
+                                    const DispatchSendArgs& a, uint32_t* dyn_smem, const int TEAM) {
   const A2ALocal& ws = st.local;
-  const Team<TEAM> team;
+  const Team team(TEAM);
   const int world = cfg.world;
   const int K = cfg.topk;
   const int L = cfg.experts_per_rank;
@@ -269,19 +268,39 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
                    : nullptr;
     }
 
-    // header
-    for (int wi = team.lane; wi < 1 + 2 * K; wi += TEAM) {
-      uint32_t word;
-      if (wi == 0) {
-        word = tag;
-      } else if (wi <= K) {
-        word = s_idx[team.in_block][wi - 1];
-      } else {
-        word = __float_as_uint(s_w[team.in_block][wi - 1 - K]);
-      }
-      #pragma unroll
-      for (int d = 0; d < kMaxRanks; ++d) {
-        if (rec[d] != nullptr) st_stream_u32(rec[d] + 4 * wi, word);
+    // header (and, when the caller supplies them, the scales) as 16-byte stores: small
+    // stores cost a full NVLink packet each
+    {
+      const int hdr_vecs = cfg.d_header_bytes / 16;
+      const int scale_vecs = (!a.quantize && hs > 0) ? cfg.d_scale_bytes / 16 : 0;
+      const float* xs = reinterpret_cast<const float*>(a.x_scale);
+      for (int vi = team.lane; vi < hdr_vecs + scale_vecs; vi += TEAM) {
+        uint32_t word[4];
+        uint32_t at;
+        if (vi < hdr_vecs) {
+          #pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int wi = 4 * vi + c;
+            if (wi == 0) word[c] = tag;
+            else if (wi <= K) word[c] = s_idx[team.in_block][wi - 1];
+            else if (wi <= 2 * K) word[c] = __float_as_uint(s_w[team.in_block][wi - 1 - K]);
+            else word[c] = 0;
+          }
+          at = 16u * vi;
+        } else {
+          const int sv = vi - hdr_vecs;
+          #pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int j = 4 * sv + c;
+            word[c] = j < hs ? __float_as_uint(xs[t * a.x_scale_stride_token + j * a.x_scale_stride_elem]) : 0u;
+          }
+          at = cfg.d_header_bytes + cfg.d_payload_bytes + 16u * sv;
+        }
+        const Vec16 q = {word[0], word[1], word[2], word[3]};
+        #pragma unroll
+        for (int d = 0; d < kMaxRanks; ++d) {
+          if (rec[d] != nullptr) st_stream_v4(rec[d] + at, q);
+        }
       }
     }
 
@@ -301,20 +320,6 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
             #pragma unroll
             for (int d = 0; d < kMaxRanks; ++d) {
               if (rec[d] != nullptr) st_stream_v4(rec[d] + cfg.d_header_bytes + 16ull * i, v[u]);
-            }
-          }
-        }
-      }
-      // scales travel packed as fp32 right after the payload
-      if (hs > 0) {
-        const float* xs = reinterpret_cast<const float*>(a.x_scale);
-        for (int j = team.lane; j < hs; j += TEAM) {
-          const float s = xs[t * a.x_scale_stride_token + j * a.x_scale_stride_elem];
-          #pragma unroll
-          for (int d = 0; d < kMaxRanks; ++d) {
-            if (rec[d] != nullptr) {
-              st_stream_u32(rec[d] + cfg.d_header_bytes + cfg.d_payload_bytes + 4 * j,
-                            __float_as_uint(s));
             }
           }
         }
@@ -381,11 +386,10 @@ __device__ __forceinline__ void compact_warp(bool valid, uint32_t va, uint32_t v
   if (lane == 0) *out_n = __popc(mask);
 }
 
-template <int TEAM>
 __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
-                                    const DispatchRecvArgs& a, uint32_t* dyn_smem) {
+                                    const DispatchRecvArgs& a, uint32_t* dyn_smem, const int TEAM) {
   const A2ALocal& ws = st.local;
-  const Team<TEAM> team;
+  const Team team(TEAM);
   const int G = cfg.num_groups;
   const int K = cfg.topk;
   const int L = cfg.experts_per_rank;
@@ -443,6 +447,8 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
     __syncthreads();
     // Warp 0 owns the layout: lane j covers a contiguous chunk of experts, sums the groups,
     // scans the padded totals across lanes and writes every (group, expert) base row.
+    // (With many experts per rank the per-lane chunks get long, but that is the
+    // small-world case where nothing else is latency critical.)
     if (threadIdx.x < 32) {
       const int per = (L + 31) / 32;
       const int lo = threadIdx.x * per;
@@ -505,7 +511,7 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
     constexpr int U = kCopyUnroll;
     // Wide teams have few slots each: fetch the payload together with the header
     // instead of after it (a slot that turns out to be stale costs one wasted read).
-    constexpr bool kSpeculate = TEAM >= 128;
+    const bool kSpeculate = TEAM >= 128;
     for (uint32_t s = team.id; s < total_slots; s += team.count) {
       int g = 0;
       #pragma unroll
@@ -697,11 +703,11 @@ __device__ __forceinline__ void weighted_gather8(float (&acc)[8], const uint8_t*
 
 // Per-route mode: plain byte copy of each valid expert row to every member of the
 // origin dp group. Pre-reduce mode: weighted partial sum per received record.
-template <int TEAM, typename Y>
+template <typename Y>
 __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
-                                   const CombineSendArgs& a) {
+                                   const CombineSendArgs& a, const int TEAM) {
   const A2ALocal& ws = st.local;
-  const Team<TEAM> team;
+  const Team team(TEAM);
   const int K = cfg.topk;
   trace_mark(cfg, ws, kTraceCSendStart);
 
@@ -776,15 +782,42 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
       const uint32_t n = s_n[team.in_block];
       if (n != 0) {
         const uint64_t slot = static_cast<uint64_t>(t) * cfg.world + st.rank;
-        for (uint32_t i = team.lane; i < ngran; i += TEAM) {
-          float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-          weighted_gather8<Y>(acc, a.expert_y, a.expert_y_stride, s_rows[team.in_block],
-                              s_wbits[team.in_block], n,
-                              static_cast<uint64_t>(i) * Elem8<Y>::kBytes, false);
-          for (int m = 0; m < cfg.dp_size; ++m) {
-            Elem8<Y>::store(st.recv[g * cfg.dp_size + m] + cfg.off_crecv + slot * cfg.c_stride +
-                                static_cast<uint64_t>(i) * Elem8<Y>::kBytes,
-                            acc);
+        constexpr int GB = 4;  // granules a thread carries at once: GB independent loads per row
+        for (uint32_t i0 = team.lane; i0 < ngran; i0 += TEAM * GB) {
+          float acc[GB][8];
+          #pragma unroll
+          for (int u = 0; u < GB; ++u) {
+            #pragma unroll
+            for (int q = 0; q < 8; ++q) acc[u][q] = 0.f;
+          }
+          for (uint32_t j = 0; j < n; ++j) {
+            const uint8_t* row = a.expert_y + static_cast<uint64_t>(s_rows[team.in_block][j]) * a.expert_y_stride;
+            const float w = __uint_as_float(s_wbits[team.in_block][j]);
+            float f[GB][8];
+            #pragma unroll
+            for (int u = 0; u < GB; ++u) {
+              const uint32_t i = i0 + u * TEAM;
+              if (i < ngran) Elem8<Y>::load(row + static_cast<uint64_t>(i) * Elem8<Y>::kBytes, f[u], false);
+            }
+            #pragma unroll
+            for (int u = 0; u < GB; ++u) {
+              const uint32_t i = i0 + u * TEAM;
+              if (i < ngran) {
+                #pragma unroll
+                for (int q = 0; q < 8; ++q) acc[u][q] = fmaf(w, f[u][q], acc[u][q]);
+              }
+            }
+          }
+          #pragma unroll
+          for (int u = 0; u < GB; ++u) {
+            const uint32_t i = i0 + u * TEAM;
+            if (i < ngran) {
+              for (int m = 0; m < cfg.dp_size; ++m) {
+                Elem8<Y>::store(st.recv[g * cfg.dp_size + m] + cfg.off_crecv + slot * cfg.c_stride +
+                                    static_cast<uint64_t>(i) * Elem8<Y>::kBytes,
+                                acc[u]);
+              }
+            }
           }
         }
       }
@@ -839,11 +872,11 @@ __device__ __forceinline__ void combine_sources(const A2AConfig& cfg, const Comb
   compact_warp(valid, slot, wb, out_slot, out_wbits, out_n);
 }
 
-template <int TEAM, typename Y, typename O>
+template <typename Y, typename O>
 __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
-                                   const CombineRecvArgs& a) {
+                                   const CombineRecvArgs& a, const int TEAM) {
   const A2ALocal& ws = st.local;
-  const Team<TEAM> team;
+  const Team team(TEAM);
   const uint32_t epoch = read_epoch(ws, 1);
   const uint32_t expected = (epoch + 1) * gridDim.x;
   trace_mark(cfg, ws, kTraceCRecvStart);
@@ -912,42 +945,43 @@ __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
 // kernels
 // ---------------------------------------------------------------------------
 
-template <int TEAM>
 __global__ void __launch_bounds__(kA2AThreads, 1)
 dispatch_kernel(const __grid_constant__ A2AConfig cfg, const __grid_constant__ A2ARankStates states,
                 const __grid_constant__ PerRank<DispatchSendArgs> send,
-                const __grid_constant__ PerRank<DispatchRecvArgs> recv, int do_send, int do_recv) {
+                const __grid_constant__ PerRank<DispatchRecvArgs> recv, int send_team,
+                int recv_team) {
   extern __shared__ __align__(16) uint32_t dyn_smem[];
   const A2ARankState& st = states.r[blockIdx.y];
-  if (do_send) dispatch_send_phase<TEAM>(cfg, st, send.r[blockIdx.y], dyn_smem);
-  if (do_send && do_recv) __syncthreads();
-  if (do_recv) dispatch_recv_phase<TEAM>(cfg, st, recv.r[blockIdx.y], dyn_smem);
+  if (send_team) dispatch_send_phase(cfg, st, send.r[blockIdx.y], dyn_smem, send_team);
+  if (send_team && recv_team) __syncthreads();
+  if (recv_team) dispatch_recv_phase(cfg, st, recv.r[blockIdx.y], dyn_smem, recv_team);
 }
 
-template <int TEAM, typename Y>
+template <typename Y>
 __global__ void __launch_bounds__(kA2AThreads, 1)
 combine_send_kernel(const __grid_constant__ A2AConfig cfg,
                     const __grid_constant__ A2ARankStates states,
-                    const __grid_constant__ PerRank<CombineSendArgs> send) {
-  combine_send_phase<TEAM, Y>(cfg, states.r[blockIdx.y], send.r[blockIdx.y]);
+                    const __grid_constant__ PerRank<CombineSendArgs> send, int send_team) {
+  combine_send_phase<Y>(cfg, states.r[blockIdx.y], send.r[blockIdx.y], send_team);
 }
 
-template <int TEAM, typename Y, typename O>
+template <typename Y, typename O>
 __global__ void __launch_bounds__(kA2AThreads, 1)
 combine_recv_kernel(const __grid_constant__ A2AConfig cfg,
                     const __grid_constant__ A2ARankStates states,
-                    const __grid_constant__ PerRank<CombineRecvArgs> recv) {
-  combine_recv_phase<TEAM, Y, O>(cfg, states.r[blockIdx.y], recv.r[blockIdx.y]);
+                    const __grid_constant__ PerRank<CombineRecvArgs> recv, int recv_team) {
+  combine_recv_phase<Y, O>(cfg, states.r[blockIdx.y], recv.r[blockIdx.y], recv_team);
 }
 
-template <int TEAM, typename Y, typename O>
+template <typename Y, typename O>
 __global__ void __launch_bounds__(kA2AThreads, 1)
 combine_kernel(const __grid_constant__ A2AConfig cfg, const __grid_constant__ A2ARankStates states,
                const __grid_constant__ PerRank<CombineSendArgs> send,
-               const __grid_constant__ PerRank<CombineRecvArgs> recv) {
-  combine_send_phase<TEAM, Y>(cfg, states.r[blockIdx.y], send.r[blockIdx.y]);
+               const __grid_constant__ PerRank<CombineRecvArgs> recv, int send_team,
+               int recv_team) {
+  combine_send_phase<Y>(cfg, states.r[blockIdx.y], send.r[blockIdx.y], send_team);
   __syncthreads();
-  combine_recv_phase<TEAM, Y, O>(cfg, states.r[blockIdx.y], recv.r[blockIdx.y]);
+  combine_recv_phase<Y, O>(cfg, states.r[blockIdx.y], recv.r[blockIdx.y], recv_team);
 }
 
 size_t dispatch_smem_bytes(const A2AConfig& cfg) {
@@ -955,16 +989,6 @@ size_t dispatch_smem_bytes(const A2AConfig& cfg) {
   const size_t gl = static_cast<size_t>(cfg.num_groups) * cfg.experts_per_rank;
   const size_t recv = (2 * gl + 2 * cfg.experts_per_rank + 32) * sizeof(uint32_t);
   return send > recv ? send : recv;
-}
-
-template <typename F>
-cudaError_t with_team(int team, F&& f) {
-  switch (team) {
-    case 32: return f(std::integral_constant<int, 32>{});
-    case 128: return f(std::integral_constant<int, 128>{});
-    case 512: return f(std::integral_constant<int, 512>{});
-    default: return cudaErrorInvalidValue;
-  }
 }
 
 template <typename F>
@@ -1019,40 +1043,34 @@ int a2a_pick_team(const A2AConfig& cfg, int64_t work_items, int64_t vectors_per_
 
 cudaError_t a2a_launch_dispatch(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
                                 const PerRank<DispatchSendArgs>& send,
-                                const PerRank<DispatchRecvArgs>& recv, bool do_send, bool do_recv,
-                                int team, cudaStream_t stream) {
+                                const PerRank<DispatchRecvArgs>& recv, int send_team, int recv_team,
+                                cudaStream_t stream) {
   const dim3 grid(cfg.num_blocks, nranks);
   const size_t smem = dispatch_smem_bytes(cfg);
   // One launch that plays several ranks contains blocks that wait for one another:
   // co-residency must be guaranteed (or the launch refused) by the driver.
-  const bool cooperative = nranks > 1 && do_send && do_recv;
-  return with_team(team, [&](auto t) {
-    constexpr int TEAM = decltype(t)::value;
-    return launch(dispatch_kernel<TEAM>, grid, smem, stream, cooperative, cfg, states, send, recv,
-                  static_cast<int>(do_send), static_cast<int>(do_recv));
-  });
+  const bool cooperative = nranks > 1 && send_team && recv_team;
+  return launch(dispatch_kernel, grid, smem, stream, cooperative, cfg, states, send, recv,
+                send_team, recv_team);
 }
 
 cudaError_t a2a_launch_combine(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
                                const PerRank<CombineSendArgs>& send,
-                               const PerRank<CombineRecvArgs>& recv, bool do_send, bool do_recv,
-                               int y_dtype, int out_dtype, int team, cudaStream_t stream) {
+                               const PerRank<CombineRecvArgs>& recv, int send_team, int recv_team,
+                               int y_dtype, int out_dtype, cudaStream_t stream) {
   const dim3 grid(cfg.num_blocks, nranks);
-  return with_team(team, [&](auto t) {
-    constexpr int TEAM = decltype(t)::value;
-    return with_dtype(y_dtype, [&](auto* yp) {
-      using Y = std::remove_pointer_t<decltype(yp)>;
-      if (do_send && !do_recv) {
-        return launch(combine_send_kernel<TEAM, Y>, grid, 0, stream, false, cfg, states, send);
+  return with_dtype(y_dtype, [&](auto* yp) {
+    using Y = std::remove_pointer_t<decltype(yp)>;
+    if (send_team && !recv_team) {
+      return launch(combine_send_kernel<Y>, grid, 0, stream, false, cfg, states, send, send_team);
+    }
+    return with_dtype(out_dtype, [&](auto* op) {
+      using O = std::remove_pointer_t<decltype(op)>;
+      if (send_team) {
+        return launch(combine_kernel<Y, O>, grid, 0, stream, nranks > 1, cfg, states, send, recv,
+                      send_team, recv_team);
       }
-      return with_dtype(out_dtype, [&](auto* op) {
-        using O = std::remove_pointer_t<decltype(op)>;
-        if (do_send) {
-          return launch(combine_kernel<TEAM, Y, O>, grid, 0, stream, nranks > 1, cfg, states, send,
-                        recv);
-        }
-        return launch(combine_recv_kernel<TEAM, Y, O>, grid, 0, stream, false, cfg, states, recv);
-      });
+      return launch(combine_recv_kernel<Y, O>, grid, 0, stream, false, cfg, states, recv, recv_team);
     });
   });
 }

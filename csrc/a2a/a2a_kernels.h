@@ -14,14 +14,15 @@ namespace pplx {
 int a2a_pick_team(const A2AConfig& cfg, int64_t work_items, int64_t vectors_per_item);
 
 // `nranks` > 1 plays that many virtual ranks in one launch on the current device.
+// A team size of 0 skips that phase; otherwise it is 32, 128 or 512.
 cudaError_t a2a_launch_dispatch(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
                                 const PerRank<DispatchSendArgs>& send,
-                                const PerRank<DispatchRecvArgs>& recv, bool do_send, bool do_recv,
-                                int team, cudaStream_t stream);
+                                const PerRank<DispatchRecvArgs>& recv, int send_team, int recv_team,
+                                cudaStream_t stream);
 
 cudaError_t a2a_launch_combine(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
                                const PerRank<CombineSendArgs>& send,
-                               const PerRank<CombineRecvArgs>& recv, bool do_send, bool do_recv,
-                               int y_dtype, int out_dtype, int team, cudaStream_t stream);
+                               const PerRank<CombineRecvArgs>& recv, int send_team, int recv_team,
+                               int y_dtype, int out_dtype, cudaStream_t stream);
 
 }  // namespace pplx

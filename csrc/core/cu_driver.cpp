@@ -52,6 +52,7 @@ Loaded& loaded() {
     bind(t.cuMemSetAccess, "cuMemSetAccess", true);
     bind(t.cuMemExportToShareableHandle, "cuMemExportToShareableHandle", true);
     bind(t.cuMemImportFromShareableHandle, "cuMemImportFromShareableHandle", true);
+    bind(t.cuMemGetAddressRange, "cuMemGetAddressRange_v2", true);
     bind(t.cuMemGetHandleForAddressRange, "cuMemGetHandleForAddressRange", false);
     bind(t.cuMulticastCreate, "cuMulticastCreate", false);
     bind(t.cuMulticastAddDevice, "cuMulticastAddDevice", false);

@@ -34,6 +34,7 @@ struct CuDriver {
                                            CUmemAllocationHandleType, unsigned long long);
   CUresult (*cuMemImportFromShareableHandle)(CUmemGenericAllocationHandle*, void*,
                                              CUmemAllocationHandleType);
+  CUresult (*cuMemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr);
   CUresult (*cuMemGetHandleForAddressRange)(void*, CUdeviceptr, size_t,
                                             CUmemRangeHandleType, unsigned long long);
   CUresult (*cuMulticastCreate)(CUmemGenericAllocationHandle*, const CUmulticastObjectProp*);

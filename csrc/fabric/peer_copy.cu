@@ -1,0 +1,139 @@
+#include "peer_copy.h"
+
+#include <algorithm>
+
+#include "../a2a/ptx.cuh"
+
+namespace pplx::fabric {
+namespace {
+
+constexpr uint32_t kChunkBytes = 32 * 1024;  // one bulk copy
+constexpr int kStages = 4;                   // chunks in flight per CTA (128 KiB of smem)
+constexpr int kBulkThreads = 32;
+
+__device__ __forceinline__ uint64_t page_offset(const uint32_t* pages, uint32_t i, uint64_t stride,
+                                                uint64_t offset) {
+  const uint64_t idx = pages != nullptr ? pages[i] : i;
+  return idx * stride + offset;
+}
+
+// One elected thread per CTA drives a ring of shared-memory stages:
+//   global --cp.async.bulk--> smem stage --cp.async.bulk--> (peer) global
+// Loads complete on an mbarrier per stage, stores in bulk groups; a stage is reused once
+// the store that read it has finished reading. SMs only issue descriptors.
+__global__ void __launch_bounds__(kBulkThreads)
+paged_copy_bulk_kernel(const __grid_constant__ PagedCopyArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ uint64_t bars[kStages];
+  if (threadIdx.x != 0) return;
+
+  for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+
+  const uint32_t chunks_per_page = static_cast<uint32_t>((a.length + kChunkBytes - 1) / kChunkBytes);
+  const uint64_t total = static_cast<uint64_t>(a.num_pages) * chunks_per_page;
+  uint32_t phase[kStages] = {0, 0, 0, 0};
+  uint64_t issued = 0;
+  bool failed = false;
+
+  // Software pipeline: keep up to kStages loads in flight, store each as it lands.
+  auto item_of = [&](uint64_t n) { return blockIdx.x + n * gridDim.x; };
+  auto load = [&](uint64_t n) {
+    const uint64_t item = item_of(n);
+    const uint32_t page = static_cast<uint32_t>(item / chunks_per_page);
+    const uint64_t within = (item % chunks_per_page) * kChunkBytes;
+    const uint32_t bytes = static_cast<uint32_t>(min(static_cast<uint64_t>(kChunkBytes), a.length - within));
+    const int s = static_cast<int>(n % kStages);
+    mbar_expect_tx(&bars[s], bytes);
+    bulk_g2s(smem + s * kChunkBytes, a.src_base + page_offset(a.src_pages, page, a.src_stride, a.src_offset) + within,
+             bytes, &bars[s]);
+  };
+  uint64_t mine = 0;
+  if (total > blockIdx.x) mine = (total - blockIdx.x + gridDim.x - 1) / gridDim.x;
+
+  for (; issued < mine && issued < kStages; ++issued) load(issued);
+  for (uint64_t n = 0; n < mine; ++n) {
+    const int s = static_cast<int>(n % kStages);
+    if (!mbar_wait_bounded(&bars[s], phase[s])) {
+      failed = true;
+      break;
+    }
+    phase[s] ^= 1u;
+    const uint64_t item = item_of(n);
+    const uint32_t page = static_cast<uint32_t>(item / chunks_per_page);
+    const uint64_t within = (item % chunks_per_page) * kChunkBytes;
+    const uint32_t bytes = static_cast<uint32_t>(min(static_cast<uint64_t>(kChunkBytes), a.length - within));
+    fence_proxy_async_smem();
+    bulk_s2g(a.dst_base + page_offset(a.dst_pages, page, a.dst_stride, a.dst_offset) + within,
+             smem + s * kChunkBytes, bytes);
+    bulk_commit();
+    // All but the newest store have finished reading their stage: the stage of store
+    // n - 1 is free for the next load, while store n still overlaps with it.
+    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    if (n >= 1 && issued < mine) {
+      load(issued);  // issued == n - 1 + kStages: lands in stage (n - 1) % kStages
+      ++issued;
+    }
+  }
+  // Stores must be complete (not merely read) before the kernel, and with it the stream
+  // event the host polls, finishes.
+  bulk_wait0();
+  if (failed) {
+    atomicExch(a.error_flag, 1u);
+    // loads that are still in flight land in this CTA's shared memory: wait for them
+    // (bounded) before the CTA may exit
+    for (uint64_t n = 0; n < issued; ++n) {
+      const int s = static_cast<int>(n % kStages);
+      (void)mbar_wait_bounded(&bars[s], phase[s], 1u << 16);
+    }
+  }
+}
+
+// Fallback for arbitrary alignment: 16-byte vectors where both sides allow it, bytes else.
+__global__ void __launch_bounds__(256) paged_copy_simt_kernel(const __grid_constant__ PagedCopyArgs a) {
+  const uint32_t chunks_per_page = static_cast<uint32_t>((a.length + kChunkBytes - 1) / kChunkBytes);
+  const uint64_t total = static_cast<uint64_t>(a.num_pages) * chunks_per_page;
+  for (uint64_t item = blockIdx.x; item < total; item += gridDim.x) {
+    const uint32_t page = static_cast<uint32_t>(item / chunks_per_page);
+    const uint64_t within = (item % chunks_per_page) * kChunkBytes;
+    const uint64_t bytes = min(static_cast<uint64_t>(kChunkBytes), a.length - within);
+    const uint8_t* src = a.src_base + page_offset(a.src_pages, page, a.src_stride, a.src_offset) + within;
+    uint8_t* dst = a.dst_base + page_offset(a.dst_pages, page, a.dst_stride, a.dst_offset) + within;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15u) == 0;
+    if (aligned) {
+      const uint64_t nvec = bytes / 16;
+      for (uint64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+        st_stream_v4(dst + 16 * i, ld_input_v4(src + 16 * i));
+      }
+      for (uint64_t i = nvec * 16 + threadIdx.x; i < bytes; i += blockDim.x) dst[i] = src[i];
+    } else {
+      for (uint64_t i = threadIdx.x; i < bytes; i += blockDim.x) dst[i] = src[i];
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_paged_copy(const PagedCopyArgs& args, int max_ctas, cudaStream_t stream) {
+  if (args.num_pages == 0 || args.length == 0) return cudaSuccess;
+  const uint64_t chunks_per_page = (args.length + kChunkBytes - 1) / kChunkBytes;
+  const uint64_t total = args.num_pages * chunks_per_page;
+  if (max_ctas <= 0) max_ctas = 64;
+  const int grid = static_cast<int>(std::min<uint64_t>(total, static_cast<uint64_t>(max_ctas)));
+  const uint64_t all = reinterpret_cast<uintptr_t>(args.src_base) | reinterpret_cast<uintptr_t>(args.dst_base) |
+                       args.src_stride | args.dst_stride | args.src_offset | args.dst_offset | args.length;
+  if ((all & 15u) == 0) {
+    const size_t smem = static_cast<size_t>(kStages) * kChunkBytes;
+    // per device and cheap: set it on every launch rather than tracking devices
+    cudaError_t e = cudaFuncSetAttribute(paged_copy_bulk_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    paged_copy_bulk_kernel<<<grid, kBulkThreads, smem, stream>>>(args);
+  } else {
+    paged_copy_simt_kernel<<<grid, 256, 0, stream>>>(args);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace pplx::fabric
