@@ -7,6 +7,7 @@
 #include "../core/error.h"
 #include "../core/log.h"
 #include "../core/thread_util.h"
+#include "py_util.h"
 
 namespace py = pybind11;
 
@@ -68,6 +69,13 @@ PYBIND11_MODULE(_native, m) {
     else if (level == "debug") l = pplx::LogLevel::kDebug;
     if (pplx::log_enabled(l)) pplx::log_message(l, target.c_str(), "%s", msg.c_str());
   });
+
+  m.def("_tensor_from_ptr",
+        [](uint64_t ptr, uint64_t nbytes, int device) {
+          return pplx_py::device_bytes_tensor(ptr, nbytes, device, py::none());
+        },
+        py::arg("ptr"), py::arg("nbytes"), py::arg("device"),
+        "uint8 tensor over raw memory the caller keeps alive (device >= 0: CUDA, -1: host).");
 
   bind_cumem(m);
   bind_a2a(m);

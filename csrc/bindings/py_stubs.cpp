@@ -1,5 +1,4 @@
 // Placeholders until the corresponding components are linked in.
 #include <pybind11/pybind11.h>
 namespace py = pybind11;
-void bind_fabric(py::module_&) {}
 void bind_ops(py::module_&) {}

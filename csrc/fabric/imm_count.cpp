@@ -48,14 +48,14 @@ ImmIncResult ImmCountMap::inc(uint32_t imm, uint32_t n) {
   Entry& e = it->second;
   switch (e.kind) {
     case Entry::Kind::kExpected: {
+      // Consumes exactly `expected` arrivals: the one that completes the count reports
+      // kReached, every later one is surplus and is treated as if no counter existed.
       const int64_t prev = e.counter->fetch_add(n, std::memory_order_acq_rel);
-      const int64_t now = prev + n;
-      // "reached" exactly once: when the count crosses the expected value
-      if (prev < e.expected && now >= e.expected) {
-        e.counter->fetch_sub(e.expected, std::memory_order_acq_rel);
-        return ImmIncResult::kReached;
+      if (prev >= e.expected) {
+        e.counter->fetch_sub(n, std::memory_order_acq_rel);
+        return ImmIncResult::kVacant;
       }
-      return ImmIncResult::kNotReached;
+      return prev + n >= e.expected ? ImmIncResult::kReached : ImmIncResult::kNotReached;
     }
     case Entry::Kind::kFree:
       e.counter->fetch_add(n, std::memory_order_acq_rel);

@@ -1,7 +1,8 @@
 // Arrival counters keyed by the 32-bit immediate value of one-sided writes.
 //
 // Three flavours, as in the reference's fabric-lib/src/imm_count.rs:15-144:
-//   Expected  fire once the count reaches an expected value, then start over at zero;
+//   Expected  fire once when the count reaches an expected value; later arrivals are surplus
+//             and are reported as if no counter were installed, until it is set again;
 //   Free      count forever, the user waits on the counter (ImmCounter::wait);
 //   Flag      count upwards from a negative "debt"; when the debt is paid (value 0) raise a
 //             flag in mapped memory that a GPU kernel polls (the reference raises a GDRCopy
