@@ -1,0 +1,48 @@
+// Bindings of the expert-side compute ops (no counterpart in the reference, which ships no
+// expert computation at all).
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include "../core/error.h"
+#include "../ops/grouped_gemm.h"
+
+namespace py = pybind11;
+using namespace pplx;
+using namespace pplx::ops;
+
+void bind_ops(py::module_& m) {
+  m.def(
+      "grouped_fp8_gemm",
+      [](uint64_t a, int64_t a_stride, uint64_t a_scale, int64_t a_scale_stride_row, int64_t a_scale_stride_k,
+         uint64_t b, uint64_t b_scale, uint64_t expert_num_tokens, uint64_t out, int64_t out_stride,
+         uint64_t out_scale, int64_t out_scale_stride_row, uint64_t error_flag, int num_experts, int N, int K,
+         int expert_padding, int max_rows, int mode, int num_ctas, uint64_t stream) {
+        GroupedGemmParams p;
+        p.a = reinterpret_cast<const void*>(a);
+        p.a_stride = a_stride;
+        p.a_scale = reinterpret_cast<const float*>(a_scale);
+        p.a_scale_stride_row = a_scale_stride_row;
+        p.a_scale_stride_k = a_scale_stride_k;
+        p.b = reinterpret_cast<const void*>(b);
+        p.b_scale = reinterpret_cast<const float*>(b_scale);
+        p.expert_num_tokens = reinterpret_cast<const int32_t*>(expert_num_tokens);
+        p.out = reinterpret_cast<void*>(out);
+        p.out_stride = out_stride;
+        p.out_scale = reinterpret_cast<float*>(out_scale);
+        p.out_scale_stride_row = out_scale_stride_row;
+        p.error_flag = reinterpret_cast<uint32_t*>(error_flag);
+        p.num_experts = num_experts;
+        p.N = N;
+        p.K = K;
+        p.expert_padding = expert_padding;
+        p.max_rows = max_rows;
+        p.mode = mode;
+        p.num_ctas = num_ctas;
+        grouped_fp8_gemm(p, reinterpret_cast<cudaStream_t>(stream));
+      },
+      py::arg("a"), py::arg("a_stride"), py::arg("a_scale"), py::arg("a_scale_stride_row"),
+      py::arg("a_scale_stride_k"), py::arg("b"), py::arg("b_scale"), py::arg("expert_num_tokens"), py::arg("out"),
+      py::arg("out_stride"), py::arg("out_scale"), py::arg("out_scale_stride_row"), py::arg("error_flag"),
+      py::arg("num_experts"), py::arg("N"), py::arg("K"), py::arg("expert_padding"), py::arg("max_rows"),
+      py::arg("mode"), py::arg("num_ctas"), py::arg("stream"));
+}

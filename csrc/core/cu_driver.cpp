@@ -54,6 +54,7 @@ Loaded& loaded() {
     bind(t.cuMemImportFromShareableHandle, "cuMemImportFromShareableHandle", true);
     bind(t.cuMemGetAddressRange, "cuMemGetAddressRange_v2", true);
     bind(t.cuMemGetHandleForAddressRange, "cuMemGetHandleForAddressRange", false);
+    bind(t.cuTensorMapEncodeTiled, "cuTensorMapEncodeTiled", false);
     bind(t.cuMulticastCreate, "cuMulticastCreate", false);
     bind(t.cuMulticastAddDevice, "cuMulticastAddDevice", false);
     bind(t.cuMulticastBindMem, "cuMulticastBindMem", false);

@@ -37,6 +37,10 @@ struct CuDriver {
   CUresult (*cuMemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr);
   CUresult (*cuMemGetHandleForAddressRange)(void*, CUdeviceptr, size_t,
                                             CUmemRangeHandleType, unsigned long long);
+  CUresult (*cuTensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                     CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                     CUtensorMapFloatOOBfill);
   CUresult (*cuMulticastCreate)(CUmemGenericAllocationHandle*, const CUmulticastObjectProp*);
   CUresult (*cuMulticastAddDevice)(CUmemGenericAllocationHandle, CUdevice);
   CUresult (*cuMulticastBindMem)(CUmemGenericAllocationHandle, size_t,

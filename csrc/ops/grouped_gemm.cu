@@ -1,0 +1,392 @@
+// Grouped (per-expert) block-scaled fp8 GEMM on the Blackwell tensor cores.
+//
+//   for every local expert e with rows [row_start(e), row_start(e) + count(e)):
+//     D = dequant(A rows) x dequant(B[e])^T
+//   A  e4m3 [rows, K]      one fp32 scale per row and 128 columns (1x128)
+//   B  e4m3 [E, N, K]      one fp32 scale per 128x128 block
+//
+// Two epilogues:
+//   kSwiGLUQuant  B = [gate; up] stacked along N (N = 2 I): out = silu(gate) * up, re-quantised
+//                 to e4m3 with 1x128 scales -> the input of the down projection
+//   kBf16         out = D as bf16 -> the rows handed to combine
+//
+// Structure (one persistent CTA per SM, 10 warps):
+//   warp 0      TMA producer: 128x128-byte A tile + four 64-row B boxes per K block into a
+//               4-stage shared-memory ring (SWIZZLE_128B), completion on mbarriers
+//   warp 1      one thread issues tcgen05.mma (M 128, N 256, K 32 x 4 per K block) into one of
+//               two 256-column TMEM accumulators and commits to mbarriers
+//   warps 2-9   epilogue: tcgen05.ld the K block's partial sums, scale them by
+//               a_scale[row, kb] * b_scale[nb, kb] and add into fp32 registers (the per-block
+//               scales differ along K, so the running sum cannot stay in TMEM), then apply the
+//               epilogue and store
+// The two TMEM accumulators let the tensor cores work on K block i+1 while block i is being
+// folded. No TMA multicast, no clusters: every CTA loads its own tiles.
+//
+// The reference has no GEMM of any kind (its "expert" is x * 2 in tests and benchmarks:
+// tests/p2p_all_to_all/test_p2p_all_to_all.py:44-50); this kernel is the expert-side half of
+// the fused MoE layer built on top of dispatch / combine.
+
+#include "grouped_gemm.h"
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include <algorithm>
+
+#include "../core/cu_driver.h"
+#include "../core/error.h"
+#include "tcgen05.cuh"
+
+namespace pplx::ops {
+namespace {
+
+using namespace pplx::tc;
+
+constexpr int kBM = 128, kBN = 256, kBK = 128;
+constexpr int kStages = 4;
+constexpr int kThreads = 320;
+constexpr int kEpilogueThreads = 256;
+constexpr uint32_t kABytes = kBM * kBK;        // 16 KiB
+constexpr uint32_t kBBoxBytes = 64 * kBK;      // 8 KiB, four boxes per stage
+constexpr uint32_t kStageBytes = kABytes + 4 * kBBoxBytes;  // 48 KiB
+constexpr uint32_t kTmemCols = 512;
+constexpr int kMaxExperts = 64;
+constexpr uint32_t kWaitPolls = 1u << 22;
+
+struct KernelArgs {
+  alignas(64) CUtensorMap map_a;
+  alignas(64) CUtensorMap map_b;
+  const float* a_scale;
+  int64_t a_scale_stride_row;
+  int64_t a_scale_stride_k;
+  const float* b_scale;            // [E][N/128][K/128]
+  const int32_t* expert_num_tokens;
+  uint8_t* out;
+  int64_t out_stride;              // bytes per output row
+  float* out_scale;
+  int64_t out_scale_stride_row;    // elements
+  uint32_t* error_flag;
+  int num_experts;
+  int N, K;
+  int expert_padding;
+  int max_rows;
+  int mode;
+};
+
+struct Schedule {
+  int row_start[kMaxExperts];
+  int count[kMaxExperts];
+  int tile_prefix[kMaxExperts + 1];
+};
+
+__device__ __forceinline__ void decode_tile(const Schedule& s, int num_experts, int n_tiles, int t, int* e,
+                                            int* m_tile, int* n_tile) {
+  int lo = 0;
+  while (lo + 1 < num_experts && t >= s.tile_prefix[lo + 1]) ++lo;
+  const int local = t - s.tile_prefix[lo];
+  *e = lo;
+  *m_tile = local / n_tiles;
+  *n_tile = local % n_tiles;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __grid_constant__ KernelArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ uint64_t full_bar[kStages], empty_bar[kStages], tmem_full_bar[2], tmem_empty_bar[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ Schedule sched;
+  __shared__ float s_amax[2][kBM][2];
+  __shared__ uint32_t s_failed;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const bool swiglu = a.mode == kSwiGLUQuant;
+  const int I = a.N / 2;
+  const int n_tiles = swiglu ? I / 128 : a.N / kBN;
+  const int nkb = a.K / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full_bar[b], 1);
+      mbar_init(&tmem_empty_bar[b], kEpilogueThreads / 32);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    s_failed = 0;
+    // expert-major row layout (each expert's block starts at a multiple of the padding)
+    int row = 0, tiles = 0;
+    for (int e = 0; e < a.num_experts; ++e) {
+      const int n = max(a.expert_num_tokens[e], 0);
+      sched.row_start[e] = row;
+      sched.count[e] = n;
+      sched.tile_prefix[e] = tiles;
+      tiles += (n + kBM - 1) / kBM * n_tiles;
+      row += (n + a.expert_padding - 1) / a.expert_padding * a.expert_padding;
+    }
+    sched.tile_prefix[a.num_experts] = tiles;
+    prefetch_tensormap(&a.map_a);
+    prefetch_tensormap(&a.map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&tmem_base_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  fence_before_thread_sync();
+  __syncthreads();
+  fence_after_thread_sync();
+  const uint32_t tmem_base = tmem_base_slot;
+  const int total_tiles = sched.tile_prefix[a.num_experts];
+  // operand tiles need the 1024-byte alignment of the 128-byte swizzle atom
+  uint8_t* const tiles = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total_tiles && !s_failed; t += gridDim.x) {
+        int e, m_tile, n_tile;
+        decode_tile(sched, a.num_experts, n_tiles, t, &e, &m_tile, &n_tile);
+        const int row0 = sched.row_start[e] + m_tile * kBM;
+        int brow[4];
+        if (swiglu) {
+          brow[0] = e * a.N + n_tile * 128;
+          brow[1] = e * a.N + I + n_tile * 128;
+          brow[2] = brow[0] + 64;
+          brow[3] = brow[1] + 64;
+        } else {
+          for (int i = 0; i < 4; ++i) brow[i] = e * a.N + n_tile * kBN + 64 * i;
+        }
+        for (int kb = 0; kb < nkb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
+          if (!mbar_wait_bounded(&empty_bar[s], parity, kWaitPolls)) {
+            s_failed = 1;
+            atomicExch(a.error_flag, 1u);
+            break;
+          }
+          uint8_t* stage = tiles + static_cast<size_t>(s) * kStageBytes;
+          mbar_expect_tx(&full_bar[s], kStageBytes);
+          tma_load_2d(stage, &a.map_a, kb * kBK, row0, &full_bar[s]);
+          #pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            tma_load_2d(stage + kABytes + i * kBBoxBytes, &a.map_b, kb * kBK, brow[i], &full_bar[s]);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_e4m3_f32(kBM, kBN);
+      uint32_t it = 0, acc_it = 0;
+      for (int t = blockIdx.x; t < total_tiles && !s_failed; t += gridDim.x) {
+        for (int kb = 0; kb < nkb; ++kb, ++it, ++acc_it) {
+          const int s = it % kStages;
+          const int buf = acc_it & 1;
+          if (!mbar_wait_bounded(&tmem_empty_bar[buf], ((acc_it >> 1) & 1u) ^ 1u, kWaitPolls) ||
+              !mbar_wait_bounded(&full_bar[s], (it / kStages) & 1u, kWaitPolls)) {
+            s_failed = 1;
+            atomicExch(a.error_flag, 2u);
+            break;
+          }
+          fence_after_thread_sync();
+          const uint8_t* stage = tiles + static_cast<size_t>(s) * kStageBytes;
+          const uint64_t a_desc = smem_desc_k_sw128(stage);
+          const uint64_t b_desc = smem_desc_k_sw128(stage + kABytes);
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf) * kBN;
+          #pragma unroll
+          for (int k4 = 0; k4 < kBK / 32; ++k4) {
+            // advancing 32 bytes along K inside the 128-byte swizzled row: +2 in 16-byte units
+            mma_f8f6f4(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+          }
+          mma_commit(&empty_bar[s]);          // the stage may be refilled once these MMAs are done
+          mma_commit(&tmem_full_bar[buf]);    // ... and the partial sums may be read
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;                      // TMEM lane quarter this warp may read
+    const int h = (warp - 2) >> 2;               // column half: 0 -> cols [0,128), 1 -> [128,256)
+    const int row_in_tile = q * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+    uint32_t acc_it = 0;
+    uint32_t tile_parity = 0;
+    const int nkb_scale = a.K / 128;
+    const int nb_per_expert = a.N / 128;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, tile_parity ^= 1u) {
+      int e, m_tile, n_tile;
+      decode_tile(sched, a.num_experts, n_tiles, t, &e, &m_tile, &n_tile);
+      const int row = sched.row_start[e] + m_tile * kBM + row_in_tile;
+      const bool valid = m_tile * kBM + row_in_tile < sched.count[e] && row < a.max_rows;
+      const float* a_scale_row = a.a_scale + static_cast<int64_t>(valid ? row : 0) * a.a_scale_stride_row;
+      // block rows of B this thread's columns fall into
+      int nb0, nb1;
+      if (swiglu) {
+        nb0 = n_tile;                 // gate columns
+        nb1 = I / 128 + n_tile;       // up columns
+      } else {
+        nb0 = nb1 = n_tile * 2 + h;
+      }
+      const float* bs0 = a.b_scale + (static_cast<int64_t>(e) * nb_per_expert + nb0) * nkb_scale;
+      const float* bs1 = a.b_scale + (static_cast<int64_t>(e) * nb_per_expert + nb1) * nkb_scale;
+
+      float acc[128];
+      #pragma unroll
+      for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+      float as_next = a_scale_row[0];
+      float b0_next = bs0[0], b1_next = bs1[0];
+      bool failed = false;
+      for (int kb = 0; kb < nkb; ++kb, ++acc_it) {
+        const int buf = acc_it & 1;
+        const float as = as_next, b0 = b0_next, b1 = b1_next;
+        if (kb + 1 < nkb) {
+          as_next = a_scale_row[(kb + 1) * a.a_scale_stride_k];
+          b0_next = bs0[kb + 1];
+          b1_next = bs1[kb + 1];
+        }
+        if (!mbar_wait_bounded(&tmem_full_bar[buf], (acc_it >> 1) & 1u, kWaitPolls)) {
+          failed = true;
+          break;
+        }
+        fence_after_thread_sync();
+        const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(buf) * kBN + static_cast<uint32_t>(h) * 128;
+        #pragma unroll
+        for (int c8 = 0; c8 < 8; ++c8) {
+          uint32_t tmp[16];
+          tmem_ld16(taddr + c8 * 16, tmp);
+          tmem_ld_wait();
+          // swiglu: thread columns [0,64) are gate, [64,128) up; plain: one block row for all
+          const float sc = as * ((swiglu ? c8 < 4 : true) ? b0 : b1);
+          #pragma unroll
+          for (int i = 0; i < 16; ++i) acc[c8 * 16 + i] = fmaf(sc, __uint_as_float(tmp[i]), acc[c8 * 16 + i]);
+        }
+        fence_before_thread_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+      }
+      if (failed) {
+        atomicExch(a.error_flag, 3u);
+        s_failed = 1;
+      }
+
+      if (swiglu) {
+        // out[c] = silu(gate[c]) * up[c] for this thread's 64 columns
+        float amax = 0.f;
+        #pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const float g = acc[i];
+          const float v = g / (1.f + __expf(-g)) * acc[64 + i];
+          acc[i] = v;
+          amax = fmaxf(amax, fabsf(v));
+        }
+        s_amax[tile_parity][row_in_tile][h] = amax;
+        bar_sync(1, kEpilogueThreads);   // every epilogue thread gets here, also after a failed wait
+        amax = fmaxf(s_amax[tile_parity][row_in_tile][0], s_amax[tile_parity][row_in_tile][1]);
+        const float scale = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+        const float inv = 1.0f / scale;
+        if (valid && !failed) {
+          uint8_t* dst = a.out + static_cast<int64_t>(row) * a.out_stride + n_tile * 128 + h * 64;
+          #pragma unroll
+          for (int v4 = 0; v4 < 4; ++v4) {
+            uint32_t w[4];
+            #pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int i = v4 * 16 + j * 4;
+              const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(acc[i] * inv, acc[i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+              const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(acc[i + 2] * inv, acc[i + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+              w[j] = lo | (hi << 16);
+            }
+            *reinterpret_cast<uint4*>(dst + 16 * v4) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          if (h == 0) a.out_scale[static_cast<int64_t>(row) * a.out_scale_stride_row + n_tile] = scale;
+        }
+      } else if (valid && !failed) {
+        uint8_t* dst = a.out + static_cast<int64_t>(row) * a.out_stride + (static_cast<int64_t>(n_tile) * kBN + h * 128) * 2;
+        #pragma unroll
+        for (int v8 = 0; v8 < 16; ++v8) {
+          __nv_bfloat162 p[4];
+          #pragma unroll
+          for (int j = 0; j < 4; ++j) p[j] = __floats2bfloat162_rn(acc[v8 * 8 + 2 * j], acc[v8 * 8 + 2 * j + 1]);
+          *reinterpret_cast<uint4*>(dst + 16 * v8) = *reinterpret_cast<uint4*>(p);
+        }
+      }
+      if (failed) break;
+    }
+  }
+
+  fence_before_thread_sync();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after_thread_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+CUtensorMap make_map(const void* base, uint64_t rows, uint64_t cols_bytes, uint64_t row_stride_bytes,
+                     uint32_t box_rows) {
+  const CuDriver& cu = CuDriver::get();
+  PPLX_REQUIRE(cu.cuTensorMapEncodeTiled != nullptr, "this CUDA driver has no cuTensorMapEncodeTiled");
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {cols_bytes, rows};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  PPLX_CU_CHECK(cu.cuTensorMapEncodeTiled(&map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+                                          strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return map;
+}
+
+}  // namespace
+
+void grouped_fp8_gemm(const GroupedGemmParams& p, cudaStream_t stream) {
+  PPLX_REQUIRE(p.K % kBK == 0 && p.K >= kBK, "K must be a multiple of 128");
+  PPLX_REQUIRE(p.num_experts >= 1 && p.num_experts <= kMaxExperts, "between 1 and 64 local experts");
+  PPLX_REQUIRE(p.expert_padding >= 1, "expert_padding must be positive");
+  if (p.mode == kSwiGLUQuant) {
+    PPLX_REQUIRE(p.N % 256 == 0, "SwiGLU needs N = 2 * intermediate with intermediate a multiple of 128");
+    PPLX_REQUIRE(p.out_scale != nullptr, "the SwiGLU epilogue writes scales");
+  } else {
+    PPLX_REQUIRE(p.N % kBN == 0, "N must be a multiple of 256");
+  }
+  PPLX_REQUIRE(reinterpret_cast<uintptr_t>(p.a) % 16 == 0 && reinterpret_cast<uintptr_t>(p.b) % 16 == 0 &&
+                   p.a_stride % 16 == 0 && reinterpret_cast<uintptr_t>(p.out) % 16 == 0 && p.out_stride % 16 == 0,
+               "operands must be 16-byte aligned");
+  KernelArgs a{};
+  a.map_a = make_map(p.a, static_cast<uint64_t>(p.max_rows), static_cast<uint64_t>(p.K),
+                     static_cast<uint64_t>(p.a_stride), kBM);
+  a.map_b = make_map(p.b, static_cast<uint64_t>(p.num_experts) * p.N, static_cast<uint64_t>(p.K),
+                     static_cast<uint64_t>(p.K), 64);
+  a.a_scale = p.a_scale;
+  a.a_scale_stride_row = p.a_scale_stride_row;
+  a.a_scale_stride_k = p.a_scale_stride_k;
+  a.b_scale = p.b_scale;
+  a.expert_num_tokens = p.expert_num_tokens;
+  a.out = static_cast<uint8_t*>(p.out);
+  a.out_stride = p.out_stride;
+  a.out_scale = p.out_scale;
+  a.out_scale_stride_row = p.out_scale_stride_row;
+  a.error_flag = p.error_flag;
+  a.num_experts = p.num_experts;
+  a.N = p.N;
+  a.K = p.K;
+  a.expert_padding = p.expert_padding;
+  a.max_rows = p.max_rows;
+  a.mode = p.mode;
+
+  int device = 0, sms = 0;
+  PPLX_CUDA_CHECK(cudaGetDevice(&device));
+  PPLX_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+  const size_t smem = static_cast<size_t>(kStages) * kStageBytes + 1024;
+  PPLX_CUDA_CHECK(cudaFuncSetAttribute(grouped_fp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem)));
+  const int grid = p.num_ctas > 0 ? p.num_ctas : sms;
+  grouped_fp8_gemm_kernel<<<grid, kThreads, smem, stream>>>(a);
+  PPLX_CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace pplx::ops

@@ -1,0 +1,39 @@
+// Host interface of the grouped block-scaled fp8 GEMM (see grouped_gemm.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace pplx::ops {
+
+enum GroupedGemmMode : int {
+  kSwiGLUQuant = 0,  // B = [gate; up]; out = e4m3(silu(gate) * up) with 1x128 fp32 scales
+  kBf16 = 1,         // out = bf16(A B^T)
+};
+
+struct GroupedGemmParams {
+  const void* a = nullptr;          // e4m3 [max_rows, K], expert-major rows
+  int64_t a_stride = 0;             // bytes per row
+  const float* a_scale = nullptr;   // [max_rows, K / 128]
+  int64_t a_scale_stride_row = 0;   // elements
+  int64_t a_scale_stride_k = 1;
+  const void* b = nullptr;          // e4m3 [num_experts, N, K] contiguous
+  const float* b_scale = nullptr;   // [num_experts, N / 128, K / 128] contiguous
+  const int32_t* expert_num_tokens = nullptr;  // device, [num_experts]
+  void* out = nullptr;
+  int64_t out_stride = 0;           // bytes per row
+  float* out_scale = nullptr;       // kSwiGLUQuant: [max_rows, N / 256]
+  int64_t out_scale_stride_row = 0;
+  uint32_t* error_flag = nullptr;   // device word, set non-zero when a bounded wait ran out
+  int num_experts = 0;
+  int N = 0, K = 0;
+  int expert_padding = 1;           // every expert's rows start at a multiple of this
+  int max_rows = 0;
+  int mode = kBf16;
+  int num_ctas = 0;                 // 0: one per SM
+};
+
+void grouped_fp8_gemm(const GroupedGemmParams& params, cudaStream_t stream);
+
+}  // namespace pplx::ops

@@ -1,0 +1,11 @@
+"""Expert-side compute ops for the fused MoE layer (block-scaled fp8 grouped GEMM)."""
+
+from pplx_garden.ops.grouped_gemm import (
+    MODE_BF16 as MODE_BF16,
+    MODE_SWIGLU_QUANT as MODE_SWIGLU_QUANT,
+    dequantize_1x128 as dequantize_1x128,
+    dequantize_128x128 as dequantize_128x128,
+    grouped_fp8_gemm as grouped_fp8_gemm,
+    quantize_1x128 as quantize_1x128,
+    quantize_128x128 as quantize_128x128,
+)
