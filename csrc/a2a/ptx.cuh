@@ -166,6 +166,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
+// Wait on an mbarrier phase for at most `timeout_ns` of wall time. Returns false when the
+// time ran out (the caller reports the failure and unwinds; it never spins forever).
+__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity, uint64_t timeout_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t start = globaltimer_ns();
+  for (;;) {
+    #pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (globaltimer_ns() - start > timeout_ns) return false;
+  }
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -54,7 +54,7 @@ paged_copy_bulk_kernel(const __grid_constant__ PagedCopyArgs a) {
   for (; issued < mine && issued < kStages; ++issued) load(issued);
   for (uint64_t n = 0; n < mine; ++n) {
     const int s = static_cast<int>(n % kStages);
-    if (!mbar_wait_bounded(&bars[s], phase[s])) {
+    if (!mbar_wait_timed(&bars[s], phase[s], 2000000000ull)) {
       failed = true;
       break;
     }
@@ -84,7 +84,7 @@ paged_copy_bulk_kernel(const __grid_constant__ PagedCopyArgs a) {
     // (bounded) before the CTA may exit
     for (uint64_t n = 0; n < issued; ++n) {
       const int s = static_cast<int>(n % kStages);
-      (void)mbar_wait_bounded(&bars[s], phase[s], 1u << 16);
+      (void)mbar_wait_timed(&bars[s], phase[s], 100000000ull);
     }
   }
 }

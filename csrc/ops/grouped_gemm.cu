@@ -51,7 +51,7 @@ constexpr uint32_t kBBoxBytes = 64 * kBK;      // 8 KiB, four boxes per stage
 constexpr uint32_t kStageBytes = kABytes + 4 * kBBoxBytes;  // 48 KiB
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxExperts = 64;
-constexpr uint32_t kWaitPolls = 1u << 22;
+constexpr uint64_t kWaitNs = 2000000000ull;  // every mbarrier wait gives up after 2 s
 
 struct KernelArgs {
   alignas(64) CUtensorMap map_a;
@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
-          if (!mbar_wait_bounded(&empty_bar[s], parity, kWaitPolls)) {
+          if (!mbar_wait_timed(&empty_bar[s], parity, kWaitNs)) {
             s_failed = 1;
             atomicExch(a.error_flag, 1u);
             break;
@@ -185,8 +185,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
         for (int kb = 0; kb < nkb; ++kb, ++it, ++acc_it) {
           const int s = it % kStages;
           const int buf = acc_it & 1;
-          if (!mbar_wait_bounded(&tmem_empty_bar[buf], ((acc_it >> 1) & 1u) ^ 1u, kWaitPolls) ||
-              !mbar_wait_bounded(&full_bar[s], (it / kStages) & 1u, kWaitPolls)) {
+          if (!mbar_wait_timed(&tmem_empty_bar[buf], ((acc_it >> 1) & 1u) ^ 1u, kWaitNs) ||
+              !mbar_wait_timed(&full_bar[s], (it / kStages) & 1u, kWaitNs)) {
             s_failed = 1;
             atomicExch(a.error_flag, 2u);
             break;
@@ -247,7 +247,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
           b0_next = bs0[kb + 1];
           b1_next = bs1[kb + 1];
         }
-        if (!mbar_wait_bounded(&tmem_full_bar[buf], (acc_it >> 1) & 1u, kWaitPolls)) {
+        // the verdict must be the same for the whole warp: tcgen05.ld below is warp-collective
+        if (!__all_sync(0xffffffffu, mbar_wait_timed(&tmem_full_bar[buf], (acc_it >> 1) & 1u, kWaitNs))) {
           failed = true;
           break;
         }
