@@ -166,17 +166,21 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   return false;
 }
 
-// Wait on an mbarrier phase for at most `timeout_ns` of wall time. Returns false when the
-// time ran out (the caller reports the failure and unwinds; it never spins forever).
+// Wait on an mbarrier phase for at most about `timeout_ns`. Returns false when the time ran
+// out (the caller reports the failure and unwinds; it never spins forever). Time is taken
+// from the SM's cycle counter (reading %globaltimer costs hundreds of cycles and would sit on
+// the critical path of every wait that is not satisfied at once); 2 cycles per ns is an upper
+// bound on the clock, so the real limit is at least `timeout_ns`.
 __device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity, uint64_t timeout_ns) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t start = globaltimer_ns();
+  const long long start = clock64();
+  const long long limit = static_cast<long long>(timeout_ns) * 2;
   for (;;) {
     #pragma unroll 1
     for (int i = 0; i < 32; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
     }
-    if (globaltimer_ns() - start > timeout_ns) return false;
+    if (clock64() - start > limit) return false;
   }
 }
 

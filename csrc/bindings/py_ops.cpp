@@ -16,7 +16,7 @@ void bind_ops(py::module_& m) {
       [](uint64_t a, int64_t a_stride, uint64_t a_scale, int64_t a_scale_stride_row, int64_t a_scale_stride_k,
          uint64_t b, uint64_t b_scale, uint64_t expert_num_tokens, uint64_t out, int64_t out_stride,
          uint64_t out_scale, int64_t out_scale_stride_row, uint64_t error_flag, int num_experts, int N, int K,
-         int expert_padding, int max_rows, int mode, int num_ctas, uint64_t stream) {
+         int expert_padding, int max_rows, int mode, int num_ctas, uint64_t stream, uint64_t wait_cycles) {
         GroupedGemmParams p;
         p.a = reinterpret_cast<const void*>(a);
         p.a_stride = a_stride;
@@ -38,11 +38,12 @@ void bind_ops(py::module_& m) {
         p.max_rows = max_rows;
         p.mode = mode;
         p.num_ctas = num_ctas;
+        p.wait_cycles = reinterpret_cast<unsigned long long*>(wait_cycles);
         grouped_fp8_gemm(p, reinterpret_cast<cudaStream_t>(stream));
       },
       py::arg("a"), py::arg("a_stride"), py::arg("a_scale"), py::arg("a_scale_stride_row"),
       py::arg("a_scale_stride_k"), py::arg("b"), py::arg("b_scale"), py::arg("expert_num_tokens"), py::arg("out"),
       py::arg("out_stride"), py::arg("out_scale"), py::arg("out_scale_stride_row"), py::arg("error_flag"),
       py::arg("num_experts"), py::arg("N"), py::arg("K"), py::arg("expert_padding"), py::arg("max_rows"),
-      py::arg("mode"), py::arg("num_ctas"), py::arg("stream"));
+      py::arg("mode"), py::arg("num_ctas"), py::arg("stream"), py::arg("wait_cycles") = 0);
 }

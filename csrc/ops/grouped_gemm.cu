@@ -10,12 +10,13 @@
 //                 to e4m3 with 1x128 scales -> the input of the down projection
 //   kBf16         out = D as bf16 -> the rows handed to combine
 //
-// Structure (one persistent CTA per SM, 10 warps):
+// Structure (one persistent CTA per SM, three warpgroups):
 //   warp 0      TMA producer: 128x128-byte A tile + four 64-row B boxes per K block into a
 //               4-stage shared-memory ring (SWIZZLE_128B), completion on mbarriers
 //   warp 1      one thread issues tcgen05.mma (M 128, N 256, K 32 x 4 per K block) into one of
 //               two 256-column TMEM accumulators and commits to mbarriers
-//   warps 2-9   epilogue: tcgen05.ld the K block's partial sums, scale them by
+//   (warps 2-3 idle; the first warpgroup gives most of its registers away with setmaxnreg)
+//   warps 4-11  epilogue: tcgen05.ld the K block's partial sums, scale them by
 //               a_scale[row, kb] * b_scale[nb, kb] and add into fp32 registers (the per-block
 //               scales differ along K, so the running sum cannot stay in TMEM), then apply the
 //               epilogue and store
@@ -44,7 +45,8 @@ using namespace pplx::tc;
 
 constexpr int kBM = 128, kBN = 256, kBK = 128;
 constexpr int kStages = 4;
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;
+constexpr int kFirstEpilogueWarp = 4;
 constexpr int kEpilogueThreads = 256;
 constexpr uint32_t kABytes = kBM * kBK;        // 16 KiB
 constexpr uint32_t kBBoxBytes = 64 * kBK;      // 8 KiB, four boxes per stage
@@ -66,6 +68,7 @@ struct KernelArgs {
   float* out_scale;
   int64_t out_scale_stride_row;    // elements
   uint32_t* error_flag;
+  unsigned long long* wait_cycles;  // optional [grid][4]: cycles each role spent waiting
   int num_experts;
   int N, K;
   int expert_padding;
@@ -141,10 +144,15 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
   // operand tiles need the 1024-byte alignment of the 128-byte swizzle atom
   uint8_t* const tiles = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
 
+  if (warp < kFirstEpilogueWarp) {
+    // The first warpgroup only issues copies and MMAs: it keeps 40 registers per thread and
+    // the epilogue warpgroups take the rest of the register file.
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
+      long long waited = 0;
       for (int t = blockIdx.x; t < total_tiles && !s_failed; t += gridDim.x) {
         int e, m_tile, n_tile;
         decode_tile(sched, a.num_experts, n_tiles, t, &e, &m_tile, &n_tile);
@@ -161,7 +169,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
-          if (!mbar_wait_timed(&empty_bar[s], parity, kWaitNs)) {
+          const long long w0 = clock64();
+          const bool got = mbar_wait_timed(&empty_bar[s], parity, kWaitNs);
+          waited += clock64() - w0;
+          if (!got) {
             s_failed = 1;
             atomicExch(a.error_flag, 1u);
             break;
@@ -175,18 +186,25 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
           }
         }
       }
+      if (a.wait_cycles != nullptr) a.wait_cycles[blockIdx.x * 4 + 0] = static_cast<unsigned long long>(waited);
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_e4m3_f32(kBM, kBN);
       uint32_t it = 0, acc_it = 0;
+      long long waited_tmem = 0, waited_full = 0;
       for (int t = blockIdx.x; t < total_tiles && !s_failed; t += gridDim.x) {
         for (int kb = 0; kb < nkb; ++kb, ++it, ++acc_it) {
           const int s = it % kStages;
           const int buf = acc_it & 1;
-          if (!mbar_wait_timed(&tmem_empty_bar[buf], ((acc_it >> 1) & 1u) ^ 1u, kWaitNs) ||
-              !mbar_wait_timed(&full_bar[s], (it / kStages) & 1u, kWaitNs)) {
+          const long long w0 = clock64();
+          const bool got_tmem = mbar_wait_timed(&tmem_empty_bar[buf], ((acc_it >> 1) & 1u) ^ 1u, kWaitNs);
+          const long long w1 = clock64();
+          const bool got_full = got_tmem && mbar_wait_timed(&full_bar[s], (it / kStages) & 1u, kWaitNs);
+          waited_tmem += w1 - w0;
+          waited_full += clock64() - w1;
+          if (!got_tmem || !got_full) {
             s_failed = 1;
             atomicExch(a.error_flag, 2u);
             break;
@@ -205,15 +223,22 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
           mma_commit(&tmem_full_bar[buf]);    // ... and the partial sums may be read
         }
       }
+      if (a.wait_cycles != nullptr) {
+        a.wait_cycles[blockIdx.x * 4 + 1] = static_cast<unsigned long long>(waited_tmem);
+        a.wait_cycles[blockIdx.x * 4 + 2] = static_cast<unsigned long long>(waited_full);
+      }
     }
+  }
   } else {
     // ------------------------------------------------------------------ epilogue warps
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
-    const int h = (warp - 2) >> 2;               // column half: 0 -> cols [0,128), 1 -> [128,256)
+    const int h = (warp - kFirstEpilogueWarp) >> 2;  // column half: 0 -> cols [0,128), 1 -> [128,256)
     const int row_in_tile = q * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     uint32_t acc_it = 0;
     uint32_t tile_parity = 0;
+    long long waited_acc = 0;
     const int nkb_scale = a.K / 128;
     const int nb_per_expert = a.N / 128;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, tile_parity ^= 1u) {
@@ -248,25 +273,37 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
           b1_next = bs1[kb + 1];
         }
         // the verdict must be the same for the whole warp: tcgen05.ld below is warp-collective
-        if (!__all_sync(0xffffffffu, mbar_wait_timed(&tmem_full_bar[buf], (acc_it >> 1) & 1u, kWaitNs))) {
+        const long long w0 = clock64();
+        const bool got = mbar_wait_timed(&tmem_full_bar[buf], (acc_it >> 1) & 1u, kWaitNs);
+        waited_acc += clock64() - w0;
+        if (!__all_sync(0xffffffffu, got)) {
           failed = true;
           break;
         }
         fence_after_thread_sync();
         const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(buf) * kBN + static_cast<uint32_t>(h) * 128;
+        // Two rounds of 64 columns: both 32-column loads of a round are in flight together,
+        // so the TMEM latency is paid twice per K block instead of once per 16 columns.
         #pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-          uint32_t tmp[16];
-          tmem_ld16(taddr + c8 * 16, tmp);
+        for (int r = 0; r < 2; ++r) {
+          uint32_t t0[32], t1[32];
+          tmem_ld32(taddr + r * 64, t0);
+          tmem_ld32(taddr + r * 64 + 32, t1);
           tmem_ld_wait();
+          if (r == 1) {
+            // everything this warp needs from the buffer is in registers: hand it back early
+            fence_before_thread_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+          }
           // swiglu: thread columns [0,64) are gate, [64,128) up; plain: one block row for all
-          const float sc = as * ((swiglu ? c8 < 4 : true) ? b0 : b1);
+          const float sc = as * ((swiglu ? r == 0 : true) ? b0 : b1);
           #pragma unroll
-          for (int i = 0; i < 16; ++i) acc[c8 * 16 + i] = fmaf(sc, __uint_as_float(tmp[i]), acc[c8 * 16 + i]);
+          for (int i = 0; i < 32; ++i) {
+            acc[r * 64 + i] = fmaf(sc, __uint_as_float(t0[i]), acc[r * 64 + i]);
+            acc[r * 64 + 32 + i] = fmaf(sc, __uint_as_float(t1[i]), acc[r * 64 + 32 + i]);
+          }
         }
-        fence_before_thread_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
       }
       if (failed) {
         atomicExch(a.error_flag, 3u);
@@ -315,6 +352,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
         }
       }
       if (failed) break;
+    }
+    if (a.wait_cycles != nullptr && warp == kFirstEpilogueWarp && lane == 0) {
+      a.wait_cycles[blockIdx.x * 4 + 3] = static_cast<unsigned long long>(waited_acc);
     }
   }
 
@@ -372,6 +412,7 @@ void grouped_fp8_gemm(const GroupedGemmParams& p, cudaStream_t stream) {
   a.out_scale = p.out_scale;
   a.out_scale_stride_row = p.out_scale_stride_row;
   a.error_flag = p.error_flag;
+  a.wait_cycles = p.wait_cycles;
   a.num_experts = p.num_experts;
   a.N = p.N;
   a.K = p.K;

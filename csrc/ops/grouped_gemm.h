@@ -26,6 +26,10 @@ struct GroupedGemmParams {
   float* out_scale = nullptr;       // kSwiGLUQuant: [max_rows, N / 256]
   int64_t out_scale_stride_row = 0;
   uint32_t* error_flag = nullptr;   // device word, set non-zero when a bounded wait ran out
+  // Optional device array [num CTAs][4]: cycles spent waiting by the TMA producer (for a free
+  // stage), the MMA issuer (for a free accumulator, for operands) and the first epilogue warp
+  // (for partial sums). Shows which stage of the pipeline is the bottleneck.
+  unsigned long long* wait_cycles = nullptr;
   int num_experts = 0;
   int N = 0, K = 0;
   int expert_padding = 1;           // every expert's rows start at a multiple of this

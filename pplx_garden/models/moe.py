@@ -1,0 +1,109 @@
+"""Expert-parallel MoE feed-forward layer, fused end to end on the GPU:
+
+    route (softmax over the top-k logits) ->
+    dispatch       bf16 tokens are quantised to e4m3 (1x128 scales) inside the kernel that
+                   pushes them to the expert ranks over NVLink
+    gate/up GEMM   grouped block-scaled fp8 GEMM on tcgen05 tensor cores with the SwiGLU and the
+                   re-quantisation to e4m3 fused into its epilogue
+    down GEMM      same kernel, bf16 epilogue
+    combine        expert rows return to their home rank and are reduced with the routing weights
+
+The reference provides only the dispatch and combine steps (with an identity expert in its
+tests: tests/p2p_all_to_all/test_p2p_all_to_all.py:44-50); the expert computation and its
+fusion with the communication are additions of this library.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from pplx_garden.distributed import ParallelGroup
+from pplx_garden.kernels.p2p_all_to_all import P2PAllToAll
+from pplx_garden.ops import MODE_BF16, MODE_SWIGLU_QUANT, grouped_fp8_gemm, quantize_128x128
+from pplx_garden.utils.math import ceil_div
+
+
+def route_topk(logits: torch.Tensor, topk: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Top-k experts by logit and their softmax weights renormalised over the chosen k.
+    Returns (indices uint32 [tokens, k], weights float32 [tokens, k])."""
+    top = torch.topk(logits.float(), topk, dim=-1)
+    weights = torch.softmax(top.values, dim=-1)
+    return top.indices.to(torch.int32).view(torch.uint32), weights
+
+
+class ExpertParallelMoE:
+    """Holds this rank's expert weights (fp8, 128x128 block scales) and the all-to-all context."""
+
+    def __init__(
+        self,
+        *,
+        hidden_dim: int,
+        intermediate_dim: int,
+        num_experts: int,
+        num_experts_per_token: int,
+        max_num_tokens: int,
+        device: torch.device,
+        global_group: Optional[ParallelGroup],
+        w13: Optional[torch.Tensor] = None,   # [local experts, 2 * intermediate, hidden], any float dtype
+        w2: Optional[torch.Tensor] = None,    # [local experts, hidden, intermediate]
+        init_std: float = 0.02,
+        seed: int = 0,
+        combine_mode: str = "per_route",
+    ) -> None:
+        assert hidden_dim % 256 == 0 and intermediate_dim % 128 == 0
+        self.hidden_dim = hidden_dim
+        self.intermediate_dim = intermediate_dim
+        self.topk = num_experts_per_token
+        self.device = torch.device(device)
+        world = global_group.size if global_group is not None else 1
+        rank = global_group.rank if global_group is not None else 0
+        self.num_local_experts = ceil_div(num_experts, world)
+        L = self.num_local_experts
+        if w13 is None or w2 is None:
+            gen = torch.Generator(device="cpu").manual_seed(seed + 1000 * rank)
+            w13 = torch.randn((L, 2 * intermediate_dim, hidden_dim), generator=gen) * init_std
+            w2 = torch.randn((L, hidden_dim, intermediate_dim), generator=gen) * init_std
+        self.w13, self.w13_scale = (t.to(self.device) for t in quantize_128x128(w13))
+        self.w2, self.w2_scale = (t.to(self.device) for t in quantize_128x128(w2))
+        self.a2a = P2PAllToAll(
+            max_num_tokens=max_num_tokens, num_experts=num_experts, expert_padding=1,
+            hidden_dim=hidden_dim, hidden_dim_scale=hidden_dim // 128, in_dtype=torch.float8_e4m3fn,
+            out_dtype=torch.bfloat16, scale_dtype=torch.float32,
+            num_experts_per_token=num_experts_per_token, device=self.device, dp_group=None,
+            node_group=None, global_group=global_group, combine_mode=combine_mode)
+        rows = self.a2a.max_recv_rows
+        dev = self.device
+        self.expert_num_tokens = torch.zeros(L, dtype=torch.int32, device=dev)
+        self.expert_x = torch.zeros((rows, hidden_dim), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+        self.expert_x_scale = torch.zeros((rows, hidden_dim // 128), dtype=torch.float32, device=dev)
+        self.act = torch.zeros((rows, intermediate_dim), dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+        self.act_scale = torch.zeros((rows, intermediate_dim // 128), dtype=torch.float32, device=dev)
+        self.expert_y = torch.zeros((rows, hidden_dim), dtype=torch.bfloat16, device=dev)
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def forward(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x bf16 [tokens, hidden]; indices uint32 and weights fp32 [tokens, k]."""
+        assert x.dtype == torch.bfloat16 and x.shape[1] == self.hidden_dim
+        if out is None:
+            out = torch.empty_like(x)
+        self.a2a.dispatch(self.expert_num_tokens, self.expert_x, self.expert_x_scale, x, None, indices, weights)
+        grouped_fp8_gemm(self.expert_x, self.expert_x_scale, self.w13, self.w13_scale, self.expert_num_tokens,
+                         self.act, self.act_scale, mode=MODE_SWIGLU_QUANT, error_flag=self.error_flag)
+        grouped_fp8_gemm(self.act, self.act_scale, self.w2, self.w2_scale, self.expert_num_tokens,
+                         self.expert_y, mode=MODE_BF16, error_flag=self.error_flag)
+        self.a2a.combine(out, indices, weights, self.expert_y)
+        return out
+
+    __call__ = forward
+
+    def check(self) -> None:
+        """Raise if any kernel of the layer reported a failed wait (synchronises)."""
+        self.a2a.check()
+        if int(self.error_flag.item()) != 0:
+            raise RuntimeError(f"grouped GEMM gave up on a wait (code {int(self.error_flag.item())})")
+
+    def destroy(self) -> None:
+        self.a2a.destroy()

@@ -56,6 +56,7 @@ def grouped_fp8_gemm(
     expert_padding: int = 1,
     error_flag: Optional[torch.Tensor] = None,
     num_ctas: int = 0,
+    wait_cycles: Optional[torch.Tensor] = None,
 ) -> None:
     """``out[rows of expert e] = epilogue(dequant(a rows) @ dequant(b[e]).T)``.
 
@@ -64,6 +65,9 @@ def grouped_fp8_gemm(
     (rows are expert-major, each expert's block starting at a multiple of ``expert_padding``).
     mode MODE_SWIGLU_QUANT: b = [gate; up], out [rows, N/2] e4m3 and out_scale [rows, N/256];
     mode MODE_BF16: out [rows, N] bf16.
+    ``wait_cycles`` (int64 [num CTAs, 4], optional) receives the cycles each pipeline role spent
+    waiting: producer for a free stage, MMA for a free accumulator, MMA for operands, epilogue
+    for partial sums.
     """
     assert a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn
     assert a.dim() == 2 and b.dim() == 3 and b.is_contiguous() and b_scale.is_contiguous()
@@ -86,4 +90,5 @@ def grouped_fp8_gemm(
         b.data_ptr(), b_scale.data_ptr(), expert_num_tokens.data_ptr(), out.data_ptr(),
         out.stride(0) * out.element_size(), 0 if out_scale is None else out_scale.data_ptr(),
         0 if out_scale is None else out_scale.stride(0), error_flag.data_ptr(), e, n, k, expert_padding, rows, mode,
-        num_ctas, torch.cuda.current_stream().cuda_stream)
+        num_ctas, torch.cuda.current_stream().cuda_stream,
+        0 if wait_cycles is None else wait_cycles.data_ptr())
