@@ -43,6 +43,7 @@ def main() -> None:
     ap.add_argument("--intermediate", type=int, default=768)
     ap.add_argument("--copies", type=int, default=4, help="operand sets rotated to defeat L2")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--ablate", action="store_true", help="also time the kernel with one pipeline stage removed")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     E, M, H, I = args.experts, args.rows_per_expert, args.hidden, args.intermediate
@@ -99,6 +100,22 @@ def main() -> None:
         waits[name] = {"kernel_us": c0.elapsed_time(c1) * 1e3, "mean_wait_cycles": {
             "producer_for_free_stage": m[0], "mma_for_free_accumulator": m[1], "mma_for_operands": m[2],
             "epilogue_for_partial_sums": m[3]}}
+    # what the remaining stages sustain with one stage removed (results are garbage, timing only)
+    ablation = {}
+    if args.ablate:
+        for label, skip in (("no_epilogue_reads", 1), ("no_mma", 2), ("no_tma", 4), ("tma_only", 3), ("mma_only", 5)):
+            def g1() -> None:
+                x, xs, w13, w13s, _, _ = sets[state["i"] % args.copies]
+                state["i"] += 1
+                grouped_fp8_gemm(x, xs, w13, w13s, cnt, act, act_s, mode=MODE_SWIGLU_QUANT, error_flag=flag,
+                                 debug_skip=skip)
+
+            def g2() -> None:
+                _, _, _, _, w2, w2s = sets[state["i"] % args.copies]
+                state["i"] += 1
+                grouped_fp8_gemm(act, act_s, w2, w2s, cnt, y, mode=MODE_BF16, error_flag=flag, debug_skip=skip)
+
+            ablation[label] = {"gate_up_us": time_op(g1, iters=args.iters), "down_us": time_op(g2, iters=args.iters)}
     f1, f2 = 2.0 * rows * 2 * I * H, 2.0 * rows * H * I
     out = {
         "shape": {"experts": E, "rows_per_expert": M, "hidden": H, "intermediate": I},
@@ -109,6 +126,7 @@ def main() -> None:
         "ffn_fraction_of_roofline": (f1 + f2) / t12 / 1e6 / (2 * bf16_peak),
         "roofline_note": f"2 x cuBLAS bf16 burst peak ({peak_kind})",
         "waits": waits,
+        "ablation": ablation,
     }
     print(json.dumps(out, indent=1))
 

@@ -112,6 +112,22 @@ __device__ __forceinline__ void bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" : : "r"(id), "r"(nthreads) : "memory");
 }
 
+// Named barrier that also ORs a predicate over its participants; every thread gets the result.
+__device__ __forceinline__ bool bar_red_or(int id, int nthreads, bool pred) {
+  uint32_t out;
+  asm volatile(
+      "{\n"
+      ".reg .pred p, q;\n"
+      "setp.ne.u32 p, %3, 0;\n"
+      "bar.red.or.pred q, %1, %2, p;\n"
+      "selp.u32 %0, 1, 0, q;\n"
+      "}\n"
+      : "=r"(out)
+      : "r"(id), "r"(nthreads), "r"(static_cast<uint32_t>(pred))
+      : "memory");
+  return out != 0;
+}
+
 __device__ __forceinline__ uint32_t elect_one() {
   uint32_t pred;
   asm volatile(

@@ -5,6 +5,7 @@
 
 #include "../core/error.h"
 #include "../ops/grouped_gemm.h"
+#include "../ops/router.h"
 
 namespace py = pybind11;
 using namespace pplx;
@@ -12,11 +13,34 @@ using namespace pplx::ops;
 
 void bind_ops(py::module_& m) {
   m.def(
+      "topk_route",
+      [](uint64_t logits, int64_t logits_stride, bool logits_bf16, uint64_t bias, uint64_t indices,
+         int64_t indices_stride, uint64_t weights, int64_t weights_stride, int tokens, int num_experts, int k,
+         uint64_t stream) {
+        TopkRouteParams p;
+        p.logits = reinterpret_cast<const void*>(logits);
+        p.logits_stride = logits_stride;
+        p.logits_bf16 = logits_bf16;
+        p.bias = reinterpret_cast<const float*>(bias);
+        p.indices = reinterpret_cast<uint32_t*>(indices);
+        p.indices_stride = indices_stride;
+        p.weights = reinterpret_cast<float*>(weights);
+        p.weights_stride = weights_stride;
+        p.tokens = tokens;
+        p.num_experts = num_experts;
+        p.k = k;
+        topk_route(p, reinterpret_cast<cudaStream_t>(stream));
+      },
+      py::arg("logits"), py::arg("logits_stride"), py::arg("logits_bf16"), py::arg("bias"), py::arg("indices"),
+      py::arg("indices_stride"), py::arg("weights"), py::arg("weights_stride"), py::arg("tokens"),
+      py::arg("num_experts"), py::arg("k"), py::arg("stream"));
+  m.def(
       "grouped_fp8_gemm",
       [](uint64_t a, int64_t a_stride, uint64_t a_scale, int64_t a_scale_stride_row, int64_t a_scale_stride_k,
          uint64_t b, uint64_t b_scale, uint64_t expert_num_tokens, uint64_t out, int64_t out_stride,
          uint64_t out_scale, int64_t out_scale_stride_row, uint64_t error_flag, int num_experts, int N, int K,
-         int expert_padding, int max_rows, int mode, int num_ctas, uint64_t stream, uint64_t wait_cycles) {
+         int expert_padding, int max_rows, int mode, int num_ctas, uint64_t stream, uint64_t wait_cycles,
+         int debug_skip, uint64_t trace) {
         GroupedGemmParams p;
         p.a = reinterpret_cast<const void*>(a);
         p.a_stride = a_stride;
@@ -39,11 +63,14 @@ void bind_ops(py::module_& m) {
         p.mode = mode;
         p.num_ctas = num_ctas;
         p.wait_cycles = reinterpret_cast<unsigned long long*>(wait_cycles);
+        p.debug_skip = debug_skip;
+        p.trace = reinterpret_cast<long long*>(trace);
         grouped_fp8_gemm(p, reinterpret_cast<cudaStream_t>(stream));
       },
       py::arg("a"), py::arg("a_stride"), py::arg("a_scale"), py::arg("a_scale_stride_row"),
       py::arg("a_scale_stride_k"), py::arg("b"), py::arg("b_scale"), py::arg("expert_num_tokens"), py::arg("out"),
       py::arg("out_stride"), py::arg("out_scale"), py::arg("out_scale_stride_row"), py::arg("error_flag"),
       py::arg("num_experts"), py::arg("N"), py::arg("K"), py::arg("expert_padding"), py::arg("max_rows"),
-      py::arg("mode"), py::arg("num_ctas"), py::arg("stream"), py::arg("wait_cycles") = 0);
+      py::arg("mode"), py::arg("num_ctas"), py::arg("stream"), py::arg("wait_cycles") = 0,
+      py::arg("debug_skip") = 0, py::arg("trace") = 0);
 }

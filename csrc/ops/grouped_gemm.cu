@@ -13,9 +13,9 @@
 // Structure (one persistent CTA per SM, three warpgroups):
 //   warp 0      TMA producer: 128x128-byte A tile + four 64-row B boxes per K block into a
 //               4-stage shared-memory ring (SWIZZLE_128B), completion on mbarriers
-//   warp 1      one thread issues tcgen05.mma (M 128, N 256, K 32 x 4 per K block) into one of
-//               two 256-column TMEM accumulators and commits to mbarriers
-//   (warps 2-3 idle; the first warpgroup gives most of its registers away with setmaxnreg)
+//   warps 1, 2  one thread each issues tcgen05.mma (M 128, N 256, K 32 x 4 per K block) into its
+//               own 256-column TMEM accumulator (even / odd K blocks) and commits to mbarriers
+//   (warp 3 idle; the first warpgroup gives most of its registers away with setmaxnreg)
 //   warps 4-11  epilogue: tcgen05.ld the K block's partial sums, scale them by
 //               a_scale[row, kb] * b_scale[nb, kb] and add into fp32 registers (the per-block
 //               scales differ along K, so the running sum cannot stay in TMEM), then apply the
@@ -51,8 +51,25 @@ constexpr int kEpilogueThreads = 256;
 constexpr uint32_t kABytes = kBM * kBK;        // 16 KiB
 constexpr uint32_t kBBoxBytes = 64 * kBK;      // 8 KiB, four boxes per stage
 constexpr uint32_t kStageBytes = kABytes + 4 * kBBoxBytes;  // 48 KiB
+constexpr uint32_t kWarpStageBytes = 32 * 64;   // per epilogue warp, for coalesced output stores
 constexpr uint32_t kTmemCols = 512;
+// Register split between the first warpgroup (copies, MMA issue) and the epilogue warps. The
+// pool is what the CTA was launched with, 168 registers for each of its 384 threads, not the
+// whole register file: setmaxnreg.inc waits until the registers it asks for are free, so a split
+// that asks for more than the first warpgroup gave back would wait for ever.
+constexpr int kLaunchRegs = 168;
+constexpr int kLightRegs = 48;
+constexpr int kEpilogueRegs = 224;
+static_assert(kFirstEpilogueWarp * 32 * kLightRegs + kEpilogueThreads * kEpilogueRegs <= kThreads * kLaunchRegs,
+              "the epilogue's setmaxnreg.inc could never be granted");
+static_assert(kLightRegs % 8 == 0 && kEpilogueRegs % 8 == 0, "setmaxnreg takes multiples of 8");
 constexpr int kMaxExperts = 64;
+constexpr int kTraceTiles = 64;
+// Rows 32..61 of the trace hold stamps for CTA 0's first K blocks, one row each: MMA committed,
+// epilogue saw the partial sums, epilogue released the accumulator, MMA got the accumulator,
+// MMA got the operands, MMA issued.
+constexpr int kTraceBlockBase = 32 * 8;
+constexpr uint32_t kTraceBlocks = 30;
 constexpr uint64_t kWaitNs = 2000000000ull;  // every mbarrier wait gives up after 2 s
 
 struct KernelArgs {
@@ -69,11 +86,13 @@ struct KernelArgs {
   int64_t out_scale_stride_row;    // elements
   uint32_t* error_flag;
   unsigned long long* wait_cycles;  // optional [grid][4]: cycles each role spent waiting
+  long long* trace;                 // optional [kTraceTiles][8]: SM clock at the phases of CTA 0's tiles
   int num_experts;
   int N, K;
   int expert_padding;
   int max_rows;
   int mode;
+  int debug_skip;   // profiling aid, 0 in production: 1 epilogue reads nothing, 2 no MMAs, 4 no TMA loads, 8 every MMA is issued twice
 };
 
 struct Schedule {
@@ -82,14 +101,38 @@ struct Schedule {
   int tile_prefix[kMaxExperts + 1];
 };
 
+// `*e` is a cursor: a CTA's tiles come in increasing order, so the search resumes at the expert of
+// the previous call (start it at 0) and costs a step or two instead of a scan.
 __device__ __forceinline__ void decode_tile(const Schedule& s, int num_experts, int n_tiles, int t, int* e,
                                             int* m_tile, int* n_tile) {
-  int lo = 0;
+  int lo = *e;
   while (lo + 1 < num_experts && t >= s.tile_prefix[lo + 1]) ++lo;
   const int local = t - s.tile_prefix[lo];
   *e = lo;
   *m_tile = local / n_tiles;
   *n_tile = local % n_tiles;
+}
+
+// One warp writes 64 bytes per row for its 32 rows (lane = row, as tensor memory hands them out)
+// with coalesced stores: the rows are transposed through a 2 KiB staging buffer so that one store
+// instruction covers 8 rows x 64 contiguous bytes instead of 32 rows x 16 bytes. The 16-byte units
+// of a row are XOR-swizzled with the row pair index, which keeps both sides free of bank conflicts.
+__device__ __forceinline__ void store_rows_64B(uint8_t* stage, int lane, const uint32_t (&w)[16], uint8_t* dst_row0,
+                                               int64_t row_stride, uint32_t valid_mask) {
+  #pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int pu = u ^ ((lane >> 1) & 3);
+    *reinterpret_cast<uint4*>(stage + lane * 64 + pu * 16) = make_uint4(w[4 * u], w[4 * u + 1], w[4 * u + 2], w[4 * u + 3]);
+  }
+  __syncwarp();
+  #pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = 8 * i + (lane >> 2);
+    const int u = lane & 3;
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 + ((u ^ ((r >> 1) & 3)) * 16));
+    if ((valid_mask >> r) & 1u) *reinterpret_cast<uint4*>(dst_row0 + r * row_stride + u * 16) = v;
+  }
+  __syncwarp();
 }
 
 __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __grid_constant__ KernelArgs a) {
@@ -108,6 +151,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
   const int nkb = a.K / kBK;
 
   if (threadIdx.x == 0) {
+    if (a.trace != nullptr && blockIdx.x == 0) {   // last row: kernel start / end, SM clock and ns
+      a.trace[(kTraceTiles - 1) * 8 + 0] = clock64();
+      a.trace[(kTraceTiles - 1) * 8 + 1] = static_cast<long long>(globaltimer_ns());
+    }
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
@@ -145,16 +192,17 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
   uint8_t* const tiles = smem + ((1024u - (smem_u32(smem) & 1023u)) & 1023u);
 
   if (warp < kFirstEpilogueWarp) {
-    // The first warpgroup only issues copies and MMAs: it keeps 40 registers per thread and
+    // The first warpgroup only issues copies and MMAs: it keeps kLightRegs registers per thread and
     // the epilogue warpgroups take the rest of the register file.
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kLightRegs) : "memory");
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
       long long waited = 0;
+      int e = 0;
       for (int t = blockIdx.x; t < total_tiles && !s_failed; t += gridDim.x) {
-        int e, m_tile, n_tile;
+        int m_tile, n_tile;
         decode_tile(sched, a.num_experts, n_tiles, t, &e, &m_tile, &n_tile);
         const int row0 = sched.row_start[e] + m_tile * kBM;
         int brow[4];
@@ -166,6 +214,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
         } else {
           for (int i = 0; i < 4; ++i) brow[i] = e * a.N + n_tile * kBN + 64 * i;
         }
+        const int trace_row = (a.trace != nullptr && blockIdx.x == 0 && t / gridDim.x < 32) ? t / gridDim.x : -1;
+        if (trace_row >= 0) a.trace[trace_row * 8 + 6] = clock64();
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t parity = ((it / kStages) & 1u) ^ 1u;
@@ -178,6 +228,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
             break;
           }
           uint8_t* stage = tiles + static_cast<size_t>(s) * kStageBytes;
+          if (a.debug_skip & 4) {   // profiling aid: hand over the stage without loading it
+            mbar_arrive(&full_bar[s]);
+            continue;
+          }
           mbar_expect_tx(&full_bar[s], kStageBytes);
           tma_load_2d(stage, &a.map_a, kb * kBK, row0, &full_bar[s]);
           #pragma unroll
@@ -185,84 +239,136 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
             tma_load_2d(stage + kABytes + i * kBBoxBytes, &a.map_b, kb * kBK, brow[i], &full_bar[s]);
           }
         }
+        if (trace_row >= 0) a.trace[trace_row * 8 + 7] = clock64();
       }
       if (a.wait_cycles != nullptr) a.wait_cycles[blockIdx.x * 4 + 0] = static_cast<unsigned long long>(waited);
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------------------------------------------ MMA issuers
+    // Two issuing threads, one per accumulator: warp 1 takes the even K blocks, warp 2 the odd
+    // ones. One thread's loop (two mbarrier waits, four tcgen05.mma, two commits) takes longer
+    // than the tensor cores need for a K block, so a single issuer leaves them idle half the
+    // time; the two streams are independent (different accumulators, different stages).
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_e4m3_f32(kBM, kBN);
-      uint32_t it = 0, acc_it = 0;
+      const uint32_t w = warp - 1;
+      const uint32_t my_tiles = static_cast<int>(blockIdx.x) < total_tiles
+                                    ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      const uint32_t total_blocks = my_tiles * static_cast<uint32_t>(nkb);
+      const bool timing = a.wait_cycles != nullptr;
+      const bool stamps = a.trace != nullptr && blockIdx.x == 0 && w == 0;
+      const int reps = (a.debug_skip & 2) ? 0 : ((a.debug_skip & 8) ? 2 : 1);   // profiling aid
+      const uint32_t d_tmem = tmem_base + w * kBN;
       long long waited_tmem = 0, waited_full = 0;
-      for (int t = blockIdx.x; t < total_tiles && !s_failed; t += gridDim.x) {
-        for (int kb = 0; kb < nkb; ++kb, ++it, ++acc_it) {
-          const int s = it % kStages;
-          const int buf = acc_it & 1;
-          const long long w0 = clock64();
-          const bool got_tmem = mbar_wait_timed(&tmem_empty_bar[buf], ((acc_it >> 1) & 1u) ^ 1u, kWaitNs);
-          const long long w1 = clock64();
-          const bool got_full = got_tmem && mbar_wait_timed(&full_bar[s], (it / kStages) & 1u, kWaitNs);
-          waited_tmem += w1 - w0;
-          waited_full += clock64() - w1;
-          if (!got_tmem || !got_full) {
-            s_failed = 1;
-            atomicExch(a.error_flag, 2u);
-            break;
-          }
-          fence_after_thread_sync();
-          const uint8_t* stage = tiles + static_cast<size_t>(s) * kStageBytes;
-          const uint64_t a_desc = smem_desc_k_sw128(stage);
-          const uint64_t b_desc = smem_desc_k_sw128(stage + kABytes);
-          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf) * kBN;
+      for (uint32_t it = w; it < total_blocks && !s_failed; it += 2) {
+        const int s = it % kStages;
+        // Operands first: they are usually there already (the producer runs ahead), so that
+        // nothing but the MMAs stands between getting the accumulator and using it.
+        const long long w0 = timing ? clock64() : 0;
+        const bool got_full = mbar_wait_timed(&full_bar[s], (it / kStages) & 1u, kWaitNs);
+        const uint8_t* stage = tiles + static_cast<size_t>(s) * kStageBytes;
+        const uint64_t a_desc = smem_desc_k_sw128(stage);
+        const uint64_t b_desc = smem_desc_k_sw128(stage + kABytes);
+        const long long w1 = (timing || stamps) ? clock64() : 0;
+        if (stamps && it < kTraceBlocks) a.trace[kTraceBlockBase + it * 8 + 4] = w1;
+        const bool got_tmem = got_full && mbar_wait_timed(&tmem_empty_bar[w], ((it >> 1) & 1u) ^ 1u, kWaitNs);
+        if (timing) {
+          waited_full += w1 - w0;
+          waited_tmem += clock64() - w1;
+        }
+        if (!got_tmem || !got_full) {
+          s_failed = 1;
+          atomicExch(a.error_flag, 2u);
+          break;
+        }
+        fence_after_thread_sync();
+        if (stamps && it < kTraceBlocks) a.trace[kTraceBlockBase + it * 8 + 3] = clock64();
+        for (int rep = 0; rep < reps; ++rep) {
           #pragma unroll
           for (int k4 = 0; k4 < kBK / 32; ++k4) {
             // advancing 32 bytes along K inside the 128-byte swizzled row: +2 in 16-byte units
             mma_f8f6f4(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
           }
-          mma_commit(&empty_bar[s]);          // the stage may be refilled once these MMAs are done
-          mma_commit(&tmem_full_bar[buf]);    // ... and the partial sums may be read
         }
+        if (stamps && it < kTraceBlocks) a.trace[kTraceBlockBase + it * 8 + 5] = clock64();
+        mma_commit(&tmem_full_bar[w]);     // the partial sums may be read once these MMAs are done
+        mma_commit(&empty_bar[s]);         // ... and the stage may be refilled
+        if (stamps && it < kTraceBlocks) a.trace[kTraceBlockBase + it * 8 + 0] = clock64();
       }
-      if (a.wait_cycles != nullptr) {
-        a.wait_cycles[blockIdx.x * 4 + 1] = static_cast<unsigned long long>(waited_tmem);
-        a.wait_cycles[blockIdx.x * 4 + 2] = static_cast<unsigned long long>(waited_full);
+      if (timing) {   // the two issuers' waits are summed
+        atomicAdd(&a.wait_cycles[blockIdx.x * 4 + 1], static_cast<unsigned long long>(waited_tmem));
+        atomicAdd(&a.wait_cycles[blockIdx.x * 4 + 2], static_cast<unsigned long long>(waited_full));
       }
     }
   }
   } else {
     // ------------------------------------------------------------------ epilogue warps
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kEpilogueRegs) : "memory");
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
     const int h = (warp - kFirstEpilogueWarp) >> 2;  // column half: 0 -> cols [0,128), 1 -> [128,256)
     const int row_in_tile = q * 32 + lane;
+    uint8_t* const warp_stage = tiles + static_cast<size_t>(kStages) * kStageBytes + (warp - kFirstEpilogueWarp) * kWarpStageBytes;
     const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
     uint32_t acc_it = 0;
     uint32_t tile_parity = 0;
     long long waited_acc = 0;
     const int nkb_scale = a.K / 128;
     const int nb_per_expert = a.N / 128;
+    // Where a tile's scales live for this thread: its row's a_scale and the two block rows of
+    // b_scale its columns fall into (gate / up under SwiGLU; one block row otherwise).
+    struct TileScales {
+      const float* a_row;
+      const float* b0;
+      const float* b1;
+    };
+    auto tile_scales = [&](int e, int m_tile, int n_tile) {
+      const int row = sched.row_start[e] + m_tile * kBM + row_in_tile;
+      const bool valid = m_tile * kBM + row_in_tile < sched.count[e] && row < a.max_rows;
+      const int nb0 = swiglu ? n_tile : n_tile * 2 + h;
+      const int nb1 = swiglu ? I / 128 + n_tile : nb0;
+      TileScales ts;
+      ts.a_row = a.a_scale + static_cast<int64_t>(valid ? row : 0) * a.a_scale_stride_row;
+      ts.b0 = a.b_scale + (static_cast<int64_t>(e) * nb_per_expert + nb0) * nkb_scale;
+      ts.b1 = a.b_scale + (static_cast<int64_t>(e) * nb_per_expert + nb1) * nkb_scale;
+      return ts;
+    };
+    // The first K block's scales of a tile are fetched one tile ahead: at a tile boundary they
+    // would otherwise be a cold read in front of the first fold.
+    float as_first = 0.f, b0_first = 0.f, b1_first = 0.f;
+    int e = 0, e_ahead = 0;   // expert cursors of this tile and of the next one
+    if (static_cast<int>(blockIdx.x) < total_tiles) {
+      int m_ahead, n_ahead;
+      decode_tile(sched, a.num_experts, n_tiles, blockIdx.x, &e_ahead, &m_ahead, &n_ahead);
+      const TileScales ts = tile_scales(e_ahead, m_ahead, n_ahead);
+      as_first = ts.a_row[0];
+      b0_first = ts.b0[0];
+      b1_first = ts.b1[0];
+    }
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, tile_parity ^= 1u) {
-      int e, m_tile, n_tile;
+      int m_tile, n_tile;
+      const int trace_row = (a.trace != nullptr && blockIdx.x == 0 && warp == kFirstEpilogueWarp && lane == 0 &&
+                             t / gridDim.x < 32) ? t / gridDim.x : -1;
+      if (trace_row >= 0) a.trace[trace_row * 8 + 0] = clock64();
       decode_tile(sched, a.num_experts, n_tiles, t, &e, &m_tile, &n_tile);
       const int row = sched.row_start[e] + m_tile * kBM + row_in_tile;
       const bool valid = m_tile * kBM + row_in_tile < sched.count[e] && row < a.max_rows;
-      const float* a_scale_row = a.a_scale + static_cast<int64_t>(valid ? row : 0) * a.a_scale_stride_row;
-      // block rows of B this thread's columns fall into
-      int nb0, nb1;
-      if (swiglu) {
-        nb0 = n_tile;                 // gate columns
-        nb1 = I / 128 + n_tile;       // up columns
-      } else {
-        nb0 = nb1 = n_tile * 2 + h;
+      const TileScales cur = tile_scales(e, m_tile, n_tile);
+      const float* a_scale_row = cur.a_row;
+      const float* bs0 = cur.b0;
+      const float* bs1 = cur.b1;
+      float as_next = as_first, b0_next = b0_first, b1_next = b1_first;
+      if (t + static_cast<int>(gridDim.x) < total_tiles) {
+        int m_ahead, n_ahead;
+        decode_tile(sched, a.num_experts, n_tiles, t + gridDim.x, &e_ahead, &m_ahead, &n_ahead);
+        const TileScales nx = tile_scales(e_ahead, m_ahead, n_ahead);
+        as_first = nx.a_row[0];
+        b0_first = nx.b0[0];
+        b1_first = nx.b1[0];
       }
-      const float* bs0 = a.b_scale + (static_cast<int64_t>(e) * nb_per_expert + nb0) * nkb_scale;
-      const float* bs1 = a.b_scale + (static_cast<int64_t>(e) * nb_per_expert + nb1) * nkb_scale;
 
       float acc[128];
       #pragma unroll
       for (int i = 0; i < 128; ++i) acc[i] = 0.f;
-      float as_next = a_scale_row[0];
-      float b0_next = bs0[0], b1_next = bs1[0];
       bool failed = false;
       for (int kb = 0; kb < nkb; ++kb, ++acc_it) {
         const int buf = acc_it & 1;
@@ -272,6 +378,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
           b0_next = bs0[kb + 1];
           b1_next = bs1[kb + 1];
         }
+        // thread columns [0,64) belong to block row nb0 and [64,128) to nb1 (gate / up under
+        // SwiGLU; the same block row twice otherwise)
+        const float sc0 = as * b0, sc1 = as * b1;
         // the verdict must be the same for the whole warp: tcgen05.ld below is warp-collective
         const long long w0 = clock64();
         const bool got = mbar_wait_timed(&tmem_full_bar[buf], (acc_it >> 1) & 1u, kWaitNs);
@@ -281,76 +390,95 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
           break;
         }
         fence_after_thread_sync();
-        const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(buf) * kBN + static_cast<uint32_t>(h) * 128;
-        // Two rounds of 64 columns: both 32-column loads of a round are in flight together,
-        // so the TMEM latency is paid twice per K block instead of once per 16 columns.
-        #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          uint32_t t0[32], t1[32];
-          tmem_ld32(taddr + r * 64, t0);
-          tmem_ld32(taddr + r * 64 + 32, t1);
-          tmem_ld_wait();
-          if (r == 1) {
-            // everything this warp needs from the buffer is in registers: hand it back early
-            fence_before_thread_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
-          }
-          // swiglu: thread columns [0,64) are gate, [64,128) up; plain: one block row for all
-          const float sc = as * ((swiglu ? r == 0 : true) ? b0 : b1);
-          #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            acc[r * 64 + i] = fmaf(sc, __uint_as_float(t0[i]), acc[r * 64 + i]);
-            acc[r * 64 + 32 + i] = fmaf(sc, __uint_as_float(t1[i]), acc[r * 64 + 32 + i]);
-          }
+        if (kb == 0 && trace_row >= 0) a.trace[trace_row * 8 + 1] = clock64();
+        const bool trace_block = trace_row >= 0 && acc_it < kTraceBlocks;
+        if (trace_block) a.trace[kTraceBlockBase + acc_it * 8 + 1] = clock64();
+        if (a.debug_skip & 1) {   // profiling aid: leave the partial sums unread
+          fence_before_thread_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+          if (trace_block) a.trace[kTraceBlockBase + acc_it * 8 + 2] = clock64();
+          continue;
         }
+        const uint32_t taddr = tmem_base + lane_addr + static_cast<uint32_t>(buf) * kBN + static_cast<uint32_t>(h) * 128;
+        // Four chunks of 32 columns, software-pipelined. A warp's tensor-memory loads do not
+        // overlap one another (a 32-column load takes about 90 cycles however many are in
+        // flight), but they do overlap its FMAs: the load of chunk c+1 runs while chunk c is folded.
+        uint32_t ta[32], tb[32];
+        tmem_ld32(taddr, ta);
+        tmem_ld_wait();
+        tmem_ld32(taddr + 32, tb);
+        #pragma unroll
+        for (int i = 0; i < 32; ++i) acc[i] = fmaf(sc0, __uint_as_float(ta[i]), acc[i]);
+        tmem_ld_wait();
+        tmem_ld32(taddr + 64, ta);
+        #pragma unroll
+        for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(sc0, __uint_as_float(tb[i]), acc[32 + i]);
+        tmem_ld_wait();
+        tmem_ld32(taddr + 96, tb);
+        #pragma unroll
+        for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(sc1, __uint_as_float(ta[i]), acc[64 + i]);
+        tmem_ld_wait();
+        // everything this warp needs from the buffer is in registers: hand it back
+        fence_before_thread_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+        if (trace_block) a.trace[kTraceBlockBase + acc_it * 8 + 2] = clock64();
+        #pragma unroll
+        for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(sc1, __uint_as_float(tb[i]), acc[96 + i]);
       }
       if (failed) {
         atomicExch(a.error_flag, 3u);
         s_failed = 1;
       }
+      if (trace_row >= 0) a.trace[trace_row * 8 + 2] = clock64();
 
+      // Rows of this warp that may be written, and the address of its first row.
+      const uint32_t valid_mask = __ballot_sync(0xffffffffu, valid && !failed);
+      const int64_t warp_row0 = static_cast<int64_t>(sched.row_start[e] + m_tile * kBM + q * 32);
       if (swiglu) {
         // out[c] = silu(gate[c]) * up[c] for this thread's 64 columns
         float amax = 0.f;
         #pragma unroll
         for (int i = 0; i < 64; ++i) {
           const float g = acc[i];
-          const float v = g / (1.f + __expf(-g)) * acc[64 + i];
+          const float v = __fdividef(g, 1.f + __expf(-g)) * acc[64 + i];
           acc[i] = v;
           amax = fmaxf(amax, fabsf(v));
         }
         s_amax[tile_parity][row_in_tile][h] = amax;
-        bar_sync(1, kEpilogueThreads);   // every epilogue thread gets here, also after a failed wait
+        // Every epilogue thread gets here, also after a failed wait, and all of them leave with
+        // the same verdict: a warp that went on alone would wait at this barrier for ever.
+        const bool any_failed = bar_red_or(1, kEpilogueThreads, failed || s_failed != 0);
         amax = fmaxf(s_amax[tile_parity][row_in_tile][0], s_amax[tile_parity][row_in_tile][1]);
         const float scale = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
         const float inv = 1.0f / scale;
-        if (valid && !failed) {
-          uint8_t* dst = a.out + static_cast<int64_t>(row) * a.out_stride + n_tile * 128 + h * 64;
-          #pragma unroll
-          for (int v4 = 0; v4 < 4; ++v4) {
-            uint32_t w[4];
-            #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int i = v4 * 16 + j * 4;
-              const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(acc[i] * inv, acc[i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
-              const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(acc[i + 2] * inv, acc[i + 3] * inv), __NV_SATFINITE, __NV_E4M3);
-              w[j] = lo | (hi << 16);
-            }
-            *reinterpret_cast<uint4*>(dst + 16 * v4) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-          if (h == 0) a.out_scale[static_cast<int64_t>(row) * a.out_scale_stride_row + n_tile] = scale;
-        }
-      } else if (valid && !failed) {
-        uint8_t* dst = a.out + static_cast<int64_t>(row) * a.out_stride + (static_cast<int64_t>(n_tile) * kBN + h * 128) * 2;
+        uint32_t w[16];
         #pragma unroll
-        for (int v8 = 0; v8 < 16; ++v8) {
-          __nv_bfloat162 p[4];
+        for (int j = 0; j < 16; ++j) {
+          const int i = j * 4;
+          const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(acc[i] * inv, acc[i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+          const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(acc[i + 2] * inv, acc[i + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+          w[j] = lo | (hi << 16);
+        }
+        store_rows_64B(warp_stage, lane, w, a.out + warp_row0 * a.out_stride + n_tile * 128 + h * 64, a.out_stride,
+                       any_failed ? 0u : valid_mask);
+        if (h == 0 && valid && !any_failed) a.out_scale[static_cast<int64_t>(row) * a.out_scale_stride_row + n_tile] = scale;
+        failed = any_failed;
+      } else {
+        uint8_t* dst = a.out + warp_row0 * a.out_stride + (static_cast<int64_t>(n_tile) * kBN + h * 128) * 2;
+        #pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t w[16];
           #pragma unroll
-          for (int j = 0; j < 4; ++j) p[j] = __floats2bfloat162_rn(acc[v8 * 8 + 2 * j], acc[v8 * 8 + 2 * j + 1]);
-          *reinterpret_cast<uint4*>(dst + 16 * v8) = *reinterpret_cast<uint4*>(p);
+          for (int j = 0; j < 16; ++j) {
+            const __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[c * 32 + 2 * j], acc[c * 32 + 2 * j + 1]);
+            w[j] = *reinterpret_cast<const uint32_t*>(&p2);
+          }
+          store_rows_64B(warp_stage, lane, w, dst + c * 64, a.out_stride, valid_mask);
         }
       }
+      if (trace_row >= 0) a.trace[trace_row * 8 + 3] = clock64();
       if (failed) break;
     }
     if (a.wait_cycles != nullptr && warp == kFirstEpilogueWarp && lane == 0) {
@@ -360,6 +488,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
 
   fence_before_thread_sync();
   __syncthreads();
+  if (a.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+    a.trace[(kTraceTiles - 1) * 8 + 2] = clock64();
+    a.trace[(kTraceTiles - 1) * 8 + 3] = static_cast<long long>(globaltimer_ns());
+  }
   if (warp == 1) {
     fence_after_thread_sync();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -413,17 +545,19 @@ void grouped_fp8_gemm(const GroupedGemmParams& p, cudaStream_t stream) {
   a.out_scale_stride_row = p.out_scale_stride_row;
   a.error_flag = p.error_flag;
   a.wait_cycles = p.wait_cycles;
+  a.trace = p.trace;
   a.num_experts = p.num_experts;
   a.N = p.N;
   a.K = p.K;
   a.expert_padding = p.expert_padding;
   a.max_rows = p.max_rows;
   a.mode = p.mode;
+  a.debug_skip = p.debug_skip;
 
   int device = 0, sms = 0;
   PPLX_CUDA_CHECK(cudaGetDevice(&device));
   PPLX_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-  const size_t smem = static_cast<size_t>(kStages) * kStageBytes + 1024;
+  const size_t smem = static_cast<size_t>(kStages) * kStageBytes + (kEpilogueThreads / 32) * kWarpStageBytes + 1024;
   PPLX_CUDA_CHECK(cudaFuncSetAttribute(grouped_fp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem)));
   const int grid = p.num_ctas > 0 ? p.num_ctas : sms;

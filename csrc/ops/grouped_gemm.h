@@ -30,12 +30,21 @@ struct GroupedGemmParams {
   // stage), the MMA issuer (for a free accumulator, for operands) and the first epilogue warp
   // (for partial sums). Shows which stage of the pipeline is the bottleneck.
   unsigned long long* wait_cycles = nullptr;
+  // Optional device array [64][8] of SM clock readings for the first 64 tiles of CTA 0: epilogue
+  // tile start, first partial sums ready, K loop done, tile stored; MMA first issue, last commit;
+  // producer first load, last load.
+  long long* trace = nullptr;
   int num_experts = 0;
   int N = 0, K = 0;
   int expert_padding = 1;           // every expert's rows start at a multiple of this
   int max_rows = 0;
   int mode = kBf16;
   int num_ctas = 0;                 // 0: one per SM
+  // Profiling aid, 0 in production (results are wrong otherwise). Bit 0: the epilogue leaves the
+  // partial sums unread; bit 1: no MMAs are issued; bit 2: no TMA loads;
+  // bit 3: every MMA is issued twice. Timing the kernel with
+  // one stage removed shows what the other stages can sustain.
+  int debug_skip = 0;
 };
 
 void grouped_fp8_gemm(const GroupedGemmParams& params, cudaStream_t stream);

@@ -22,15 +22,16 @@ import torch
 from pplx_garden.distributed import ParallelGroup
 from pplx_garden.kernels.p2p_all_to_all import P2PAllToAll
 from pplx_garden.ops import MODE_BF16, MODE_SWIGLU_QUANT, grouped_fp8_gemm, quantize_128x128
+from pplx_garden.ops.router import topk_route, topk_route_reference
 from pplx_garden.utils.math import ceil_div
 
 
 def route_topk(logits: torch.Tensor, topk: int) -> tuple[torch.Tensor, torch.Tensor]:
     """Top-k experts by logit and their softmax weights renormalised over the chosen k.
     Returns (indices uint32 [tokens, k], weights float32 [tokens, k])."""
-    top = torch.topk(logits.float(), topk, dim=-1)
-    weights = torch.softmax(top.values, dim=-1)
-    return top.indices.to(torch.int32).view(torch.uint32), weights
+    if logits.is_cuda:
+        return topk_route(logits, topk)
+    return topk_route_reference(logits, topk)
 
 
 class ExpertParallelMoE:
@@ -90,12 +91,20 @@ class ExpertParallelMoE:
         if out is None:
             out = torch.empty_like(x)
         self.a2a.dispatch(self.expert_num_tokens, self.expert_x, self.expert_x_scale, x, None, indices, weights)
-        grouped_fp8_gemm(self.expert_x, self.expert_x_scale, self.w13, self.w13_scale, self.expert_num_tokens,
-                         self.act, self.act_scale, mode=MODE_SWIGLU_QUANT, error_flag=self.error_flag)
-        grouped_fp8_gemm(self.act, self.act_scale, self.w2, self.w2_scale, self.expert_num_tokens,
-                         self.expert_y, mode=MODE_BF16, error_flag=self.error_flag)
+        self.gate_up()
+        self.down()
         self.a2a.combine(out, indices, weights, self.expert_y)
         return out
+
+    def gate_up(self) -> None:
+        """act = quantise(silu(x W_gate^T) * (x W_up^T)) on the rows dispatch delivered."""
+        grouped_fp8_gemm(self.expert_x, self.expert_x_scale, self.w13, self.w13_scale, self.expert_num_tokens,
+                         self.act, self.act_scale, mode=MODE_SWIGLU_QUANT, error_flag=self.error_flag)
+
+    def down(self) -> None:
+        """expert_y = act W_down^T in bf16: the rows combine sends home."""
+        grouped_fp8_gemm(self.act, self.act_scale, self.w2, self.w2_scale, self.expert_num_tokens,
+                         self.expert_y, mode=MODE_BF16, error_flag=self.error_flag)
 
     __call__ = forward
 

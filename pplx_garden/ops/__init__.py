@@ -9,3 +9,7 @@ from pplx_garden.ops.grouped_gemm import (
     quantize_1x128 as quantize_1x128,
     quantize_128x128 as quantize_128x128,
 )
+from pplx_garden.ops.router import (
+    topk_route as topk_route,
+    topk_route_reference as topk_route_reference,
+)

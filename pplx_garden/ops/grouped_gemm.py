@@ -57,6 +57,8 @@ def grouped_fp8_gemm(
     error_flag: Optional[torch.Tensor] = None,
     num_ctas: int = 0,
     wait_cycles: Optional[torch.Tensor] = None,
+    debug_skip: int = 0,
+    trace: Optional[torch.Tensor] = None,
 ) -> None:
     """``out[rows of expert e] = epilogue(dequant(a rows) @ dequant(b[e]).T)``.
 
@@ -67,7 +69,10 @@ def grouped_fp8_gemm(
     mode MODE_BF16: out [rows, N] bf16.
     ``wait_cycles`` (int64 [num CTAs, 4], optional) receives the cycles each pipeline role spent
     waiting: producer for a free stage, MMA for a free accumulator, MMA for operands, epilogue
-    for partial sums.
+    for partial sums. ``debug_skip`` (profiling only, wrong results) removes a stage: 1 the
+    epilogue's reads, 2 the MMAs, 4 the TMA loads. ``trace`` (int64 [64, 8], optional) receives SM clock
+    readings for the tiles of CTA 0: epilogue tile start / first partial sums / K loop done / stored,
+    MMA first issue / last commit, producer first / last load.
     """
     assert a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn
     assert a.dim() == 2 and b.dim() == 3 and b.is_contiguous() and b_scale.is_contiguous()
@@ -91,4 +96,5 @@ def grouped_fp8_gemm(
         out.stride(0) * out.element_size(), 0 if out_scale is None else out_scale.data_ptr(),
         0 if out_scale is None else out_scale.stride(0), error_flag.data_ptr(), e, n, k, expert_padding, rows, mode,
         num_ctas, torch.cuda.current_stream().cuda_stream,
-        0 if wait_cycles is None else wait_cycles.data_ptr())
+        0 if wait_cycles is None else wait_cycles.data_ptr(), debug_skip,
+        0 if trace is None else trace.data_ptr())
