@@ -143,7 +143,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
   __shared__ float s_amax[2][kBM][2];
   __shared__ uint32_t s_failed;
 
-  const int warp = threadIdx.x >> 5;
+  // broadcast from lane 0 so that the compiler knows the warp index is the same in every lane
+  // and keeps the role code (loop counters, descriptors, addresses) in the uniform datapath
+  const int warp = __shfl_sync(0xffffffffu, threadIdx.x >> 5, 0);
   const int lane = threadIdx.x & 31;
   const bool swiglu = a.mode == kSwiGLUQuant;
   const int I = a.N / 2;
@@ -249,53 +251,64 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
     // ones. One thread's loop (two mbarrier waits, four tcgen05.mma, two commits) takes longer
     // than the tensor cores need for a K block, so a single issuer leaves them idle half the
     // time; the two streams are independent (different accumulators, different stages).
-    if (lane == 0) {
+    {
+      // The whole warp runs the loop and one elected lane issues: descriptors and addresses then
+      // stay in uniform registers, which is what tcgen05.mma takes, instead of being moved there
+      // one by one in front of every instruction.
       constexpr uint32_t idesc = idesc_e4m3_f32(kBM, kBN);
       const uint32_t w = warp - 1;
       const uint32_t my_tiles = static_cast<int>(blockIdx.x) < total_tiles
                                     ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
       const uint32_t total_blocks = my_tiles * static_cast<uint32_t>(nkb);
       const bool timing = a.wait_cycles != nullptr;
-      const bool stamps = a.trace != nullptr && blockIdx.x == 0 && w == 0;
+      const bool stamps = a.trace != nullptr && blockIdx.x == 0 && w == 0 && lane == 0;
       const int reps = (a.debug_skip & 2) ? 0 : ((a.debug_skip & 8) ? 2 : 1);   // profiling aid
       const uint32_t d_tmem = tmem_base + w * kBN;
       long long waited_tmem = 0, waited_full = 0;
-      for (uint32_t it = w; it < total_blocks && !s_failed; it += 2) {
+      for (uint32_t it = w; it < total_blocks; it += 2) {
+        // one lane's reading for all: lanes that disagreed about leaving would split the warp
+        // in front of the warp-wide votes below
+        if (__shfl_sync(0xffffffffu, *reinterpret_cast<volatile uint32_t*>(&s_failed), 0) != 0) break;
         const int s = it % kStages;
         // Operands first: they are usually there already (the producer runs ahead), so that
         // nothing but the MMAs stands between getting the accumulator and using it.
         const long long w0 = timing ? clock64() : 0;
-        const bool got_full = mbar_wait_timed(&full_bar[s], (it / kStages) & 1u, kWaitNs);
+        const bool got_full = __all_sync(0xffffffffu, mbar_wait_timed(&full_bar[s], (it / kStages) & 1u, kWaitNs));
         const uint8_t* stage = tiles + static_cast<size_t>(s) * kStageBytes;
         const uint64_t a_desc = smem_desc_k_sw128(stage);
         const uint64_t b_desc = smem_desc_k_sw128(stage + kABytes);
         const long long w1 = (timing || stamps) ? clock64() : 0;
         if (stamps && it < kTraceBlocks) a.trace[kTraceBlockBase + it * 8 + 4] = w1;
-        const bool got_tmem = got_full && mbar_wait_timed(&tmem_empty_bar[w], ((it >> 1) & 1u) ^ 1u, kWaitNs);
+        const bool got_tmem =
+            got_full && __all_sync(0xffffffffu, mbar_wait_timed(&tmem_empty_bar[w], ((it >> 1) & 1u) ^ 1u, kWaitNs));
         if (timing) {
           waited_full += w1 - w0;
           waited_tmem += clock64() - w1;
         }
         if (!got_tmem || !got_full) {
-          s_failed = 1;
-          atomicExch(a.error_flag, 2u);
+          if (lane == 0) {
+            s_failed = 1;
+            atomicExch(a.error_flag, 2u);
+          }
           break;
         }
         fence_after_thread_sync();
         if (stamps && it < kTraceBlocks) a.trace[kTraceBlockBase + it * 8 + 3] = clock64();
-        for (int rep = 0; rep < reps; ++rep) {
-          #pragma unroll
-          for (int k4 = 0; k4 < kBK / 32; ++k4) {
-            // advancing 32 bytes along K inside the 128-byte swizzled row: +2 in 16-byte units
-            mma_f8f6f4(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+        if (elect_one()) {
+          for (int rep = 0; rep < reps; ++rep) {
+            #pragma unroll
+            for (int k4 = 0; k4 < kBK / 32; ++k4) {
+              // advancing 32 bytes along K inside the 128-byte swizzled row: +2 in 16-byte units
+              mma_f8f6f4(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+            }
           }
+          mma_commit(&tmem_full_bar[w]);     // the partial sums may be read once these MMAs are done
+          mma_commit(&empty_bar[s]);         // ... and the stage may be refilled
         }
-        if (stamps && it < kTraceBlocks) a.trace[kTraceBlockBase + it * 8 + 5] = clock64();
-        mma_commit(&tmem_full_bar[w]);     // the partial sums may be read once these MMAs are done
-        mma_commit(&empty_bar[s]);         // ... and the stage may be refilled
+        __syncwarp();
         if (stamps && it < kTraceBlocks) a.trace[kTraceBlockBase + it * 8 + 0] = clock64();
       }
-      if (timing) {   // the two issuers' waits are summed
+      if (timing && lane == 0) {   // the two issuers' waits are summed
         atomicAdd(&a.wait_cycles[blockIdx.x * 4 + 1], static_cast<unsigned long long>(waited_tmem));
         atomicAdd(&a.wait_cycles[blockIdx.x * 4 + 2], static_cast<unsigned long long>(waited_full));
       }
