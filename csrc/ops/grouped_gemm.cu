@@ -43,14 +43,14 @@ namespace {
 
 using namespace pplx::tc;
 
-constexpr int kBM = 128, kBN = 256, kBK = 128;
-constexpr int kStages = 4;
+constexpr int kBM = 128, kBN = 256, kBK = 128;   // per CTA; a CTA pair computes 256 x 256
+constexpr int kStages = 6;
 constexpr int kThreads = 384;
 constexpr int kFirstEpilogueWarp = 4;
 constexpr int kEpilogueThreads = 256;
 constexpr uint32_t kABytes = kBM * kBK;        // 16 KiB
-constexpr uint32_t kBBoxBytes = 64 * kBK;      // 8 KiB, four boxes per stage
-constexpr uint32_t kStageBytes = kABytes + 4 * kBBoxBytes;  // 48 KiB
+constexpr uint32_t kBBoxBytes = 64 * kBK;      // 8 KiB; a CTA holds two boxes: its half of the tile's B rows
+constexpr uint32_t kStageBytes = kABytes + 2 * kBBoxBytes;  // 32 KiB per CTA
 constexpr uint32_t kWarpStageBytes = 32 * 64;   // per epilogue warp, for coalesced output stores
 constexpr uint32_t kTmemCols = 512;
 // Register split between the first warpgroup (copies, MMA issue) and the epilogue warps. The
@@ -135,7 +135,8 @@ __device__ __forceinline__ void store_rows_64B(uint8_t* stage, int lane, const u
   __syncwarp();
 }
 
-__global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __grid_constant__ KernelArgs a) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+    grouped_fp8_gemm_kernel(const __grid_constant__ KernelArgs a) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ uint64_t full_bar[kStages], empty_bar[kStages], tmem_full_bar[2], tmem_empty_bar[2];
   __shared__ uint32_t tmem_base_slot;
@@ -151,6 +152,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
   const int I = a.N / 2;
   const int n_tiles = swiglu ? I / 128 : a.N / kBN;
   const int nkb = a.K / kBK;
+  // The two CTAs of a cluster form a pair: rank 0 (the leader) issues the MMAs for both.
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
     if (a.trace != nullptr && blockIdx.x == 0) {   // last row: kernel start / end, SM clock and ns
@@ -163,7 +168,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full_bar[b], 1);
-      mbar_init(&tmem_empty_bar[b], kEpilogueThreads / 32);
+      mbar_init(&tmem_empty_bar[b], 2 * kEpilogueThreads / 32);   // the epilogue warps of both CTAs (leader's copy is used)
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_failed = 0;
@@ -174,7 +179,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
       sched.row_start[e] = row;
       sched.count[e] = n;
       sched.tile_prefix[e] = tiles;
-      tiles += (n + kBM - 1) / kBM * n_tiles;
+      tiles += (n + 2 * kBM - 1) / (2 * kBM) * n_tiles;   // one tile = 256 rows: 128 per CTA of the pair
       row += (n + a.expert_padding - 1) / a.expert_padding * a.expert_padding;
     }
     sched.tile_prefix[a.num_experts] = tiles;
@@ -182,11 +187,12 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
     prefetch_tensormap(&a.map_b);
   }
   if (warp == 1) {
-    tmem_alloc(&tmem_base_slot, kTmemCols);
-    tmem_relinquish();
+    tmem_alloc_pair(&tmem_base_slot, kTmemCols);
+    tmem_relinquish_pair();
   }
+  // Both CTAs' barriers and tensor memory must exist before either signals the other.
   fence_before_thread_sync();
-  __syncthreads();
+  cluster_sync_all();
   fence_after_thread_sync();
   const uint32_t tmem_base = tmem_base_slot;
   const int total_tiles = sched.tile_prefix[a.num_experts];
@@ -203,20 +209,22 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
       uint32_t it = 0;
       long long waited = 0;
       int e = 0;
-      for (int t = blockIdx.x; t < total_tiles && !s_failed; t += gridDim.x) {
-        int m_tile, n_tile;
-        decode_tile(sched, a.num_experts, n_tiles, t, &e, &m_tile, &n_tile);
-        const int row0 = sched.row_start[e] + m_tile * kBM;
-        int brow[4];
+      const uint32_t full_leader = map_to_cta(&full_bar[0], 0);   // the leader's barriers count both CTAs' bytes
+      for (int t = pair; t < total_tiles && !s_failed; t += num_pairs) {
+        int m_pair, n_tile;
+        decode_tile(sched, a.num_experts, n_tiles, t, &e, &m_pair, &n_tile);
+        const int row0 = sched.row_start[e] + (2 * m_pair + static_cast<int>(rank)) * kBM;
+        // This CTA's half of the tile's 256 B rows (accumulator columns [128 rank, 128 rank + 128)).
+        // SwiGLU interleaves gate and up in 64-row boxes so that a thread's columns hold both.
+        int brow[2];
         if (swiglu) {
-          brow[0] = e * a.N + n_tile * 128;
-          brow[1] = e * a.N + I + n_tile * 128;
-          brow[2] = brow[0] + 64;
-          brow[3] = brow[1] + 64;
+          brow[0] = e * a.N + n_tile * 128 + 64 * static_cast<int>(rank);
+          brow[1] = brow[0] + I;
         } else {
-          for (int i = 0; i < 4; ++i) brow[i] = e * a.N + n_tile * kBN + 64 * i;
+          brow[0] = e * a.N + n_tile * kBN + 128 * static_cast<int>(rank);
+          brow[1] = brow[0] + 64;
         }
-        const int trace_row = (a.trace != nullptr && blockIdx.x == 0 && t / gridDim.x < 32) ? t / gridDim.x : -1;
+        const int trace_row = (a.trace != nullptr && blockIdx.x == 0 && t / num_pairs < 32) ? t / num_pairs : -1;
         if (trace_row >= 0) a.trace[trace_row * 8 + 6] = clock64();
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % kStages;
@@ -231,21 +239,22 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
           }
           uint8_t* stage = tiles + static_cast<size_t>(s) * kStageBytes;
           if (a.debug_skip & 4) {   // profiling aid: hand over the stage without loading it
-            mbar_arrive(&full_bar[s]);
+            if (rank == 0) mbar_arrive(&full_bar[s]);
             continue;
           }
-          mbar_expect_tx(&full_bar[s], kStageBytes);
-          tma_load_2d(stage, &a.map_a, kb * kBK, row0, &full_bar[s]);
+          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * kStageBytes);
+          const uint32_t full_s = full_leader + static_cast<uint32_t>(s) * 8u;
+          tma_load_2d_pair(stage, &a.map_a, kb * kBK, row0, full_s);
           #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            tma_load_2d(stage + kABytes + i * kBBoxBytes, &a.map_b, kb * kBK, brow[i], &full_bar[s]);
+          for (int i = 0; i < 2; ++i) {
+            tma_load_2d_pair(stage + kABytes + i * kBBoxBytes, &a.map_b, kb * kBK, brow[i], full_s);
           }
         }
         if (trace_row >= 0) a.trace[trace_row * 8 + 7] = clock64();
       }
       if (a.wait_cycles != nullptr) a.wait_cycles[blockIdx.x * 4 + 0] = static_cast<unsigned long long>(waited);
     }
-  } else if (warp == 1 || warp == 2) {
+  } else if ((warp == 1 || warp == 2) && rank == 0) {
     // ------------------------------------------------------------------ MMA issuers
     // Two issuing threads, one per accumulator: warp 1 takes the even K blocks, warp 2 the odd
     // ones. One thread's loop (two mbarrier waits, four tcgen05.mma, two commits) takes longer
@@ -255,10 +264,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
       // The whole warp runs the loop and one elected lane issues: descriptors and addresses then
       // stay in uniform registers, which is what tcgen05.mma takes, instead of being moved there
       // one by one in front of every instruction.
-      constexpr uint32_t idesc = idesc_e4m3_f32(kBM, kBN);
+      constexpr uint32_t idesc = idesc_e4m3_f32(2 * kBM, kBN);
       const uint32_t w = warp - 1;
-      const uint32_t my_tiles = static_cast<int>(blockIdx.x) < total_tiles
-                                    ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+      const uint32_t my_tiles = pair < total_tiles ? (total_tiles - pair + num_pairs - 1) / num_pairs : 0;
       const uint32_t total_blocks = my_tiles * static_cast<uint32_t>(nkb);
       const bool timing = a.wait_cycles != nullptr;
       const bool stamps = a.trace != nullptr && blockIdx.x == 0 && w == 0 && lane == 0;
@@ -299,11 +307,12 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
             #pragma unroll
             for (int k4 = 0; k4 < kBK / 32; ++k4) {
               // advancing 32 bytes along K inside the 128-byte swizzled row: +2 in 16-byte units
-              mma_f8f6f4(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+              mma_f8f6f4_pair(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
             }
           }
-          mma_commit(&tmem_full_bar[w]);     // the partial sums may be read once these MMAs are done
-          mma_commit(&empty_bar[s]);         // ... and the stage may be refilled
+          // in both CTAs: the partial sums may be read once these MMAs are done, and the stage refilled
+          mma_commit_pair(&tmem_full_bar[w], 0x3);
+          mma_commit_pair(&empty_bar[s], 0x3);
         }
         __syncwarp();
         if (stamps && it < kTraceBlocks) a.trace[kTraceBlockBase + it * 8 + 0] = clock64();
@@ -349,20 +358,22 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
     // would otherwise be a cold read in front of the first fold.
     float as_first = 0.f, b0_first = 0.f, b1_first = 0.f;
     int e = 0, e_ahead = 0;   // expert cursors of this tile and of the next one
-    if (static_cast<int>(blockIdx.x) < total_tiles) {
+    const uint32_t tmem_empty_leader = map_to_cta(&tmem_empty_bar[0], 0);
+    if (pair < total_tiles) {
       int m_ahead, n_ahead;
-      decode_tile(sched, a.num_experts, n_tiles, blockIdx.x, &e_ahead, &m_ahead, &n_ahead);
-      const TileScales ts = tile_scales(e_ahead, m_ahead, n_ahead);
+      decode_tile(sched, a.num_experts, n_tiles, pair, &e_ahead, &m_ahead, &n_ahead);
+      const TileScales ts = tile_scales(e_ahead, 2 * m_ahead + static_cast<int>(rank), n_ahead);
       as_first = ts.a_row[0];
       b0_first = ts.b0[0];
       b1_first = ts.b1[0];
     }
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, tile_parity ^= 1u) {
-      int m_tile, n_tile;
+    for (int t = pair; t < total_tiles; t += num_pairs, tile_parity ^= 1u) {
+      int m_pair, n_tile;
       const int trace_row = (a.trace != nullptr && blockIdx.x == 0 && warp == kFirstEpilogueWarp && lane == 0 &&
-                             t / gridDim.x < 32) ? t / gridDim.x : -1;
+                             t / num_pairs < 32) ? t / num_pairs : -1;
       if (trace_row >= 0) a.trace[trace_row * 8 + 0] = clock64();
-      decode_tile(sched, a.num_experts, n_tiles, t, &e, &m_tile, &n_tile);
+      decode_tile(sched, a.num_experts, n_tiles, t, &e, &m_pair, &n_tile);
+      const int m_tile = 2 * m_pair + static_cast<int>(rank);   // this CTA's 128 rows of the pair's 256
       const int row = sched.row_start[e] + m_tile * kBM + row_in_tile;
       const bool valid = m_tile * kBM + row_in_tile < sched.count[e] && row < a.max_rows;
       const TileScales cur = tile_scales(e, m_tile, n_tile);
@@ -370,10 +381,10 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
       const float* bs0 = cur.b0;
       const float* bs1 = cur.b1;
       float as_next = as_first, b0_next = b0_first, b1_next = b1_first;
-      if (t + static_cast<int>(gridDim.x) < total_tiles) {
+      if (t + num_pairs < total_tiles) {
         int m_ahead, n_ahead;
-        decode_tile(sched, a.num_experts, n_tiles, t + gridDim.x, &e_ahead, &m_ahead, &n_ahead);
-        const TileScales nx = tile_scales(e_ahead, m_ahead, n_ahead);
+        decode_tile(sched, a.num_experts, n_tiles, t + num_pairs, &e_ahead, &m_ahead, &n_ahead);
+        const TileScales nx = tile_scales(e_ahead, 2 * m_ahead + static_cast<int>(rank), n_ahead);
         as_first = nx.a_row[0];
         b0_first = nx.b0[0];
         b1_first = nx.b1[0];
@@ -409,7 +420,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
         if (a.debug_skip & 1) {   // profiling aid: leave the partial sums unread
           fence_before_thread_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+          if (lane == 0) mbar_arrive_cluster(tmem_empty_leader + static_cast<uint32_t>(buf) * 8u);
           if (trace_block) a.trace[kTraceBlockBase + acc_it * 8 + 2] = clock64();
           continue;
         }
@@ -435,7 +446,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
         // everything this warp needs from the buffer is in registers: hand it back
         fence_before_thread_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty_bar[buf]);
+        if (lane == 0) mbar_arrive_cluster(tmem_empty_leader + static_cast<uint32_t>(buf) * 8u);
         if (trace_block) a.trace[kTraceBlockBase + acc_it * 8 + 2] = clock64();
         #pragma unroll
         for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(sc1, __uint_as_float(tb[i]), acc[96 + i]);
@@ -499,15 +510,17 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel(const __g
     }
   }
 
+  // Neither CTA may leave, or give its tensor memory back, while the other can still signal its
+  // barriers or write its accumulators.
   fence_before_thread_sync();
-  __syncthreads();
+  cluster_sync_all();
   if (a.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
     a.trace[(kTraceTiles - 1) * 8 + 2] = clock64();
     a.trace[(kTraceTiles - 1) * 8 + 3] = static_cast<long long>(globaltimer_ns());
   }
   if (warp == 1) {
     fence_after_thread_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
@@ -573,7 +586,7 @@ void grouped_fp8_gemm(const GroupedGemmParams& p, cudaStream_t stream) {
   const size_t smem = static_cast<size_t>(kStages) * kStageBytes + (kEpilogueThreads / 32) * kWarpStageBytes + 1024;
   PPLX_CUDA_CHECK(cudaFuncSetAttribute(grouped_fp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem)));
-  const int grid = p.num_ctas > 0 ? p.num_ctas : sms;
+  const int grid = std::max(2, (p.num_ctas > 0 ? p.num_ctas : sms) & ~1);   // whole CTA pairs
   grouped_fp8_gemm_kernel<<<grid, kThreads, smem, stream>>>(a);
   PPLX_CUDA_CHECK(cudaGetLastError());
 }

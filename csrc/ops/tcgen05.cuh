@@ -134,4 +134,80 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" : : "r"(smem_u32(bar)) : "memory");
 }
 
+// ---- CTA pairs (cta_group::2): two CTAs of one cluster, ranks 2i and 2i+1, work on one MMA ----
+// The even CTA (the leader) issues the MMAs; each CTA holds its 128 rows of A, its half of B's
+// rows, and its 128 rows of the accumulator in its own tensor memory.
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of `smem_ptr`'s counterpart in the shared memory of CTA `rank` of this cluster, for
+// instructions that take a .shared::cluster address.
+__device__ __forceinline__ uint32_t map_to_cta(const void* smem_ptr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_u32(smem_ptr)), "r"(rank));
+  return out;
+}
+// All threads of all CTAs of the cluster. Not bounded: every thread must get here on every path.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Executed by one warp in EACH CTA of the pair (as CUTLASS does in its 2-SM kernels).
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+               :
+               : "r"(smem_u32(smem_result)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" : : "r"(taddr), "r"(ncols) : "memory");
+}
+// 2-D tile load into this CTA's shared memory whose bytes are counted on the mbarrier at the
+// .shared::cluster address `bar_cluster_addr` (the leader's). No multicast: each CTA loads its own.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar_cluster_addr)
+      : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B^T over the pair: M 256 (128 rows per CTA), B's N rows split in
+// halves between the CTAs. Issued by one thread of the leader; the descriptors are the leader's
+// shared-memory addresses, which the peer mirrors.
+__device__ __forceinline__ void mma_f8f6f4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n"
+      "}\n"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// Arrives on the mbarrier at `bar`'s offset in every CTA of `cta_mask` once the pair's MMAs issued
+// so far have completed.
+__device__ __forceinline__ void mma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      :
+      : "r"(smem_u32(bar)), "h"(cta_mask)
+      : "memory");
+}
+// Arrive on an mbarrier given by a .shared::cluster address (this CTA's or a peer's). Default
+// semantics on purpose: a cluster-scope release would first drain every global store this thread
+// has in flight, and the tensor-memory reads that the arrival publishes are ordered by
+// tcgen05.fence::before_thread_sync, not by the memory model's release.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" : : "r"(bar_cluster_addr) : "memory");
+}
+
 }  // namespace pplx::tc
