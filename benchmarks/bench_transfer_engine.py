@@ -60,6 +60,11 @@ def kv_phase(src_dev: int, dst_dev: int, seqs: int, layers: int, pool_pages: int
             rx.set_imm_count_expected(0x1000 + layer, total_pages, layer_done[layer].set)
         errors: list[str] = []
         sent = threading.Semaphore(0)
+        # untimed first write: opens the peer mapping, loads the copy kernel, sizes the staging buffer
+        warm = PageIndices(list(range(min(64, pool_pages))))
+        tx.submit_paged_writes(PAGE_BYTES, hs, warm, PAGE_BYTES, 0, dd, warm, PAGE_BYTES, 0, None, sent.release,
+                               lambda e: (errors.append(e), sent.release()))
+        sent.acquire()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         for layer in range(layers):
@@ -108,6 +113,16 @@ def reshard_phase(devices: list[int], total_gb: float, hidden: int = 7168) -> di
         n_sub = 0
         row_bytes_src = cols_src * 2
         row_bytes_dst = row_bytes_src * (tp_src // tp_dst)
+        # untimed first write per source: opens the peer mapping, loads the copy kernel
+        for i, d in enumerate(devices):
+            j, slot = divmod(i, tp_src // tp_dst)
+            warm = PageIndices(list(range(8)))
+            engines[d].submit_paged_writes(row_bytes_src, handles[i], warm, row_bytes_src, 0, descs[j], warm,
+                                           row_bytes_dst, slot * row_bytes_src, None, done.release,
+                                           lambda e: (errors.append(e), done.release()))
+        for _ in devices:
+            done.acquire()
+        torch.cuda.synchronize()
         t0 = time.perf_counter()
         for i, d in enumerate(devices):
             j, slot = divmod(i, tp_src // tp_dst)
