@@ -44,6 +44,7 @@ std::string type_of(const json::Value& obj) {
 struct MetaspaceConfig {
   std::string replacement;
   bool add_prefix_space = true;
+  bool split = true;   // HuggingFace's default: the pre-tokenizer cuts the text into words
 };
 
 // Reads {"type":"Metaspace","replacement":"▁","add_prefix_space":true} or the newer
@@ -65,6 +66,7 @@ MetaspaceConfig read_metaspace(const json::Value& v) {
   } else {
     invalid("Metaspace needs add_prefix_space or prepend_scheme");
   }
+  if (const json::Value* sp = v.find("split"); sp != nullptr && sp->is_bool()) m.split = sp->as_bool();
   return m;
 }
 
@@ -214,6 +216,7 @@ std::shared_ptr<Engine> Engine::from_hf_json_bytes(std::string_view bytes) {
   if (pre_ms.add_prefix_space != dec_ms.add_prefix_space) unsupported("metaspace add_prefix_space mismatch");
   eng->replacement_ = pre_ms.replacement;
   eng->add_prefix_space_ = pre_ms.add_prefix_space;
+  eng->split_words_ = pre_ms.split;
 
   // model
   const json::Value& model = member(root, "model", "tokenizer.json");
@@ -313,7 +316,27 @@ void Engine::encode_segment(std::string_view text, EncodeState* st) const {
     st->best_start.resize(n + 1);
     st->best_id.resize(n + 1);
   }
-  if (n > 0) viterbi(reinterpret_cast<const uint8_t*>(prep.data()), n, st);
+  if (n == 0) return;
+  const uint8_t* bytes = reinterpret_cast<const uint8_t*>(prep.data());
+  if (!split_words_) {
+    viterbi(bytes, n, st);
+    return;
+  }
+  // One Viterbi pass per word, a word starting at each replacement character: what the model
+  // sees behind HuggingFace's Metaspace pre-tokenizer. The best path of the whole text is the
+  // concatenation of the words' best paths except where two paths tie, and there the rounding
+  // of the running sum decides; sums that restart at every word round as the original's do.
+  // (The reference runs one pass over the whole segment: pplx-unigram/src/engine.rs:88-165.)
+  const size_t rl = replacement_.size();
+  size_t word = 0;
+  for (size_t i = rl > 0 ? 1 : n; i + rl <= n; ++i) {
+    if (prep.compare(i, rl, replacement_) == 0) {
+      viterbi(bytes + word, i - word, st);
+      word = i;
+      i += rl - 1;
+    }
+  }
+  viterbi(bytes + word, n - word, st);
 }
 
 void Engine::viterbi(const uint8_t* prep, size_t n, EncodeState* st) const {

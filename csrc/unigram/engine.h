@@ -106,6 +106,7 @@ class Engine {
   VocabTrie trie_;
   std::string replacement_;  // UTF-8 of the metaspace replacement character
   bool add_prefix_space_ = true;
+  bool split_words_ = true;   // Metaspace "split": encode word by word
   TokenId unk_id_ = 0;
   double unk_score_ = 0.0;
   size_t vocab_size_ = 0;

@@ -2,6 +2,8 @@
 
 #include <cerrno>
 #include <cstdlib>
+#include <cmath>
+#include <cstdio>
 #include <cstring>
 #include <stdexcept>
 
@@ -99,24 +101,96 @@ class Parser {
     }
   }
 
+  // Numbers are converted the way Rust's serde_json does without its float_roundtrip feature
+  // (what HuggingFace tokenizers and pplx-unigram read vocabularies with): the digits are
+  // gathered into a 64-bit significand, converted to double, and scaled by one power of ten.
+  // That is up to one unit in the last place away from the correctly rounded value for
+  // 16-17 digit literals, and Viterbi ties between equal-score paths are decided by exactly that
+  // last bit, so strtod here would make some encodings differ from the originals'.
+  static double pow10_table(int k) {
+    static const std::vector<double> table = [] {
+      std::vector<double> t(309);
+      for (int i = 0; i <= 308; ++i) {
+        char lit[16];
+        std::snprintf(lit, sizeof(lit), "1e%d", i);
+        t[static_cast<size_t>(i)] = std::strtod(lit, nullptr);
+      }
+      return t;
+    }();
+    return table[static_cast<size_t>(k)];
+  }
+
+  static double from_parts(bool positive, uint64_t significand, long long exponent) {
+    double f = static_cast<double>(significand);
+    for (;;) {
+      const long long mag = exponent < 0 ? -exponent : exponent;
+      if (mag <= 308) {
+        if (exponent >= 0) {
+          f *= pow10_table(static_cast<int>(mag));
+        } else {
+          f /= pow10_table(static_cast<int>(mag));
+        }
+        break;
+      }
+      if (f == 0.0) break;
+      if (exponent >= 0) return positive ? HUGE_VAL : -HUGE_VAL;
+      f /= 1e308;
+      exponent += 308;
+    }
+    return positive ? f : -f;
+  }
+
   Value number() {
-    const char* start = p_;
-    if (p_ < end_ && *p_ == '-') ++p_;
-    if (p_ >= end_ || !(*p_ >= '0' && *p_ <= '9')) fail("expected a value");
-    while (p_ < end_ && ((*p_ >= '0' && *p_ <= '9') || *p_ == '.' || *p_ == 'e' || *p_ == 'E' ||
-                         *p_ == '+' || *p_ == '-')) {
+    bool positive = true;
+    if (p_ < end_ && *p_ == '-') {
+      positive = false;
       ++p_;
     }
-    // strtod needs a terminated buffer; numbers are short.
-    char buf[64];
-    const size_t n = static_cast<size_t>(p_ - start);
-    if (n >= sizeof(buf)) fail("number too long");
-    std::memcpy(buf, start, n);
-    buf[n] = 0;
-    char* endp = nullptr;
-    const double d = std::strtod(buf, &endp);
-    if (endp != buf + n) fail("malformed number");
-    return Value::make_number(d);
+    if (p_ >= end_ || !(*p_ >= '0' && *p_ <= '9')) fail("expected a value");
+    uint64_t significand = 0;
+    long long exponent = 0;
+    bool saturated = false;   // further digits no longer fit: they only move the exponent
+    auto push_digit = [&](unsigned d, bool fractional) {
+      const uint64_t max = ~uint64_t{0};
+      if (!saturated && (significand >= max / 10 && (significand > max / 10 || d > max % 10))) saturated = true;
+      if (saturated) {
+        if (!fractional) ++exponent;
+        return;
+      }
+      significand = significand * 10 + d;
+      if (fractional) --exponent;
+    };
+    if (*p_ == '0') {
+      ++p_;
+      if (p_ < end_ && *p_ >= '0' && *p_ <= '9') fail("malformed number");
+    } else {
+      while (p_ < end_ && *p_ >= '0' && *p_ <= '9') push_digit(static_cast<unsigned>(*p_++ - '0'), false);
+    }
+    bool is_float = false;
+    if (p_ < end_ && *p_ == '.') {
+      ++p_;
+      is_float = true;
+      if (p_ >= end_ || !(*p_ >= '0' && *p_ <= '9')) fail("malformed number");
+      while (p_ < end_ && *p_ >= '0' && *p_ <= '9') push_digit(static_cast<unsigned>(*p_++ - '0'), true);
+    }
+    if (p_ < end_ && (*p_ == 'e' || *p_ == 'E')) {
+      ++p_;
+      is_float = true;
+      bool exp_positive = true;
+      if (p_ < end_ && (*p_ == '+' || *p_ == '-')) exp_positive = *p_++ == '+';
+      if (p_ >= end_ || !(*p_ >= '0' && *p_ <= '9')) fail("malformed number");
+      long long e = 0;
+      while (p_ < end_ && *p_ >= '0' && *p_ <= '9') {
+        if (e < 100000) e = e * 10 + (*p_ - '0');
+        ++p_;
+      }
+      exponent += exp_positive ? e : -e;
+    }
+    if (!is_float && !saturated) {   // an integer literal: exact conversion of the integer
+      const double d = static_cast<double>(significand);
+      return Value::make_number(positive ? d : -d);
+    }
+    return Value::make_number(from_parts(positive, significand, exponent));
   }
 
   static void append_utf8(std::string* out, uint32_t cp) {
