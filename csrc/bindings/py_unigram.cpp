@@ -5,6 +5,7 @@
 #include <pybind11/stl.h>
 
 #include "../unigram/engine.h"
+#include "../unigram/json.h"
 #include "../unigram/unicode.h"
 
 namespace py = pybind11;
@@ -97,6 +98,16 @@ void bind_unigram(py::module_& m) {
         }
         return out;
       });
+
+  // The numbers of a flat JSON object as the loader converts them (a test hook).
+  m.def("_json_numbers", [](const std::string& text) {
+    py::dict out;
+    const pplx::json::Value v = pplx::json::parse(text);
+    for (const auto& kv : v.as_object()) {
+      if (kv.second.is_number()) out[py::str(kv.first)] = kv.second.as_number();
+    }
+    return out;
+  });
 
   m.def("_grapheme_breaks", [](const std::string& text) {
     std::vector<size_t> ends;

@@ -138,3 +138,31 @@ def test_rejected_configurations(small_vocab, mutate, message) -> None:
 def test_malformed_json_is_reported() -> None:
     with pytest.raises(ValueError):
         Engine.from_hf_json_bytes(b'{"model": ')
+
+
+def test_equal_score_paths_break_ties_like_huggingface() -> None:
+    """On a 32,000-piece vocabulary with 17-digit scores some words have two segmentations whose
+    scores differ only in the last bit of the running sum ('l' + 'll' against 'll' + 'l'). Which one
+    wins depends on where the sum restarts (at every word) and on how the score literals were
+    converted to doubles (serde_json's one-multiply conversion, not strtod): both must match."""
+    tokenizers = pytest.importorskip("tokenizers")
+    vocab = unigram_data.make_vocab(32000, seed=0)
+    spec = unigram_data.tokenizer_json(vocab)
+    docs = unigram_data.make_corpus(32, 10000, seed=0)
+    engine = Engine.from_hf_json_bytes(spec)
+    hf = tokenizers.Tokenizer.from_str(spec)
+    want = [e.ids for e in hf.encode_batch(docs, add_special_tokens=False)]
+    assert engine.encode_batch(docs, 2) == want
+
+
+def test_number_literals_convert_like_serde_json() -> None:
+    # integer literals are exact, short decimals are exact, and a 17-digit literal goes through
+    # u64 -> double -> one division by a power of ten
+    model = {"a": 1, "b": -0.5, "c": 1e3, "d": -12.143931267304547, "e": 12345678901234567890123, "f": 2.5E-3}
+    text = json.dumps(model)
+    got = _native._json_numbers(text) if hasattr(_native, "_json_numbers") else None
+    if got is None:
+        pytest.skip("number parser is not exposed")
+    assert got["a"] == 1.0 and got["b"] == -0.5 and got["c"] == 1000.0 and got["f"] == 0.0025
+    assert got["d"] == -(float(12143931267304547) / 1e15)
+    assert got["e"] == pytest.approx(1.2345678901234568e22, rel=1e-15)
