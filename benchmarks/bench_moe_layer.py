@@ -8,6 +8,9 @@ Two arms on the same inputs, one process per GPU:
 * ours      route (top-k kernel) -> dispatch with fused fp8 quantisation over NVLink peer
             stores -> tcgen05 grouped GEMM gate/up with SwiGLU + requantise -> grouped GEMM
             down -> weighted combine (`pplx_garden.models.ExpertParallelMoE`)
+* fused     as ours, but the down projection's epilogue writes every row over NVLink into the
+            combine receive buffer of the GPU its token came from and signals the receivers
+            (no expert_y round trip, no combine send kernel)
 * library   the same layer from library parts only: torch top-k, NCCL all_to_all_single
             dispatch / combine (`NcclAllToAll`), per-expert cuBLAS bf16 matmuls on the
             dequantised weights. The reference's own kernels cannot be built here, so this is
@@ -48,6 +51,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-library", action="store_true")
+    ap.add_argument("--no-fused", action="store_true", help="skip the arm whose down projection sends the rows itself")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -120,6 +124,20 @@ def main() -> None:
                          ("down", o_gemm2), ("combine", o_combine)])
     layer.check()
     ours_out = out.float().clone()
+
+    # the same layer with the down projection writing its rows into the peers' combine buffers
+    fused = None
+    if not args.no_fused:
+        def f_down_send() -> None:
+            layer.down_and_send()
+
+        def f_recv() -> None:
+            layer.a2a.combine(out, st["idx"], st["w"], None, do_send=False, do_recv=True)
+
+        fused = timed_phases([("route", o_route), ("dispatch", o_dispatch), ("gate_up_swiglu", o_gemm1),
+                              ("down_and_combine_send", f_down_send), ("combine_recv", f_recv)])
+        layer.check()
+        fused["equal_to_unfused"] = bool(torch.equal(out.float(), ours_out))
     rows = int(layer.expert_num_tokens.sum().item())
     flops = 2.0 * rows * (2 * I * H + H * I)
     ours["expert_rows_this_rank"] = rows
@@ -172,8 +190,9 @@ def main() -> None:
                        "experts": E, "topk": K, "n_gpus": world, "l2": "flushed before each layer",
                        "steps": args.steps, "warmup": args.warmup},
             "unit": "us, max over ranks",
-            "ours": ours, "library": lib, "max_rel_err_ours_vs_library": max_err,
+            "ours": ours, "ours_fused_combine": fused, "library": lib, "max_rel_err_ours_vs_library": max_err,
             "speedup_layer": None if lib is None else lib["layer"] / ours["layer"],
+            "speedup_layer_fused": None if lib is None or fused is None else lib["layer"] / fused["layer"],
         }))
     layer.destroy()
     if pg is not None:

@@ -178,6 +178,7 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
     const size_t o_status = take(sizeof(uint32_t) * 4);
     const size_t o_stats = take(sizeof(unsigned long long) * 8);
     const size_t o_trace = take(sizeof(unsigned long long) * kTraceSlots);
+    const size_t o_scatter_done = take(sizeof(uint32_t));
     void* base = nullptr;
     PPLX_CUDA_CHECK(cudaMalloc(&base, off));
     allocations_.push_back(base);
@@ -196,6 +197,7 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
     st.local.stats = reinterpret_cast<unsigned long long*>(b + o_stats);
     st.local.trace = reinterpret_cast<unsigned long long*>(b + o_trace);
     trace_ptrs_.push_back(st.local.trace);
+    scatter_done_ptrs_.push_back(reinterpret_cast<uint32_t*>(b + o_scatter_done));
     uint32_t* host_flag = nullptr;
     PPLX_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&host_flag), 64, cudaHostAllocMapped));
     std::memset(host_flag, 0, 64);
@@ -324,6 +326,32 @@ void A2AContext::combine(const CombineSendArgs* send, const CombineRecvArgs* rec
   if (do_recv) recv_team = pick(tokens, static_cast<int64_t>(cfg_.hidden_dim / 8) * 8);
   PPLX_CUDA_CHECK(a2a_launch_combine(cfg_, states_, n, s, r, send_team, recv_team, y_dtype,
                                      out_dtype, stream));
+}
+
+std::vector<A2AScatterInfo> A2AContext::combine_send_external() {
+  PPLX_REQUIRE(cfg_.combine_mode == kCombinePerRoute, "an external combine send needs the per_route mode");
+  PPLX_REQUIRE(cfg_.dp_size == 1, "an external combine send does not replicate to dp peers");
+  PPLX_REQUIRE(cfg_.out_elemsize == 2, "an external combine send writes 2-byte elements");
+  advance_phase(kPhaseCombineSend, kPhaseCombineSend);
+  std::vector<A2AScatterInfo> out(ranks_.size());
+  for (size_t i = 0; i < ranks_.size(); ++i) {
+    const A2ARankState& st = states_.r[i];
+    A2AScatterInfo& s = out[i];
+    s = A2AScatterInfo{};
+    s.row_src = st.local.row_src;
+    s.row_tk = st.local.row_tk;
+    for (int p = 0; p < cfg_.world; ++p) {
+      s.peer_recv[p] = st.recv[p] + cfg_.off_crecv;
+      // combine arrivals live in flag row 1, indexed by the sending rank
+      s.peer_flag[p] = reinterpret_cast<uint32_t*>(st.sync[p]) + (1 * kMaxRanks + st.rank) * kFlagStrideWords;
+    }
+    s.slot_stride = cfg_.c_stride;
+    s.world = cfg_.world;
+    s.signal_value = static_cast<uint32_t>(cfg_.num_blocks);   // what num_blocks sending blocks would add
+    s.done_counter = scatter_done_ptrs_[i];
+    s.status = st.local.status;
+  }
+  return out;
 }
 
 A2AStatusInfo A2AContext::status(int i) const {

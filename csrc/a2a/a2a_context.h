@@ -43,6 +43,20 @@ struct A2AStatusInfo {
   std::string message() const;
 };
 
+// What a kernel other than combine_send needs in order to play the combine's send phase
+// itself: where each received row goes and how to tell the receivers that it got there.
+struct A2AScatterInfo {
+  const uint32_t* row_src;         // [max_recv_rows] rank a row's token came from, kNoSlot = padding
+  const uint32_t* row_tk;          // [max_recv_rows] token * topk + k at that rank
+  uint8_t* peer_recv[kMaxRanks];   // combine receive area of every rank as mapped here
+  uint64_t slot_stride;            // bytes per (token, k) slot
+  uint32_t* peer_flag[kMaxRanks];  // this rank's combine arrival counter at every rank
+  int world;
+  uint32_t signal_value;           // arrivals a receiver expects from one sender per combine
+  uint32_t* done_counter;          // scratch word, zero between launches
+  const uint32_t* status;          // this rank's status word
+};
+
 class A2AContext {
  public:
   // `ranks` lists the ranks this process plays (one entry in a real multi-GPU run).
@@ -62,6 +76,12 @@ class A2AContext {
                 bool do_recv, cudaStream_t stream);
   void combine(const CombineSendArgs* send, const CombineRecvArgs* recv, bool do_send,
                bool do_recv, int y_dtype, int out_dtype, cudaStream_t stream);
+
+  // The send phase of a combine done by somebody else's kernel (the down projection's epilogue
+  // writes the rows into the peers' buffers and signals): advances the phase order as
+  // combine(do_send only) would and returns, for every local rank, what that kernel needs.
+  // Only for per-route combines without replication (dp_size 1) and 2-byte outputs.
+  std::vector<A2AScatterInfo> combine_send_external();
 
   // Synchronous read of the status word of local rank `i` (does not wait for the stream).
   A2AStatusInfo status(int i = 0) const;
@@ -95,6 +115,7 @@ class A2AContext {
   std::vector<unsigned long long*> stats_ptrs_;
   std::vector<uint32_t*> iters_ptrs_;
   std::vector<unsigned long long*> trace_ptrs_;
+  std::vector<uint32_t*> scatter_done_ptrs_;
   int next_phase_ = kPhaseDispatchSend;
   int64_t last_tokens_ = 0;
   int team_override_ = 0;

@@ -303,6 +303,24 @@ void bind_a2a(py::module_& m) {
            },
            py::arg("expert_x_ptr"), py::arg("expert_x_stride"), py::arg("stream"),
            py::arg("expert_y_dtype") = py::none())
+      .def("combine_send_external",
+           [](PyA2A& s) {
+             py::list out;
+             for (const A2AScatterInfo& i : s.ctx->combine_send_external()) {
+               py::list recv, flags;
+               for (int p = 0; p < i.world; ++p) {
+                 recv.append(reinterpret_cast<uint64_t>(i.peer_recv[p]));
+                 flags.append(reinterpret_cast<uint64_t>(i.peer_flag[p]));
+               }
+               out.append(py::make_tuple(reinterpret_cast<uint64_t>(i.row_src), reinterpret_cast<uint64_t>(i.row_tk),
+                                         recv, i.slot_stride, flags, i.world, i.signal_value,
+                                         reinterpret_cast<uint64_t>(i.done_counter),
+                                         reinterpret_cast<uint64_t>(i.status)));
+             }
+             return out;
+           },
+           "The combine's send phase is done by another kernel (grouped_fp8_gemm in its scatter mode): "
+           "counts as combine_send in the phase order and returns one descriptor per local rank.")
       .def("combine_recv",
            [](PyA2A& s, int num_tokens, const py::object& /*num_recv_tokens*/,
               const py::object& expert_y_dtype, uint64_t out_tokens_ptr,

@@ -40,7 +40,7 @@ void bind_ops(py::module_& m) {
          uint64_t b, uint64_t b_scale, uint64_t expert_num_tokens, uint64_t out, int64_t out_stride,
          uint64_t out_scale, int64_t out_scale_stride_row, uint64_t error_flag, int num_experts, int N, int K,
          int expert_padding, int max_rows, int mode, int num_ctas, uint64_t stream, uint64_t wait_cycles,
-         int debug_skip, uint64_t trace) {
+         int debug_skip, uint64_t trace, const py::object& scatter) {
         GroupedGemmParams p;
         p.a = reinterpret_cast<const void*>(a);
         p.a_stride = a_stride;
@@ -65,6 +65,28 @@ void bind_ops(py::module_& m) {
         p.wait_cycles = reinterpret_cast<unsigned long long*>(wait_cycles);
         p.debug_skip = debug_skip;
         p.trace = reinterpret_cast<long long*>(trace);
+        if (!scatter.is_none()) {
+          // the tuple AllToAllContext.combine_send_external() returns for this rank
+          const py::tuple t = scatter.cast<py::tuple>();
+          PPLX_REQUIRE(t.size() == 9, "scatter descriptor needs 9 entries");
+          CombineScatter& sc = p.scatter;
+          sc.row_src = reinterpret_cast<const uint32_t*>(t[0].cast<uint64_t>());
+          sc.row_tk = reinterpret_cast<const uint32_t*>(t[1].cast<uint64_t>());
+          const py::list recv = t[2].cast<py::list>();
+          const py::list flags = t[4].cast<py::list>();
+          sc.world = t[5].cast<int>();
+          PPLX_REQUIRE(sc.world >= 1 && sc.world <= CombineScatter::kMaxPeers &&
+                           static_cast<int>(recv.size()) == sc.world && static_cast<int>(flags.size()) == sc.world,
+                       "scatter descriptor: peer lists do not match the world size");
+          for (int i = 0; i < sc.world; ++i) {
+            sc.peer_recv[i] = reinterpret_cast<uint8_t*>(recv[i].cast<uint64_t>());
+            sc.peer_flag[i] = reinterpret_cast<uint32_t*>(flags[i].cast<uint64_t>());
+          }
+          sc.slot_stride = t[3].cast<uint64_t>();
+          sc.signal_value = t[6].cast<uint32_t>();
+          sc.done_counter = reinterpret_cast<uint32_t*>(t[7].cast<uint64_t>());
+          sc.status = reinterpret_cast<const uint32_t*>(t[8].cast<uint64_t>());
+        }
         grouped_fp8_gemm(p, reinterpret_cast<cudaStream_t>(stream));
       },
       py::arg("a"), py::arg("a_stride"), py::arg("a_scale"), py::arg("a_scale_stride_row"),
@@ -72,5 +94,6 @@ void bind_ops(py::module_& m) {
       py::arg("out_stride"), py::arg("out_scale"), py::arg("out_scale_stride_row"), py::arg("error_flag"),
       py::arg("num_experts"), py::arg("N"), py::arg("K"), py::arg("expert_padding"), py::arg("max_rows"),
       py::arg("mode"), py::arg("num_ctas"), py::arg("stream"), py::arg("wait_cycles") = 0,
-      py::arg("debug_skip") = 0, py::arg("trace") = 0);
+      py::arg("debug_skip") = 0, py::arg("trace") = 0,
+      py::arg("scatter") = py::none());
 }

@@ -92,6 +92,7 @@ struct KernelArgs {
   int expert_padding;
   int max_rows;
   int mode;
+  CombineScatter scatter;
   int debug_skip;   // profiling aid, 0 in production: 1 epilogue reads nothing, 2 no MMAs, 4 no TMA loads, 8 every MMA is issued twice
 };
 
@@ -131,6 +132,34 @@ __device__ __forceinline__ void store_rows_64B(uint8_t* stage, int lane, const u
     const int u = lane & 3;
     const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 + ((u ^ ((r >> 1) & 3)) * 16));
     if ((valid_mask >> r) & 1u) *reinterpret_cast<uint4*>(dst_row0 + r * row_stride + u * 16) = v;
+  }
+  __syncwarp();
+}
+
+// The same transposition, with every row going to an address of its own (`row_ptr`, held by the
+// lane that owns the row; null = nowhere): rows of the down projection written straight into the
+// combine receive buffers of the GPUs their tokens came from. Streaming stores: the data is not
+// read again on this GPU.
+__device__ __forceinline__ void scatter_rows_64B(uint8_t* stage, int lane, const uint32_t (&w)[16], uint8_t* row_ptr,
+                                                 uint32_t col_bytes) {
+  #pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int pu = u ^ ((lane >> 1) & 3);
+    *reinterpret_cast<uint4*>(stage + lane * 64 + pu * 16) = make_uint4(w[4 * u], w[4 * u + 1], w[4 * u + 2], w[4 * u + 3]);
+  }
+  __syncwarp();
+  const unsigned long long mine = reinterpret_cast<unsigned long long>(row_ptr);
+  #pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = 8 * i + (lane >> 2);
+    const int u = lane & 3;
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 + ((u ^ ((r >> 1) & 3)) * 16));
+    uint8_t* const base = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, mine, r));
+    if (base != nullptr) {
+      Vec16 out;
+      out.x = v.x; out.y = v.y; out.z = v.z; out.w = v.w;
+      st_stream_v4(base + col_bytes + u * 16, out);
+    }
   }
   __syncwarp();
 }
@@ -489,6 +518,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                        any_failed ? 0u : valid_mask);
         if (h == 0 && valid && !any_failed) a.out_scale[static_cast<int64_t>(row) * a.out_scale_stride_row + n_tile] = scale;
         failed = any_failed;
+      } else if (a.mode == kBf16Scatter) {
+        // this lane's row: which GPU its token came from and which slot of that GPU's combine
+        // receive buffer it fills
+        uint8_t* row_ptr = nullptr;
+        if (valid && !failed) {
+          const uint32_t src = a.scatter.row_src[row];
+          if (src < static_cast<uint32_t>(a.scatter.world)) {
+            row_ptr = a.scatter.peer_recv[src] + static_cast<uint64_t>(a.scatter.row_tk[row]) * a.scatter.slot_stride;
+          }
+        }
+        const uint32_t col0 = static_cast<uint32_t>(n_tile * kBN + h * 128) * 2u;
+        #pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t w[16];
+          #pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[c * 32 + 2 * j], acc[c * 32 + 2 * j + 1]);
+            w[j] = *reinterpret_cast<const uint32_t*>(&p2);
+          }
+          scatter_rows_64B(warp_stage, lane, w, row_ptr, col0 + c * 64);
+        }
       } else {
         uint8_t* dst = a.out + warp_row0 * a.out_stride + (static_cast<int64_t>(n_tile) * kBN + h * 128) * 2;
         #pragma unroll
@@ -514,6 +564,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   // barriers or write its accumulators.
   fence_before_thread_sync();
   cluster_sync_all();
+  if (a.mode == kBf16Scatter && threadIdx.x == 0) {
+    // The last CTA to get here tells every GPU that this rank's rows have been written. Each CTA's
+    // stores are ordered before its increment (system fence after the barrier above), the last
+    // CTA's increment reads all the others' (acq_rel), and its release covers what it has seen.
+    fence_acq_rel_sys();
+    const uint32_t before = atom_acq_rel_gpu_add(a.scatter.done_counter, 1u);
+    if (before == gridDim.x - 1) {
+      *a.scatter.done_counter = 0;   // ready for the next launch
+      const bool healthy = *a.scatter.status == 0 && s_failed == 0 && *a.error_flag == 0;
+      if (healthy) {
+        fence_acq_rel_sys();
+        for (int p = 0; p < a.scatter.world; ++p) red_release_sys_add(a.scatter.peer_flag[p], a.scatter.signal_value);
+      }
+    }
+  }
   if (a.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
     a.trace[(kTraceTiles - 1) * 8 + 2] = clock64();
     a.trace[(kTraceTiles - 1) * 8 + 3] = static_cast<long long>(globaltimer_ns());
@@ -552,6 +617,20 @@ void grouped_fp8_gemm(const GroupedGemmParams& p, cudaStream_t stream) {
   } else {
     PPLX_REQUIRE(p.N % kBN == 0, "N must be a multiple of 256");
   }
+  if (p.mode == kBf16Scatter) {
+    const CombineScatter& sc = p.scatter;
+    PPLX_REQUIRE(sc.row_src != nullptr && sc.row_tk != nullptr && sc.done_counter != nullptr && sc.status != nullptr &&
+                     sc.world >= 1 && sc.world <= CombineScatter::kMaxPeers,
+                 "kBf16Scatter needs the combine scatter description");
+    PPLX_REQUIRE(sc.slot_stride % 16 == 0 && sc.slot_stride >= static_cast<uint64_t>(p.N) * 2,
+                 "combine slots must hold a bf16 row and be 16-byte aligned");
+    for (int i = 0; i < sc.world; ++i) {
+      PPLX_REQUIRE(sc.peer_recv[i] != nullptr && reinterpret_cast<uintptr_t>(sc.peer_recv[i]) % 16 == 0 &&
+                       sc.peer_flag[i] != nullptr,
+                   "kBf16Scatter: missing peer pointer");
+    }
+    PPLX_REQUIRE(p.error_flag != nullptr, "kBf16Scatter needs an error flag");
+  }
   PPLX_REQUIRE(reinterpret_cast<uintptr_t>(p.a) % 16 == 0 && reinterpret_cast<uintptr_t>(p.b) % 16 == 0 &&
                    p.a_stride % 16 == 0 && reinterpret_cast<uintptr_t>(p.out) % 16 == 0 && p.out_stride % 16 == 0,
                "operands must be 16-byte aligned");
@@ -578,6 +657,7 @@ void grouped_fp8_gemm(const GroupedGemmParams& p, cudaStream_t stream) {
   a.expert_padding = p.expert_padding;
   a.max_rows = p.max_rows;
   a.mode = p.mode;
+  a.scatter = p.scatter;
   a.debug_skip = p.debug_skip;
 
   int device = 0, sms = 0;

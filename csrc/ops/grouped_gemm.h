@@ -10,6 +10,25 @@ namespace pplx::ops {
 enum GroupedGemmMode : int {
   kSwiGLUQuant = 0,  // B = [gate; up]; out = e4m3(silu(gate) * up) with 1x128 fp32 scales
   kBf16 = 1,         // out = bf16(A B^T)
+  // out = bf16(A B^T), every row written straight into the combine receive buffer of the GPU
+  // its token came from (peer stores over NVLink), followed by the arrival signal that the
+  // receivers' combine_recv waits for: the down projection and the combine's send phase in one
+  // kernel, so that the transfer of a tile overlaps the math of the next ones.
+  kBf16Scatter = 2,
+};
+
+// Where the rows of a kBf16Scatter GEMM go. Filled by A2AContext::combine_scatter_begin().
+struct CombineScatter {
+  static constexpr int kMaxPeers = 8;
+  const uint32_t* row_src = nullptr;   // [max_rows] rank the row's token came from, 0xffffffff = padding row
+  const uint32_t* row_tk = nullptr;    // [max_rows] token * topk + k at that rank: the slot to write
+  uint8_t* peer_recv[kMaxPeers] = {};  // combine receive area of every rank, as mapped on this GPU
+  uint64_t slot_stride = 0;            // bytes per slot
+  uint32_t* peer_flag[kMaxPeers] = {}; // this rank's combine arrival counter at every rank
+  int world = 0;
+  uint32_t signal_value = 0;           // arrivals a receiver expects from one sender per combine
+  uint32_t* done_counter = nullptr;    // device word, zero between launches (counts finished CTAs)
+  const uint32_t* status = nullptr;    // the all-to-all's status word: non-zero = do not signal
 };
 
 struct GroupedGemmParams {
@@ -45,6 +64,7 @@ struct GroupedGemmParams {
   // bit 3: every MMA is issued twice. Timing the kernel with
   // one stage removed shows what the other stages can sustain.
   int debug_skip = 0;
+  CombineScatter scatter;          // kBf16Scatter only
 };
 
 void grouped_fp8_gemm(const GroupedGemmParams& params, cudaStream_t stream);

@@ -143,13 +143,15 @@ class LocalAllToAllGroup:
         out_tokens: Sequence[torch.Tensor],
         indices: Sequence[torch.Tensor],
         weights: Sequence[torch.Tensor],
-        expert_y: Sequence[torch.Tensor],
+        expert_y: Optional[Sequence[torch.Tensor]],
         bound_m: Optional[Sequence[Optional[torch.Tensor]]] = None,
         do_send: bool = True,
         do_recv: bool = True,
         accumulate: bool = False,
     ) -> None:
         send = recv = None
+        if expert_y is None:
+            assert do_recv and not do_send, "expert_y may only be omitted when another kernel did the send"
         if do_send:
             send = [(y.data_ptr(), y.stride(0) * y.element_size()) for y in expert_y]
         if do_recv:
@@ -161,8 +163,15 @@ class LocalAllToAllGroup:
                     indices[r].data_ptr(), indices[r].stride(0),
                     weights[r].data_ptr(), weights[r].stride(0), bm, accumulate,
                 ))
-        self.context.combine_multi(send, recv, expert_y[0].dtype,
+        self.context.combine_multi(send, recv, self.out_dtype if expert_y is None else expert_y[0].dtype,
                                    torch.cuda.current_stream().cuda_stream)
+
+    def combine_send_external(self) -> list:
+        """One scatter descriptor per emulated rank (see P2PAllToAll.combine_send_external): the
+        caller runs ``grouped_fp8_gemm(..., mode=MODE_BF16_SCATTER, scatter=desc[r])`` for every rank,
+        then ``combine(..., expert_y=None, do_send=False, do_recv=True)``. The GEMMs wait for nobody,
+        so they may run one after the other on this GPU."""
+        return list(self.context.combine_send_external())
 
     def check(self) -> None:
         if self.context.failed():

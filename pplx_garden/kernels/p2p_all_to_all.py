@@ -299,7 +299,7 @@ class P2PAllToAll(AllToAllKernel):
         out_tokens: torch.Tensor,
         indices: torch.Tensor,
         weights: torch.Tensor,
-        expert_y: torch.Tensor,
+        expert_y: Optional[torch.Tensor],
         bound_m: Optional[torch.Tensor] = None,
         do_send: bool = True,
         do_recv: bool = True,
@@ -319,9 +319,12 @@ class P2PAllToAll(AllToAllKernel):
         assert indices.dtype == torch.uint32
         assert weights.shape == (num_tokens, K) and weights.stride(1) == 1
         assert weights.dtype == torch.float32
-        assert expert_y.dim() == 2 and expert_y.shape[1] == H and expert_y.stride(1) == 1
-        assert expert_y.element_size() == self._out_dtype.itemsize, (
-            "expert_y must have the element size of out_dtype")
+        if expert_y is None:
+            assert do_recv and not do_send, "expert_y may only be omitted when another kernel did the send"
+        else:
+            assert expert_y.dim() == 2 and expert_y.shape[1] == H and expert_y.stride(1) == 1
+            assert expert_y.element_size() == self._out_dtype.itemsize, (
+                "expert_y must have the element size of out_dtype")
         if bound_m is not None:
             assert bound_m.numel() == 1 and bound_m.dtype == torch.int32
             bound_m_ptr = bound_m.data_ptr()
@@ -329,6 +332,11 @@ class P2PAllToAll(AllToAllKernel):
             bound_m_ptr = None
 
         stream = torch.cuda.current_stream().cuda_stream
+        if expert_y is None:
+            recv = (out_tokens.data_ptr(), out_tokens.stride(0), indices.data_ptr(), indices.stride(0),
+                    weights.data_ptr(), weights.stride(0), bound_m_ptr, accumulate, stream)
+            a2a.combine_recv(num_tokens, 0, self._out_dtype, *recv)
+            return
         y_ptr = expert_y.data_ptr()
         y_stride = expert_y.stride(0) * expert_y.element_size()
         recv = (out_tokens.data_ptr(), out_tokens.stride(0), indices.data_ptr(), indices.stride(0),
@@ -339,6 +347,22 @@ class P2PAllToAll(AllToAllKernel):
             a2a.combine_send(y_ptr, y_stride, stream, expert_y.dtype)
         else:
             a2a.combine_recv(num_tokens, expert_y.shape[0], expert_y.dtype, *recv)
+
+    # ------------------------------------------------------------------
+    def combine_send_external(self) -> tuple:
+        """Let another kernel play the combine's send phase. Returns the descriptor that
+        ``pplx_garden.ops.grouped_fp8_gemm(..., mode=MODE_BF16_SCATTER, scatter=...)`` takes: the
+        down projection then writes every row straight into the combine receive buffer of the
+        GPU its token came from and signals the receivers when it is done. Counts as
+        ``combine(do_send=True, do_recv=False)`` in the phase order; follow it with
+        ``combine(..., expert_y=None, do_send=False, do_recv=True)``.
+        Needs the per_route combine mode, dp_size 1 and a 2-byte out_dtype. The reference has no
+        such path (its combine always reads ``expert_y`` back:
+        p2p-all-to-all/a2a-kernels/src/a2a/a2a_combine_send.cu:20-235)."""
+        a2a = self._all_to_all
+        assert a2a is not None
+        (desc,) = a2a.combine_send_external()
+        return desc
 
     # ------------------------------------------------------------------
     def destroy(self) -> None:

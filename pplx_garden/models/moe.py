@@ -21,7 +21,7 @@ import torch
 
 from pplx_garden.distributed import ParallelGroup
 from pplx_garden.kernels.p2p_all_to_all import P2PAllToAll
-from pplx_garden.ops import MODE_BF16, MODE_SWIGLU_QUANT, grouped_fp8_gemm, quantize_128x128
+from pplx_garden.ops import MODE_BF16, MODE_BF16_SCATTER, MODE_SWIGLU_QUANT, grouped_fp8_gemm, quantize_128x128
 from pplx_garden.ops.router import topk_route, topk_route_reference
 from pplx_garden.utils.math import ceil_div
 
@@ -52,6 +52,7 @@ class ExpertParallelMoE:
         init_std: float = 0.02,
         seed: int = 0,
         combine_mode: str = "per_route",
+        fused_combine: bool = False,
     ) -> None:
         assert hidden_dim % 256 == 0 and intermediate_dim % 128 == 0
         self.hidden_dim = hidden_dim
@@ -83,6 +84,9 @@ class ExpertParallelMoE:
         self.act_scale = torch.zeros((rows, intermediate_dim // 128), dtype=torch.float32, device=dev)
         self.expert_y = torch.zeros((rows, hidden_dim), dtype=torch.bfloat16, device=dev)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        # fused_combine: the down projection writes its rows into the peers' combine buffers itself
+        self.fused_combine = fused_combine
+        assert not fused_combine or combine_mode == "per_route"
 
     def forward(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -92,14 +96,25 @@ class ExpertParallelMoE:
             out = torch.empty_like(x)
         self.a2a.dispatch(self.expert_num_tokens, self.expert_x, self.expert_x_scale, x, None, indices, weights)
         self.gate_up()
-        self.down()
-        self.a2a.combine(out, indices, weights, self.expert_y)
+        if self.fused_combine:
+            self.down_and_send()
+            self.a2a.combine(out, indices, weights, None, do_send=False, do_recv=True)
+        else:
+            self.down()
+            self.a2a.combine(out, indices, weights, self.expert_y)
         return out
 
     def gate_up(self) -> None:
         """act = quantise(silu(x W_gate^T) * (x W_up^T)) on the rows dispatch delivered."""
         grouped_fp8_gemm(self.expert_x, self.expert_x_scale, self.w13, self.w13_scale, self.expert_num_tokens,
                          self.act, self.act_scale, mode=MODE_SWIGLU_QUANT, error_flag=self.error_flag)
+
+    def down_and_send(self) -> None:
+        """The down projection and the combine's send phase in one kernel: every output row is
+        written over NVLink into the combine receive buffer of the GPU its token came from."""
+        grouped_fp8_gemm(self.act, self.act_scale, self.w2, self.w2_scale, self.expert_num_tokens, None,
+                         mode=MODE_BF16_SCATTER, error_flag=self.error_flag,
+                         scatter=self.a2a.combine_send_external())
 
     def down(self) -> None:
         """expert_y = act W_down^T in bf16: the rows combine sends home."""

@@ -2,6 +2,7 @@
 
 from pplx_garden.ops.grouped_gemm import (
     MODE_BF16 as MODE_BF16,
+    MODE_BF16_SCATTER as MODE_BF16_SCATTER,
     MODE_SWIGLU_QUANT as MODE_SWIGLU_QUANT,
     dequantize_1x128 as dequantize_1x128,
     dequantize_128x128 as dequantize_128x128,

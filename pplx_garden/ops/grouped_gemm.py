@@ -15,6 +15,7 @@ from pplx_garden import _native
 
 MODE_SWIGLU_QUANT = 0
 MODE_BF16 = 1
+MODE_BF16_SCATTER = 2
 
 
 def quantize_1x128(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
@@ -49,7 +50,7 @@ def grouped_fp8_gemm(
     b: torch.Tensor,
     b_scale: torch.Tensor,
     expert_num_tokens: torch.Tensor,
-    out: torch.Tensor,
+    out: Optional[torch.Tensor],
     out_scale: Optional[torch.Tensor] = None,
     *,
     mode: int,
@@ -59,6 +60,7 @@ def grouped_fp8_gemm(
     wait_cycles: Optional[torch.Tensor] = None,
     debug_skip: int = 0,
     trace: Optional[torch.Tensor] = None,
+    scatter: Optional[tuple] = None,
 ) -> None:
     """``out[rows of expert e] = epilogue(dequant(a rows) @ dequant(b[e]).T)``.
 
@@ -67,6 +69,9 @@ def grouped_fp8_gemm(
     (rows are expert-major, each expert's block starting at a multiple of ``expert_padding``).
     mode MODE_SWIGLU_QUANT: b = [gate; up], out [rows, N/2] e4m3 and out_scale [rows, N/256];
     mode MODE_BF16: out [rows, N] bf16.
+    mode MODE_BF16_SCATTER: no ``out``; ``scatter`` is the descriptor from
+    ``P2PAllToAll.combine_send_external()``: every bf16 row goes straight into the combine receive
+    buffer of the GPU its token came from (peer stores), and the kernel signals the receivers.
     ``wait_cycles`` (int64 [num CTAs, 4], optional) receives the cycles each pipeline role spent
     waiting: producer for a free stage, MMA for a free accumulator, MMA for operands, epilogue
     for partial sums. ``debug_skip`` (profiling only, wrong results) removes a stage: 1 the
@@ -76,7 +81,7 @@ def grouped_fp8_gemm(
     """
     assert a.dtype == torch.float8_e4m3fn and b.dtype == torch.float8_e4m3fn
     assert a.dim() == 2 and b.dim() == 3 and b.is_contiguous() and b_scale.is_contiguous()
-    assert a.stride(1) == 1 and out.stride(1) == 1
+    assert a.stride(1) == 1 and (out is None or out.stride(1) == 1)
     rows, k = a.shape
     e, n, kb = b.shape
     assert kb == k and a_scale.shape == (rows, k // 128) and b_scale.shape == (e, n // 128, k // 128)
@@ -86,15 +91,17 @@ def grouped_fp8_gemm(
         assert out.dtype == torch.float8_e4m3fn and out.shape == (rows, n // 2)
         assert out_scale is not None and out_scale.shape == (rows, n // 256) and out_scale.dtype == torch.float32
         assert out_scale.stride(1) == 1
+    elif mode == MODE_BF16_SCATTER:
+        assert out is None and scatter is not None
     else:
         assert out.dtype == torch.bfloat16 and out.shape == (rows, n)
     if error_flag is None:
         error_flag = torch.zeros(1, dtype=torch.int32, device=a.device)
     _native.grouped_fp8_gemm(
         a.data_ptr(), a.stride(0) * a.element_size(), a_scale.data_ptr(), a_scale.stride(0), a_scale.stride(1),
-        b.data_ptr(), b_scale.data_ptr(), expert_num_tokens.data_ptr(), out.data_ptr(),
-        out.stride(0) * out.element_size(), 0 if out_scale is None else out_scale.data_ptr(),
+        b.data_ptr(), b_scale.data_ptr(), expert_num_tokens.data_ptr(), a.data_ptr() if out is None else out.data_ptr(),
+        16 if out is None else out.stride(0) * out.element_size(), 0 if out_scale is None else out_scale.data_ptr(),
         0 if out_scale is None else out_scale.stride(0), error_flag.data_ptr(), e, n, k, expert_padding, rows, mode,
         num_ctas, torch.cuda.current_stream().cuda_stream,
         0 if wait_cycles is None else wait_cycles.data_ptr(), debug_skip,
-        0 if trace is None else trace.data_ptr())
+        0 if trace is None else trace.data_ptr(), scatter)
