@@ -44,14 +44,14 @@ namespace {
 using namespace pplx::tc;
 
 constexpr int kBM = 128, kBN = 256, kBK = 128;   // per CTA; a CTA pair computes 256 x 256
-constexpr int kStages = 6;
+constexpr int kStages = 5;
 constexpr int kThreads = 384;
 constexpr int kFirstEpilogueWarp = 4;
 constexpr int kEpilogueThreads = 256;
 constexpr uint32_t kABytes = kBM * kBK;        // 16 KiB
 constexpr uint32_t kBBoxBytes = 64 * kBK;      // 8 KiB; a CTA holds two boxes: its half of the tile's B rows
 constexpr uint32_t kStageBytes = kABytes + 2 * kBBoxBytes;  // 32 KiB per CTA
-constexpr uint32_t kWarpStageBytes = 32 * 64;   // per epilogue warp, for coalesced output stores
+constexpr uint32_t kWarpStageBytes = 32 * 128;   // per epilogue warp, for coalesced output stores
 constexpr uint32_t kTmemCols = 512;
 // Register split between the first warpgroup (copies, MMA issue) and the epilogue warps. The
 // pool is what the CTA was launched with, 168 registers for each of its 384 threads, not the
@@ -136,29 +136,33 @@ __device__ __forceinline__ void store_rows_64B(uint8_t* stage, int lane, const u
   __syncwarp();
 }
 
-// The same transposition, with every row going to an address of its own (`row_ptr`, held by the
-// lane that owns the row; null = nowhere): rows of the down projection written straight into the
-// combine receive buffers of the GPUs their tokens came from. Streaming stores: the data is not
-// read again on this GPU.
-__device__ __forceinline__ void scatter_rows_64B(uint8_t* stage, int lane, const uint32_t (&w)[16], uint8_t* row_ptr,
-                                                 uint32_t col_bytes) {
+// 128 bytes per row (64 bf16 columns): one store instruction then covers 4 rows x one full
+// 128-byte line, which is what both the L2 and NVLink move best. `row_base(r)` gives the address
+// of row r's chunk or null. Units of 16 bytes are XOR-swizzled with the row index (conflict-free
+// on both sides: a quarter warp writes one unit of 8 rows, and reads the 8 units of one row).
+template <typename RowBase>
+__device__ __forceinline__ void store_rows_128B(uint8_t* stage, int lane, const uint32_t (&w)[32], bool streaming,
+                                                RowBase row_base) {
   #pragma unroll
-  for (int u = 0; u < 4; ++u) {
-    const int pu = u ^ ((lane >> 1) & 3);
-    *reinterpret_cast<uint4*>(stage + lane * 64 + pu * 16) = make_uint4(w[4 * u], w[4 * u + 1], w[4 * u + 2], w[4 * u + 3]);
+  for (int u = 0; u < 8; ++u) {
+    const int pu = u ^ (lane & 7);
+    *reinterpret_cast<uint4*>(stage + lane * 128 + pu * 16) = make_uint4(w[4 * u], w[4 * u + 1], w[4 * u + 2], w[4 * u + 3]);
   }
   __syncwarp();
-  const unsigned long long mine = reinterpret_cast<unsigned long long>(row_ptr);
   #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int r = 8 * i + (lane >> 2);
-    const int u = lane & 3;
-    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 + ((u ^ ((r >> 1) & 3)) * 16));
-    uint8_t* const base = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, mine, r));
+  for (int i = 0; i < 8; ++i) {
+    const int r = 4 * i + (lane >> 3);
+    const int u = lane & 7;
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 128 + ((u ^ (r & 7)) * 16));
+    uint8_t* const base = row_base(r);
     if (base != nullptr) {
-      Vec16 out;
-      out.x = v.x; out.y = v.y; out.z = v.z; out.w = v.w;
-      st_stream_v4(base + col_bytes + u * 16, out);
+      if (streaming) {
+        Vec16 out;
+        out.x = v.x; out.y = v.y; out.z = v.z; out.w = v.w;
+        st_stream_v4(base + u * 16, out);
+      } else {
+        *reinterpret_cast<uint4*>(base + u * 16) = v;
+      }
     }
   }
   __syncwarp();
@@ -529,27 +533,33 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           }
         }
         const uint32_t col0 = static_cast<uint32_t>(n_tile * kBN + h * 128) * 2u;
+        const unsigned long long mine = reinterpret_cast<unsigned long long>(row_ptr);
         #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t w[16];
+        for (int c = 0; c < 2; ++c) {
+          uint32_t w[32];
           #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[c * 32 + 2 * j], acc[c * 32 + 2 * j + 1]);
+          for (int j = 0; j < 32; ++j) {
+            const __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[c * 64 + 2 * j], acc[c * 64 + 2 * j + 1]);
             w[j] = *reinterpret_cast<const uint32_t*>(&p2);
           }
-          scatter_rows_64B(warp_stage, lane, w, row_ptr, col0 + c * 64);
+          store_rows_128B(warp_stage, lane, w, true, [&](int r) {
+            uint8_t* const base = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, mine, r));
+            return base == nullptr ? base : base + col0 + c * 128;
+          });
         }
       } else {
         uint8_t* dst = a.out + warp_row0 * a.out_stride + (static_cast<int64_t>(n_tile) * kBN + h * 128) * 2;
         #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t w[16];
+        for (int c = 0; c < 2; ++c) {
+          uint32_t w[32];
           #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[c * 32 + 2 * j], acc[c * 32 + 2 * j + 1]);
+          for (int j = 0; j < 32; ++j) {
+            const __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[c * 64 + 2 * j], acc[c * 64 + 2 * j + 1]);
             w[j] = *reinterpret_cast<const uint32_t*>(&p2);
           }
-          store_rows_64B(warp_stage, lane, w, dst + c * 64, a.out_stride, valid_mask);
+          store_rows_128B(warp_stage, lane, w, false, [&](int r) {
+            return ((valid_mask >> r) & 1u) ? dst + r * a.out_stride + c * 128 : static_cast<uint8_t*>(nullptr);
+          });
         }
       }
       if (trace_row >= 0) a.trace[trace_row * 8 + 3] = clock64();
