@@ -63,7 +63,7 @@ constexpr int kEpilogueRegs = 224;
 static_assert(kFirstEpilogueWarp * 32 * kLightRegs + kEpilogueThreads * kEpilogueRegs <= kThreads * kLaunchRegs,
               "the epilogue's setmaxnreg.inc could never be granted");
 static_assert(kLightRegs % 8 == 0 && kEpilogueRegs % 8 == 0, "setmaxnreg takes multiples of 8");
-constexpr int kMaxExperts = 64;
+constexpr int kMaxExperts = 128;
 constexpr int kTraceTiles = 64;
 // Rows 32..61 of the trace hold stamps for CTA 0's first K blocks, one row each: MMA committed,
 // epilogue saw the partial sums, epilogue released the accumulator, MMA got the accumulator,
@@ -205,19 +205,54 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_failed = 0;
-    // expert-major row layout (each expert's block starts at a multiple of the padding)
-    int row = 0, tiles = 0;
-    for (int e = 0; e < a.num_experts; ++e) {
-      const int n = max(a.expert_num_tokens[e], 0);
-      sched.row_start[e] = row;
-      sched.count[e] = n;
-      sched.tile_prefix[e] = tiles;
-      tiles += (n + 2 * kBM - 1) / (2 * kBM) * n_tiles;   // one tile = 256 rows: 128 per CTA of the pair
-      row += (n + a.expert_padding - 1) / a.expert_padding * a.expert_padding;
-    }
-    sched.tile_prefix[a.num_experts] = tiles;
     prefetch_tensormap(&a.map_a);
     prefetch_tensormap(&a.map_b);
+  }
+  if (warp == 0) {
+    // Expert-major row layout (each expert's block starts at a multiple of the padding) and the
+    // tile count before each expert. The counts live in global memory: the lanes fetch four
+    // experts each at once and combine with a warp scan, instead of one thread walking through
+    // up to 128 dependent cache misses in front of every launch.
+    constexpr int kPerLane = kMaxExperts / 32;
+    int n[kPerLane], rows_of[kPerLane], tiles_of[kPerLane];
+    int my_rows = 0, my_tiles = 0;
+    #pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      const int e = lane * kPerLane + j;
+      n[j] = e < a.num_experts ? max(a.expert_num_tokens[e], 0) : 0;
+    }
+    #pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      rows_of[j] = (n[j] + a.expert_padding - 1) / a.expert_padding * a.expert_padding;
+      tiles_of[j] = (n[j] + 2 * kBM - 1) / (2 * kBM) * n_tiles;   // one tile = 256 rows: 128 per CTA of the pair
+      my_rows += rows_of[j];
+      my_tiles += tiles_of[j];
+    }
+    int row = my_rows, tiles = my_tiles;   // inclusive scan over the lanes
+    #pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int r_up = __shfl_up_sync(0xffffffffu, row, off);
+      const int t_up = __shfl_up_sync(0xffffffffu, tiles, off);
+      if (lane >= off) {
+        row += r_up;
+        tiles += t_up;
+      }
+    }
+    const int total_tiles_all = __shfl_sync(0xffffffffu, tiles, 31);
+    row -= my_rows;      // exclusive
+    tiles -= my_tiles;
+    #pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+      const int e = lane * kPerLane + j;
+      if (e < a.num_experts) {
+        sched.row_start[e] = row;
+        sched.count[e] = n[j];
+        sched.tile_prefix[e] = tiles;
+      }
+      row += rows_of[j];
+      tiles += tiles_of[j];
+    }
+    if (lane == 0) sched.tile_prefix[a.num_experts] = total_tiles_all;
   }
   if (warp == 1) {
     tmem_alloc_pair(&tmem_base_slot, kTmemCols);
@@ -619,7 +654,7 @@ CUtensorMap make_map(const void* base, uint64_t rows, uint64_t cols_bytes, uint6
 
 void grouped_fp8_gemm(const GroupedGemmParams& p, cudaStream_t stream) {
   PPLX_REQUIRE(p.K % kBK == 0 && p.K >= kBK, "K must be a multiple of 128");
-  PPLX_REQUIRE(p.num_experts >= 1 && p.num_experts <= kMaxExperts, "between 1 and 64 local experts");
+  PPLX_REQUIRE(p.num_experts >= 1 && p.num_experts <= kMaxExperts, "between 1 and 128 local experts");
   PPLX_REQUIRE(p.expert_padding >= 1, "expert_padding must be positive");
   if (p.mode == kSwiGLUQuant) {
     PPLX_REQUIRE(p.N % 256 == 0, "SwiGLU needs N = 2 * intermediate with intermediate a multiple of 128");

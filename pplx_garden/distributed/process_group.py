@@ -206,13 +206,15 @@ def _child_main(local_rank: int, config: ParallelLaunch, init_method: str, devic
         dp_group = global_group.slice_by_lens(config.dp_lens)
     try:
         result = worker(device, dp_group, global_group, *args)
-        with open(Path(tmpdir) / f"result_{local_rank}.pkl", "wb") as f:
-            pickle.dump(result, f)
-    except Exception:
+    except BaseException:
+        # No collective teardown on this path: the peers are not at the matching barrier, and
+        # waiting for them would turn one rank's failure into a hang of the whole launch. The
+        # launcher ends the other ranks as soon as this process has exited with an error.
         logger.exception("[rank=%d] worker failed", global_rank)
         raise
-    finally:
-        if dp_group is not global_group:
-            dp_group.destroy()
-        global_group.destroy()
-        world.destroy()
+    with open(Path(tmpdir) / f"result_{local_rank}.pkl", "wb") as f:
+        pickle.dump(result, f)
+    if dp_group is not global_group:
+        dp_group.destroy()
+    global_group.destroy()
+    world.destroy()

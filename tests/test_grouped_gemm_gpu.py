@@ -55,6 +55,8 @@ def _make(counts, K, N, padding, seed=0, unit_scales=False):
     ([200, 0, 37, 128], 1024, 512, 1, False),
     ([5, 300, 64], 2048, 768, 16, False),
     ([1024] * 4, 768, 2048, 1, False),
+    ([(7 * i) % 40 for i in range(100)], 256, 256, 1, False),   # many small experts, several per lane of the scan
+    ([3] * 128, 128, 256, 4, False),
 ])
 def test_bf16_epilogue(counts, K, N, padding, unit) -> None:
     aq, a_s, bq, b_s, cnt, starts, rows = _make(counts, K, N, padding, unit_scales=unit)
