@@ -5,7 +5,8 @@ Generates a ninja file for every C++/CUDA source under ``csrc/`` and links
 
 * ``pplx_garden/_native.<abi>.so``   the Python extension (pybind11),
 * ``pplx_garden/libpplx_noalloc.so`` plain C entry points (when their source exists),
-* ``bin/pplx-fabric-debug`` and ``bin/pplx-unigram-encode`` command line tools
+* ``bin/pplx-fabric-debug`` and ``bin/pplx-unigram-encode`` command line tools, and
+  ``bin/pplx-core-tests``, the native unit tests
   (when their sources exist).
 
 CUDA is compiled for sm_100a only (``-gencode arch=compute_100a,code=sm_100a``); nvcc
@@ -53,7 +54,7 @@ def _cutlass_include() -> str | None:
 
 
 def _sources() -> dict[str, list[Path]]:
-    groups: dict[str, list[Path]] = {"ext": [], "noalloc": [], "fabric_debug": [], "unigram_cli": []}
+    groups: dict[str, list[Path]] = {"ext": [], "noalloc": [], "fabric_debug": [], "unigram_cli": [], "core_tests": []}
     for path in sorted(CSRC.rglob("*")):
         if path.suffix not in (".cpp", ".cu"):
             continue
@@ -65,6 +66,8 @@ def _sources() -> dict[str, list[Path]]:
                 groups["fabric_debug"].append(path)
             elif path.stem == "unigram_encode":
                 groups["unigram_cli"].append(path)
+            elif path.stem == "core_tests":
+                groups["core_tests"].append(path)
         else:
             groups["ext"].append(path)
     return groups
@@ -151,7 +154,8 @@ def write_ninja(verbose: bool) -> Path:
         out = Path("pplx_garden") / "libpplx_noalloc.so"
         lines.append(f"build {out}: link_shared {' '.join(objs)}")
         targets.append(str(out))
-    for key, name in (("fabric_debug", "pplx-fabric-debug"), ("unigram_cli", "pplx-unigram-encode")):
+    for key, name in (("fabric_debug", "pplx-fabric-debug"), ("unigram_cli", "pplx-unigram-encode"),
+                      ("core_tests", "pplx-core-tests")):
         if groups[key]:
             objs = compile_group(groups[key], key)
             out = Path("bin") / name

@@ -127,3 +127,17 @@ def test_fd_fetch_inside_one_process_duplicates():
     assert got != r and os.read(got, 1) == b"x"
     for f in (r, w, got):
         os.close(f)
+
+
+def test_native_unit_tests_pass():
+    """bin/pplx-core-tests: error type, scope guard, object and memory pools, imm counters,
+    sharding arithmetic, host buffer reuse, address and CPU-list helpers, JSON numbers."""
+    import subprocess
+    from pathlib import Path
+
+    exe = Path(__file__).resolve().parent.parent / "bin" / "pplx-core-tests"
+    if not exe.exists():
+        pytest.skip("run python build.py first")
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "0 failed" in res.stdout
