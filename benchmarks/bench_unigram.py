@@ -51,11 +51,13 @@ def main() -> None:
             times.append(time.perf_counter() - t)
         return min(times)
 
-    ours_1 = total_mb / best(lambda: engine.encode_batch(docs, 1))
-    ours_n = total_mb / best(lambda: engine.encode_batch(docs, args.threads))
+    ours_1 = total_mb / best(lambda: engine.encode_batch_flat(docs, 1))
+    ours_n = total_mb / best(lambda: engine.encode_batch_flat(docs, args.threads))
+    lists_n = total_mb / best(lambda: engine.encode_batch(docs, args.threads))
     result = {
         "corpus_mb": total_mb, "docs": len(docs), "vocab": len(vocab), "load_s": load_s,
         "ours_mb_s_1_thread": ours_1, f"ours_mb_s_{args.threads}_threads": ours_n,
+        f"ours_mb_s_{args.threads}_threads_python_lists": lists_n,
     }
     try:
         import tokenizers

@@ -2,6 +2,7 @@
 // crate without a Python binding (python-ext/Cargo.toml:9-15); exposing it here lets the
 // differential tests against HuggingFace `tokenizers` run from pytest.
 #include <pybind11/pybind11.h>
+#include <pybind11/numpy.h>
 #include <pybind11/stl.h>
 
 #include "../unigram/engine.h"
@@ -83,6 +84,36 @@ void bind_unigram(py::module_& m) {
              return out;
            },
            py::arg("texts"), py::arg("num_threads") = 0)
+      .def("encode_batch_flat",
+           [](PyEngine& s, const std::vector<std::string>& texts, int num_threads) {
+             for (const std::string& t : texts) {
+               if (!pplx::unicode::is_valid_utf8(t)) throw py::value_error("text is not valid UTF-8");
+             }
+             std::vector<std::string_view> views(texts.begin(), texts.end());
+             std::vector<std::vector<TokenId>> out;
+             {
+               py::gil_scoped_release release;
+               try {
+                 out = s.engine->encode_batch(views, num_threads);
+               } catch (const UnigramError& e) {
+                 py::gil_scoped_acquire acquire;
+                 rethrow(e);
+               }
+             }
+             // two arrays instead of millions of Python integers
+             py::array_t<int64_t> offsets(static_cast<py::ssize_t>(out.size() + 1));
+             int64_t* off = offsets.mutable_data();
+             off[0] = 0;
+             for (size_t i = 0; i < out.size(); ++i) off[i + 1] = off[i] + static_cast<int64_t>(out[i].size());
+             py::array_t<int32_t> ids(static_cast<py::ssize_t>(off[out.size()]));
+             int32_t* dst = ids.mutable_data();
+             for (size_t i = 0; i < out.size(); ++i) {
+               for (size_t j = 0; j < out[i].size(); ++j) dst[off[i] + static_cast<int64_t>(j)] = static_cast<int32_t>(out[i][j]);
+             }
+             return py::make_tuple(ids, offsets);
+           },
+           py::arg("texts"), py::arg("num_threads") = 0,
+           "encode_batch with the result as (ids int32 [total], offsets int64 [len(texts) + 1]).")
       .def("normalize",
            [](PyEngine& s, const std::string& text) {
              std::string out;

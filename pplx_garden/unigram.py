@@ -46,5 +46,11 @@ class Engine:
         The GIL is released while the worker threads run."""
         return self._native.encode_batch(list(texts), num_threads)
 
+    def encode_batch_flat(self, texts: Sequence[str], num_threads: int = 0):
+        """Like ``encode_batch`` but returns ``(ids, offsets)`` as numpy arrays (int32 [total tokens],
+        int64 [len(texts) + 1]; text i is ``ids[offsets[i]:offsets[i + 1]]``): no Python integer per
+        token, which is what bounds ``encode_batch`` on large batches."""
+        return self._native.encode_batch_flat(list(texts), num_threads)
+
     def normalize(self, text: str) -> str:
         return self._native.normalize(text)

@@ -166,3 +166,13 @@ def test_number_literals_convert_like_serde_json() -> None:
     assert got["a"] == 1.0 and got["b"] == -0.5 and got["c"] == 1000.0 and got["f"] == 0.0025
     assert got["d"] == -(float(12143931267304547) / 1e15)
     assert got["e"] == pytest.approx(1.2345678901234568e22, rel=1e-15)
+
+
+def test_flat_batch_equals_list_batch(pair) -> None:
+    engine, _ = pair
+    texts = ["hello world", "", "a  b   c", "ünïcödé ▁ text", "x" * 300]
+    ids, offsets = engine.encode_batch_flat(texts, 2)
+    lists = engine.encode_batch(texts, 2)
+    assert offsets.tolist() == [0] + [sum(len(l) for l in lists[:i + 1]) for i in range(len(lists))]
+    for i, want in enumerate(lists):
+        assert ids[offsets[i]:offsets[i + 1]].tolist() == want
