@@ -75,7 +75,7 @@ def grouped_fp8_gemm(
     ``wait_cycles`` (int64 [num CTAs, 4], optional) receives the cycles each pipeline role spent
     waiting: producer for a free stage, MMA for a free accumulator, MMA for operands, epilogue
     for partial sums. ``debug_skip`` (profiling only, wrong results) removes a stage: 1 the
-    epilogue's reads, 2 the MMAs, 4 the TMA loads. ``trace`` (int64 [64, 8], optional) receives SM clock
+    epilogue's reads, 2 the MMAs, 4 the TMA loads; 8 issues every MMA twice. ``trace`` (int64 [64, 8], optional) receives SM clock
     readings for the tiles of CTA 0: epilogue tile start / first partial sums / K loop done / stored,
     MMA first issue / last commit, producer first / last load.
     """
