@@ -473,7 +473,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         // thread columns [0,64) belong to block row nb0 and [64,128) to nb1 (gate / up under
         // SwiGLU; the same block row twice otherwise)
         const float sc0 = as * b0, sc1 = as * b1;
-        // the verdict must be the same for the whole warp: tcgen05.ld below is warp-collective
+        // the outcome must be the same for the whole warp: tcgen05.ld below is warp-collective
         const long long w0 = clock64();
         const bool got = mbar_wait_timed(&tmem_full_bar[buf], (acc_it >> 1) & 1u, kWaitNs);
         waited_acc += clock64() - w0;
@@ -540,7 +540,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         }
         s_amax[tile_parity][row_in_tile][h] = amax;
         // Every epilogue thread gets here, also after a failed wait, and all of them leave with
-        // the same verdict: a warp that went on alone would wait at this barrier for ever.
+        // the same outcome: a warp that went on alone would wait at this barrier for ever.
         const bool any_failed = bar_red_or(1, kEpilogueThreads, failed || s_failed != 0);
         amax = fmaxf(s_amax[tile_parity][row_in_tile][0], s_amax[tile_parity][row_in_tile][1]);
         const float scale = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
