@@ -52,6 +52,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-library", action="store_true")
     ap.add_argument("--no-fused", action="store_true", help="skip the arm whose down projection sends the rows itself")
+    ap.add_argument("--bulk", action="store_true", help="also time the fused arm with bulk copies (cp.async.bulk) as the sender")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -126,7 +127,7 @@ def main() -> None:
     ours_out = out.float().clone()
 
     # the same layer with the down projection writing its rows into the peers' combine buffers
-    fused = None
+    fused = fused_bulk = None
     if not args.no_fused:
         def f_down_send() -> None:
             layer.down_and_send()
@@ -138,6 +139,15 @@ def main() -> None:
                               ("down_and_combine_send", f_down_send), ("combine_recv", f_recv)])
         layer.check()
         fused["equal_to_unfused"] = bool(torch.equal(out.float(), ours_out))
+
+        # ... and with the rows handed to the bulk-copy engine instead of stored by the epilogue warps
+        if args.bulk:
+            layer.fused_bulk = True
+            fused_bulk = timed_phases([("route", o_route), ("dispatch", o_dispatch), ("gate_up_swiglu", o_gemm1),
+                                       ("down_and_combine_send", f_down_send), ("combine_recv", f_recv)])
+            layer.check()
+            fused_bulk["equal_to_unfused"] = bool(torch.equal(out.float(), ours_out))
+            layer.fused_bulk = False
     rows = int(layer.expert_num_tokens.sum().item())
     flops = 2.0 * rows * (2 * I * H + H * I)
     ours["expert_rows_this_rank"] = rows
@@ -190,7 +200,7 @@ def main() -> None:
                        "experts": E, "topk": K, "n_gpus": world, "l2": "flushed before each layer",
                        "steps": args.steps, "warmup": args.warmup},
             "unit": "us, max over ranks",
-            "ours": ours, "ours_fused_combine": fused, "library": lib, "max_rel_err_ours_vs_library": max_err,
+            "ours": ours, "ours_fused_combine": fused, "ours_fused_combine_bulk": fused_bulk, "library": lib, "max_rel_err_ours_vs_library": max_err,
             "speedup_layer": None if lib is None else lib["layer"] / ours["layer"],
             "speedup_layer_fused": None if lib is None or fused is None else lib["layer"] / fused["layer"],
         }))

@@ -68,7 +68,8 @@ void bind_ops(py::module_& m) {
         if (!scatter.is_none()) {
           // the tuple AllToAllContext.combine_send_external() returns for this rank
           const py::tuple t = scatter.cast<py::tuple>();
-          PPLX_REQUIRE(t.size() == 9, "scatter descriptor needs 9 entries");
+          PPLX_REQUIRE(t.size() == 9 || t.size() == 10, "scatter descriptor needs 9 entries (+ optional bulk flag)");
+          if (t.size() == 10) p.scatter.bulk = t[9].cast<int>();
           CombineScatter& sc = p.scatter;
           sc.row_src = reinterpret_cast<const uint32_t*>(t[0].cast<uint64_t>());
           sc.row_tk = reinterpret_cast<const uint32_t*>(t[1].cast<uint64_t>());

@@ -51,7 +51,8 @@ constexpr int kEpilogueThreads = 256;
 constexpr uint32_t kABytes = kBM * kBK;        // 16 KiB
 constexpr uint32_t kBBoxBytes = 64 * kBK;      // 8 KiB; a CTA holds two boxes: its half of the tile's B rows
 constexpr uint32_t kStageBytes = kABytes + 2 * kBBoxBytes;  // 32 KiB per CTA
-constexpr uint32_t kWarpStageBytes = 32 * 128;   // per epilogue warp, for coalesced output stores
+constexpr uint32_t kBulkRowStride = 144;          // staged rows for bulk copies: 128 B + 16 B against bank conflicts
+constexpr uint32_t kWarpStageBytes = 32 * kBulkRowStride;   // per epilogue warp, for coalesced output stores
 constexpr uint32_t kTmemCols = 512;
 // Register split between the first warpgroup (copies, MMA issue) and the epilogue warps. The
 // pool is what the CTA was launched with, 168 registers for each of its 384 threads, not the
@@ -577,10 +578,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             const __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[c * 64 + 2 * j], acc[c * 64 + 2 * j + 1]);
             w[j] = *reinterpret_cast<const uint32_t*>(&p2);
           }
-          store_rows_128B(warp_stage, lane, w, true, [&](int r) {
-            uint8_t* const base = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, mine, r));
-            return base == nullptr ? base : base + col0 + c * 128;
-          });
+          if (a.scatter.bulk) {
+            // Each lane stages its own row's 128 bytes and hands them to the bulk-copy engine; the
+            // warp goes on while the bytes cross NVLink. The staging buffer is reused as soon as the
+            // engine has read it (wait_group.read), not when the peer has the data.
+            bulk_wait_read0();
+            __syncwarp();
+            #pragma unroll
+            for (int u = 0; u < 8; ++u) {
+              *reinterpret_cast<uint4*>(warp_stage + lane * kBulkRowStride + u * 16) =
+                  make_uint4(w[4 * u], w[4 * u + 1], w[4 * u + 2], w[4 * u + 3]);
+            }
+            fence_proxy_async_smem();
+            if (row_ptr != nullptr) bulk_s2g(row_ptr + col0 + c * 128, warp_stage + lane * kBulkRowStride, 128);
+            bulk_commit();
+          } else {
+            store_rows_128B(warp_stage, lane, w, true, [&](int r) {
+              uint8_t* const base = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, mine, r));
+              return base == nullptr ? base : base + col0 + c * 128;
+            });
+          }
         }
       } else {
         uint8_t* dst = a.out + warp_row0 * a.out_stride + (static_cast<int64_t>(n_tile) * kBN + h * 128) * 2;
@@ -603,6 +620,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     if (a.wait_cycles != nullptr && warp == kFirstEpilogueWarp && lane == 0) {
       a.wait_cycles[blockIdx.x * 4 + 3] = static_cast<unsigned long long>(waited_acc);
     }
+    // bulk copies this thread handed over must have been performed before the arrival signal
+    if (a.mode == kBf16Scatter && a.scatter.bulk) bulk_wait0();
   }
 
   // Neither CTA may leave, or give its tensor memory back, while the other can still signal its

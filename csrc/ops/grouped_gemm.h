@@ -29,6 +29,9 @@ struct CombineScatter {
   uint32_t signal_value = 0;           // arrivals a receiver expects from one sender per combine
   uint32_t* done_counter = nullptr;    // device word, zero between launches (counts finished CTAs)
   const uint32_t* status = nullptr;    // the all-to-all's status word: non-zero = do not signal
+  // 0: the epilogue warps store the rows themselves; 1: they hand each row chunk to the bulk-copy
+  // engine (cp.async.bulk shared -> peer global), so that NVLink back-pressure does not hold them up
+  int bulk = 0;
 };
 
 struct GroupedGemmParams {

@@ -166,12 +166,12 @@ class LocalAllToAllGroup:
         self.context.combine_multi(send, recv, self.out_dtype if expert_y is None else expert_y[0].dtype,
                                    torch.cuda.current_stream().cuda_stream)
 
-    def combine_send_external(self) -> list:
+    def combine_send_external(self, bulk: bool = False) -> list:
         """One scatter descriptor per emulated rank (see P2PAllToAll.combine_send_external): the
         caller runs ``grouped_fp8_gemm(..., mode=MODE_BF16_SCATTER, scatter=desc[r])`` for every rank,
         then ``combine(..., expert_y=None, do_send=False, do_recv=True)``. The GEMMs wait for nobody,
         so they may run one after the other on this GPU."""
-        return list(self.context.combine_send_external())
+        return [(*d, 1) if bulk else d for d in self.context.combine_send_external()]
 
     def check(self) -> None:
         if self.context.failed():

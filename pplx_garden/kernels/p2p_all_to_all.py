@@ -349,7 +349,7 @@ class P2PAllToAll(AllToAllKernel):
             a2a.combine_recv(num_tokens, expert_y.shape[0], expert_y.dtype, *recv)
 
     # ------------------------------------------------------------------
-    def combine_send_external(self) -> tuple:
+    def combine_send_external(self, bulk: bool = False) -> tuple:
         """Let another kernel play the combine's send phase. Returns the descriptor that
         ``pplx_garden.ops.grouped_fp8_gemm(..., mode=MODE_BF16_SCATTER, scatter=...)`` takes: the
         down projection then writes every row straight into the combine receive buffer of the
@@ -362,7 +362,8 @@ class P2PAllToAll(AllToAllKernel):
         a2a = self._all_to_all
         assert a2a is not None
         (desc,) = a2a.combine_send_external()
-        return desc
+        # bulk: the GEMM hands row chunks to the bulk-copy engine instead of storing them itself
+        return (*desc, 1) if bulk else desc
 
     # ------------------------------------------------------------------
     def destroy(self) -> None:

@@ -53,6 +53,7 @@ class ExpertParallelMoE:
         seed: int = 0,
         combine_mode: str = "per_route",
         fused_combine: bool = False,
+        fused_bulk: bool = False,
     ) -> None:
         assert hidden_dim % 256 == 0 and intermediate_dim % 128 == 0
         self.hidden_dim = hidden_dim
@@ -86,6 +87,7 @@ class ExpertParallelMoE:
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=dev)
         # fused_combine: the down projection writes its rows into the peers' combine buffers itself
         self.fused_combine = fused_combine
+        self.fused_bulk = fused_bulk   # fused_combine through the bulk-copy engine
         assert not fused_combine or combine_mode == "per_route"
 
     def forward(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
@@ -114,7 +116,7 @@ class ExpertParallelMoE:
         written over NVLink into the combine receive buffer of the GPU its token came from."""
         grouped_fp8_gemm(self.act, self.act_scale, self.w2, self.w2_scale, self.expert_num_tokens, None,
                          mode=MODE_BF16_SCATTER, error_flag=self.error_flag,
-                         scatter=self.a2a.combine_send_external())
+                         scatter=self.a2a.combine_send_external(self.fused_bulk))
 
     def down(self) -> None:
         """expert_y = act W_down^T in bf16: the rows combine sends home."""

@@ -67,10 +67,10 @@ def test_fused_combine_equals_unfused_on_one_gpu() -> None:
     x = torch.randn((T, H), generator=gen).to(torch.bfloat16).to(dev)
     indices, weights = route_topk(torch.randn((T, E), generator=gen).to(dev), K)
     outs = []
-    for fused in (False, True):
+    for fused, bulk in ((False, False), (True, False), (True, True)):
         layer = ExpertParallelMoE(hidden_dim=H, intermediate_dim=I, num_experts=E, num_experts_per_token=K,
                                   max_num_tokens=T, device=dev, global_group=None, w13=w13, w2=w2,
-                                  fused_combine=fused)
+                                  fused_combine=fused, fused_bulk=bulk)
         try:
             for _ in range(3):   # several layers in a row: epochs, the done counter's reset
                 out = layer(x, indices, weights)
@@ -80,6 +80,7 @@ def test_fused_combine_equals_unfused_on_one_gpu() -> None:
         finally:
             layer.destroy()
     assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0], outs[2])
 
 
 def test_fused_combine_with_four_emulated_ranks() -> None:
@@ -110,14 +111,14 @@ def test_fused_combine_with_four_emulated_ranks() -> None:
         act_s = [torch.zeros((rows, I // 128), dtype=torch.float32, device=dev) for _ in range(world)]
         flag = torch.zeros(1, dtype=torch.int32, device=dev)
         results = []
-        for fused in (False, True):
+        for fused, bulk in ((False, False), (True, False), (True, True)):
             out = [torch.zeros((T, H), dtype=torch.bfloat16, device=dev) for _ in range(world)]
             group.dispatch(num, ox, osc, xs, None, idx, wts)
             for r in range(world):
                 grouped_fp8_gemm(ox[r], osc[r], q13[r][0], q13[r][1], num[r], act[r], act_s[r],
                                  mode=MODE_SWIGLU_QUANT, error_flag=flag)
             if fused:
-                descs = group.combine_send_external()
+                descs = group.combine_send_external(bulk)
                 for r in range(world):
                     grouped_fp8_gemm(act[r], act_s[r], q2[r][0], q2[r][1], num[r], None, mode=MODE_BF16_SCATTER,
                                      error_flag=flag, scatter=descs[r])
@@ -135,6 +136,7 @@ def test_fused_combine_with_four_emulated_ranks() -> None:
         for r in range(world):
             assert results[0][r].abs().max() > 0
             assert torch.equal(results[0][r], results[1][r]), f"rank {r}"
+            assert torch.equal(results[0][r], results[2][r]), f"rank {r} (bulk copies)"
     finally:
         group.destroy()
 
