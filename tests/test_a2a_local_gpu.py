@@ -291,3 +291,49 @@ def test_wait_timeout_reports_status_without_hanging() -> None:
         assert torch.ones(8, device=device).sum().item() == 8
     finally:
         group.destroy()
+
+
+def test_cuda_graph_replay_of_a_whole_layer() -> None:
+    """dispatch -> expert -> combine captured once in a CUDA graph and replayed with new tokens and
+    routing each time: the protocol keeps its epochs on the device, so a replay is a layer like any
+    other (this is how a serving loop would launch it)."""
+    cfg = Cfg(world=4, tokens=32, experts=16, hidden=256, topk=4, in_dtype=torch.bfloat16,
+              out_dtype=torch.bfloat16)
+    device = torch.device("cuda", 0)
+    group = _make_group(cfg, device)
+    try:
+        W = cfg.world
+        num, ox, os_, out = _outputs(cfg, group, device)
+        data = _inputs(cfg, device)
+        xs = [d.dp_x.clone() for d in data]
+        idx = [d.indices.clone() for d in data]
+        wts = [d.weights.clone() for d in data]
+        ys = [torch.zeros((group.max_recv_rows, cfg.hidden), dtype=cfg.out_dtype, device=device) for _ in range(W)]
+
+        def layer() -> None:
+            group.dispatch(num, ox, None, xs, None, idx, wts)
+            for r in range(W):
+                ys[r].copy_(act(ox[r], None).to(cfg.out_dtype))
+            group.combine(out, idx, wts, ys)
+
+        layer()   # eager once: everything that allocates or loads modules happens here
+        torch.cuda.synchronize()
+        stream = torch.cuda.Stream(device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(graph, stream=stream):
+                layer()
+        torch.cuda.synchronize()
+        for it in range(4):
+            fresh = _inputs(cfg, device, seed_offset=1000 * (it + 1))
+            for r in range(W):
+                xs[r].copy_(fresh[r].dp_x)
+                idx[r].copy_(fresh[r].indices)
+                wts[r].copy_(fresh[r].weights)
+            graph.replay()
+            torch.cuda.synchronize()
+            group.check()
+            _verify(cfg, fresh, num, ox, None, out)
+        assert list(group.context.iterations(0)) == [5, 5]   # 1 eager + 4 replays (capturing runs nothing)
+    finally:
+        group.destroy()
