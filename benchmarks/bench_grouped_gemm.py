@@ -43,6 +43,7 @@ def main() -> None:
     ap.add_argument("--intermediate", type=int, default=768)
     ap.add_argument("--copies", type=int, default=4, help="operand sets rotated to defeat L2")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--tile-rows", type=int, default=0, help="256 = CTA pairs, 128 = single CTAs, 0 = automatic")
     ap.add_argument("--ablate", action="store_true", help="also time the kernel with one pipeline stage removed")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
@@ -68,12 +69,13 @@ def main() -> None:
     def gemm1() -> None:
         x, xs, w13, w13s, _, _ = sets[state["i"] % args.copies]
         state["i"] += 1
-        grouped_fp8_gemm(x, xs, w13, w13s, cnt, act, act_s, mode=MODE_SWIGLU_QUANT, error_flag=flag)
+        grouped_fp8_gemm(x, xs, w13, w13s, cnt, act, act_s, mode=MODE_SWIGLU_QUANT, error_flag=flag,
+                         tile_rows=args.tile_rows)
 
     def gemm2() -> None:
         _, _, _, _, w2, w2s = sets[state["i"] % args.copies]
         state["i"] += 1
-        grouped_fp8_gemm(act, act_s, w2, w2s, cnt, y, mode=MODE_BF16, error_flag=flag)
+        grouped_fp8_gemm(act, act_s, w2, w2s, cnt, y, mode=MODE_BF16, error_flag=flag, tile_rows=args.tile_rows)
 
     def both() -> None:
         gemm1()

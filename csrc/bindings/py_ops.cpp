@@ -40,7 +40,7 @@ void bind_ops(py::module_& m) {
          uint64_t b, uint64_t b_scale, uint64_t expert_num_tokens, uint64_t out, int64_t out_stride,
          uint64_t out_scale, int64_t out_scale_stride_row, uint64_t error_flag, int num_experts, int N, int K,
          int expert_padding, int max_rows, int mode, int num_ctas, uint64_t stream, uint64_t wait_cycles,
-         int debug_skip, uint64_t trace, const py::object& scatter) {
+         int debug_skip, uint64_t trace, const py::object& scatter, int tile_rows) {
         GroupedGemmParams p;
         p.a = reinterpret_cast<const void*>(a);
         p.a_stride = a_stride;
@@ -64,6 +64,7 @@ void bind_ops(py::module_& m) {
         p.num_ctas = num_ctas;
         p.wait_cycles = reinterpret_cast<unsigned long long*>(wait_cycles);
         p.debug_skip = debug_skip;
+        p.tile_rows = tile_rows;
         p.trace = reinterpret_cast<long long*>(trace);
         if (!scatter.is_none()) {
           // the tuple AllToAllContext.combine_send_external() returns for this rank
@@ -96,5 +97,5 @@ void bind_ops(py::module_& m) {
       py::arg("num_experts"), py::arg("N"), py::arg("K"), py::arg("expert_padding"), py::arg("max_rows"),
       py::arg("mode"), py::arg("num_ctas"), py::arg("stream"), py::arg("wait_cycles") = 0,
       py::arg("debug_skip") = 0, py::arg("trace") = 0,
-      py::arg("scatter") = py::none());
+      py::arg("scatter") = py::none(), py::arg("tile_rows") = 0);
 }

@@ -44,15 +44,28 @@ namespace {
 using namespace pplx::tc;
 
 constexpr int kBM = 128, kBN = 256, kBK = 128;   // per CTA; a CTA pair computes 256 x 256
-constexpr int kStages = 5;
+// The kernel body exists for tiles worked on by a pair of CTAs (kCtas 2: 256 rows, each CTA loads
+// half of B) and by one CTA (kCtas 1: 128 rows, for experts with so few rows that a pair's second
+// CTA would idle). Stage and staging sizes differ; arrays are sized for the larger.
+constexpr int kStages = 4;
+// The two MMA issuers take alternate K blocks and every issuer waits only for its own blocks'
+// operand barriers, by phase parity. That is sound only if a stage always belongs to the same
+// issuer, i.e. if the number of stages is even: with an odd count the two issuers share each
+// stage's barrier, an issuer skips every other phase of it, and a parity wait can then be
+// satisfied by the phase before the one it means when two TMA loads complete out of order
+// (seen as a launch failure about once in a hundred launches with three stages).
+static_assert(kStages % 2 == 0, "a stage must always be consumed by the same MMA issuer");
 constexpr int kThreads = 384;
 constexpr int kFirstEpilogueWarp = 4;
 constexpr int kEpilogueThreads = 256;
 constexpr uint32_t kABytes = kBM * kBK;        // 16 KiB
-constexpr uint32_t kBBoxBytes = 64 * kBK;      // 8 KiB; a CTA holds two boxes: its half of the tile's B rows
-constexpr uint32_t kStageBytes = kABytes + 2 * kBBoxBytes;  // 32 KiB per CTA
+constexpr uint32_t kBBoxBytes = 64 * kBK;      // 8 KiB; a CTA of a pair holds two boxes (its half of the tile's B rows), a lone CTA four
+template <int kCtas> constexpr int kBBoxesOf = kCtas == 2 ? 2 : 4;
+template <int kCtas> constexpr uint32_t kStageBytesOf = kABytes + kBBoxesOf<kCtas> * kBBoxBytes;  // 32 / 48 KiB
 constexpr uint32_t kBulkRowStride = 144;          // staged rows for bulk copies: 128 B + 16 B against bank conflicts
-constexpr uint32_t kWarpStageBytes = 32 * kBulkRowStride;   // per epilogue warp, for coalesced output stores
+// per epilogue warp, for coalesced output stores: 128-byte row chunks (padded for bulk copies) in
+// the pair kernel; the lone-CTA kernel's four 48 KiB stages leave room for 64-byte chunks only
+template <int kCtas> constexpr uint32_t kWarpStageBytesOf = kCtas == 2 ? 32 * kBulkRowStride : 32 * 64;
 constexpr uint32_t kTmemCols = 512;
 // Register split between the first warpgroup (copies, MMA issue) and the epilogue warps. The
 // pool is what the CTA was launched with, 168 registers for each of its 384 threads, not the
@@ -137,6 +150,36 @@ __device__ __forceinline__ void store_rows_64B(uint8_t* stage, int lane, const u
   __syncwarp();
 }
 
+// The 64-byte transposition with a row address functor (null = skip the row), for bf16 rows in the
+// lone-CTA kernel.
+template <typename RowBase>
+__device__ __forceinline__ void store_rows_64B_fn(uint8_t* stage, int lane, const uint32_t (&w)[16], bool streaming,
+                                                  RowBase row_base) {
+  #pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int pu = u ^ ((lane >> 1) & 3);
+    *reinterpret_cast<uint4*>(stage + lane * 64 + pu * 16) = make_uint4(w[4 * u], w[4 * u + 1], w[4 * u + 2], w[4 * u + 3]);
+  }
+  __syncwarp();
+  #pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = 8 * i + (lane >> 2);
+    const int u = lane & 3;
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + r * 64 + ((u ^ ((r >> 1) & 3)) * 16));
+    uint8_t* const base = row_base(r);
+    if (base != nullptr) {
+      if (streaming) {
+        Vec16 out;
+        out.x = v.x; out.y = v.y; out.z = v.z; out.w = v.w;
+        st_stream_v4(base + u * 16, out);
+      } else {
+        *reinterpret_cast<uint4*>(base + u * 16) = v;
+      }
+    }
+  }
+  __syncwarp();
+}
+
 // 128 bytes per row (64 bf16 columns): one store instruction then covers 4 rows x one full
 // 128-byte line, which is what both the L2 and NVLink move best. `row_base(r)` gives the address
 // of row r's chunk or null. Units of 16 bytes are XOR-swizzled with the row index (conflict-free
@@ -169,8 +212,11 @@ __device__ __forceinline__ void store_rows_128B(uint8_t* stage, int lane, const 
   __syncwarp();
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-    grouped_fp8_gemm_kernel(const __grid_constant__ KernelArgs a) {
+template <int kCtas>
+__device__ __forceinline__ void grouped_fp8_gemm_body(const KernelArgs& a) {
+  constexpr uint32_t kStageBytes = kStageBytesOf<kCtas>;
+  constexpr int kBBoxes = kBBoxesOf<kCtas>;
+  constexpr uint32_t kWarpStageBytes = kWarpStageBytesOf<kCtas>;
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ uint64_t full_bar[kStages], empty_bar[kStages], tmem_full_bar[2], tmem_empty_bar[2];
   __shared__ uint32_t tmem_base_slot;
@@ -186,10 +232,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   const int I = a.N / 2;
   const int n_tiles = swiglu ? I / 128 : a.N / kBN;
   const int nkb = a.K / kBK;
-  // The two CTAs of a cluster form a pair: rank 0 (the leader) issues the MMAs for both.
-  const uint32_t rank = cluster_ctarank();
-  const int pair = blockIdx.x >> 1;
-  const int num_pairs = gridDim.x >> 1;
+  // The two CTAs of a cluster form a pair: rank 0 (the leader) issues the MMAs for both. A lone CTA
+  // is a "pair" of one: rank 0, its own leader.
+  const uint32_t rank = kCtas == 2 ? cluster_ctarank() : 0u;
+  const int pair = blockIdx.x / kCtas;
+  const int num_pairs = gridDim.x / kCtas;
 
   if (threadIdx.x == 0) {
     if (a.trace != nullptr && blockIdx.x == 0) {   // last row: kernel start / end, SM clock and ns
@@ -202,7 +249,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full_bar[b], 1);
-      mbar_init(&tmem_empty_bar[b], 2 * kEpilogueThreads / 32);   // the epilogue warps of both CTAs (leader's copy is used)
+      mbar_init(&tmem_empty_bar[b], kCtas * kEpilogueThreads / 32);   // the epilogue warps of every CTA of the tile (leader's copy is used)
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_failed = 0;
@@ -225,7 +272,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     #pragma unroll
     for (int j = 0; j < kPerLane; ++j) {
       rows_of[j] = (n[j] + a.expert_padding - 1) / a.expert_padding * a.expert_padding;
-      tiles_of[j] = (n[j] + 2 * kBM - 1) / (2 * kBM) * n_tiles;   // one tile = 256 rows: 128 per CTA of the pair
+      tiles_of[j] = (n[j] + kCtas * kBM - 1) / (kCtas * kBM) * n_tiles;   // one tile = 128 rows per CTA working on it
       my_rows += rows_of[j];
       my_tiles += tiles_of[j];
     }
@@ -256,12 +303,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     if (lane == 0) sched.tile_prefix[a.num_experts] = total_tiles_all;
   }
   if (warp == 1) {
-    tmem_alloc_pair(&tmem_base_slot, kTmemCols);
-    tmem_relinquish_pair();
+    if constexpr (kCtas == 2) {
+      tmem_alloc_pair(&tmem_base_slot, kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&tmem_base_slot, kTmemCols);
+      tmem_relinquish();
+    }
   }
   // Both CTAs' barriers and tensor memory must exist before either signals the other.
   fence_before_thread_sync();
-  cluster_sync_all();
+  if constexpr (kCtas == 2) {
+    cluster_sync_all();
+  } else {
+    __syncthreads();
+  }
   fence_after_thread_sync();
   const uint32_t tmem_base = tmem_base_slot;
   const int total_tiles = sched.tile_prefix[a.num_experts];
@@ -278,20 +334,34 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       uint32_t it = 0;
       long long waited = 0;
       int e = 0;
-      const uint32_t full_leader = map_to_cta(&full_bar[0], 0);   // the leader's barriers count both CTAs' bytes
+      // the leader's barriers count both CTAs' bytes
+      const uint32_t full_leader = kCtas == 2 ? map_to_cta(&full_bar[0], 0) : smem_u32(&full_bar[0]);
       for (int t = pair; t < total_tiles && !s_failed; t += num_pairs) {
         int m_pair, n_tile;
         decode_tile(sched, a.num_experts, n_tiles, t, &e, &m_pair, &n_tile);
-        const int row0 = sched.row_start[e] + (2 * m_pair + static_cast<int>(rank)) * kBM;
+        const int row0 = sched.row_start[e] + (kCtas * m_pair + static_cast<int>(rank)) * kBM;
         // This CTA's half of the tile's 256 B rows (accumulator columns [128 rank, 128 rank + 128)).
         // SwiGLU interleaves gate and up in 64-row boxes so that a thread's columns hold both.
-        int brow[2];
-        if (swiglu) {
-          brow[0] = e * a.N + n_tile * 128 + 64 * static_cast<int>(rank);
-          brow[1] = brow[0] + I;
+        // A lone CTA loads all four boxes: gate, up, gate + 64, up + 64.
+        int brow[kBBoxes];
+        if constexpr (kCtas == 2) {
+          if (swiglu) {
+            brow[0] = e * a.N + n_tile * 128 + 64 * static_cast<int>(rank);
+            brow[1] = brow[0] + I;
+          } else {
+            brow[0] = e * a.N + n_tile * kBN + 128 * static_cast<int>(rank);
+            brow[1] = brow[0] + 64;
+          }
         } else {
-          brow[0] = e * a.N + n_tile * kBN + 128 * static_cast<int>(rank);
-          brow[1] = brow[0] + 64;
+          if (swiglu) {
+            brow[0] = e * a.N + n_tile * 128;
+            brow[1] = brow[0] + I;
+            brow[2] = brow[0] + 64;
+            brow[3] = brow[1] + 64;
+          } else {
+            #pragma unroll
+            for (int i = 0; i < kBBoxes; ++i) brow[i] = e * a.N + n_tile * kBN + 64 * i;
+          }
         }
         const int trace_row = (a.trace != nullptr && blockIdx.x == 0 && t / num_pairs < 32) ? t / num_pairs : -1;
         if (trace_row >= 0) a.trace[trace_row * 8 + 6] = clock64();
@@ -311,12 +381,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             if (rank == 0) mbar_arrive(&full_bar[s]);
             continue;
           }
-          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * kStageBytes);
+          if (rank == 0) mbar_expect_tx(&full_bar[s], kCtas * kStageBytes);
           const uint32_t full_s = full_leader + static_cast<uint32_t>(s) * 8u;
-          tma_load_2d_pair(stage, &a.map_a, kb * kBK, row0, full_s);
+          if constexpr (kCtas == 2) {
+            tma_load_2d_pair(stage, &a.map_a, kb * kBK, row0, full_s);
+          } else {
+            tma_load_2d(stage, &a.map_a, kb * kBK, row0, &full_bar[s]);
+          }
           #pragma unroll
-          for (int i = 0; i < 2; ++i) {
-            tma_load_2d_pair(stage + kABytes + i * kBBoxBytes, &a.map_b, kb * kBK, brow[i], full_s);
+          for (int i = 0; i < kBBoxes; ++i) {
+            if constexpr (kCtas == 2) {
+              tma_load_2d_pair(stage + kABytes + i * kBBoxBytes, &a.map_b, kb * kBK, brow[i], full_s);
+            } else {
+              tma_load_2d(stage + kABytes + i * kBBoxBytes, &a.map_b, kb * kBK, brow[i], &full_bar[s]);
+            }
           }
         }
         if (trace_row >= 0) a.trace[trace_row * 8 + 7] = clock64();
@@ -333,7 +411,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       // The whole warp runs the loop and one elected lane issues: descriptors and addresses then
       // stay in uniform registers, which is what tcgen05.mma takes, instead of being moved there
       // one by one in front of every instruction.
-      constexpr uint32_t idesc = idesc_e4m3_f32(2 * kBM, kBN);
+      constexpr uint32_t idesc = idesc_e4m3_f32(kCtas * kBM, kBN);
       const uint32_t w = warp - 1;
       const uint32_t my_tiles = pair < total_tiles ? (total_tiles - pair + num_pairs - 1) / num_pairs : 0;
       const uint32_t total_blocks = my_tiles * static_cast<uint32_t>(nkb);
@@ -376,12 +454,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             #pragma unroll
             for (int k4 = 0; k4 < kBK / 32; ++k4) {
               // advancing 32 bytes along K inside the 128-byte swizzled row: +2 in 16-byte units
-              mma_f8f6f4_pair(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+              if constexpr (kCtas == 2) {
+                mma_f8f6f4_pair(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+              } else {
+                mma_f8f6f4(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+              }
             }
           }
           // in both CTAs: the partial sums may be read once these MMAs are done, and the stage refilled
-          mma_commit_pair(&tmem_full_bar[w], 0x3);
-          mma_commit_pair(&empty_bar[s], 0x3);
+          if constexpr (kCtas == 2) {
+            mma_commit_pair(&tmem_full_bar[w], 0x3);
+            mma_commit_pair(&empty_bar[s], 0x3);
+          } else {
+            mma_commit(&tmem_full_bar[w]);
+            mma_commit(&empty_bar[s]);
+          }
         }
         __syncwarp();
         if (stamps && it < kTraceBlocks) a.trace[kTraceBlockBase + it * 8 + 0] = clock64();
@@ -427,11 +514,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     // would otherwise be a cold read in front of the first fold.
     float as_first = 0.f, b0_first = 0.f, b1_first = 0.f;
     int e = 0, e_ahead = 0;   // expert cursors of this tile and of the next one
-    const uint32_t tmem_empty_leader = map_to_cta(&tmem_empty_bar[0], 0);
+    const uint32_t tmem_empty_leader = kCtas == 2 ? map_to_cta(&tmem_empty_bar[0], 0) : smem_u32(&tmem_empty_bar[0]);
     if (pair < total_tiles) {
       int m_ahead, n_ahead;
       decode_tile(sched, a.num_experts, n_tiles, pair, &e_ahead, &m_ahead, &n_ahead);
-      const TileScales ts = tile_scales(e_ahead, 2 * m_ahead + static_cast<int>(rank), n_ahead);
+      const TileScales ts = tile_scales(e_ahead, kCtas * m_ahead + static_cast<int>(rank), n_ahead);
       as_first = ts.a_row[0];
       b0_first = ts.b0[0];
       b1_first = ts.b1[0];
@@ -442,7 +529,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                              t / num_pairs < 32) ? t / num_pairs : -1;
       if (trace_row >= 0) a.trace[trace_row * 8 + 0] = clock64();
       decode_tile(sched, a.num_experts, n_tiles, t, &e, &m_pair, &n_tile);
-      const int m_tile = 2 * m_pair + static_cast<int>(rank);   // this CTA's 128 rows of the pair's 256
+      const int m_tile = kCtas * m_pair + static_cast<int>(rank);   // this CTA's 128 rows of the tile
       const int row = sched.row_start[e] + m_tile * kBM + row_in_tile;
       const bool valid = m_tile * kBM + row_in_tile < sched.count[e] && row < a.max_rows;
       const TileScales cur = tile_scales(e, m_tile, n_tile);
@@ -453,7 +540,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       if (t + num_pairs < total_tiles) {
         int m_ahead, n_ahead;
         decode_tile(sched, a.num_experts, n_tiles, t + num_pairs, &e_ahead, &m_ahead, &n_ahead);
-        const TileScales nx = tile_scales(e_ahead, 2 * m_ahead + static_cast<int>(rank), n_ahead);
+        const TileScales nx = tile_scales(e_ahead, kCtas * m_ahead + static_cast<int>(rank), n_ahead);
         as_first = nx.a_row[0];
         b0_first = nx.b0[0];
         b1_first = nx.b1[0];
@@ -489,7 +576,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         if (a.debug_skip & 1) {   // profiling aid: leave the partial sums unread
           fence_before_thread_sync();
           __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(tmem_empty_leader + static_cast<uint32_t>(buf) * 8u);
+          if (lane == 0) {
+            if constexpr (kCtas == 2) {
+              mbar_arrive_cluster(tmem_empty_leader + static_cast<uint32_t>(buf) * 8u);
+            } else {
+              mbar_arrive(&tmem_empty_bar[buf]);
+            }
+          }
           if (trace_block) a.trace[kTraceBlockBase + acc_it * 8 + 2] = clock64();
           continue;
         }
@@ -515,7 +608,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         // everything this warp needs from the buffer is in registers: hand it back
         fence_before_thread_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(tmem_empty_leader + static_cast<uint32_t>(buf) * 8u);
+        if (lane == 0) {
+            if constexpr (kCtas == 2) {
+              mbar_arrive_cluster(tmem_empty_leader + static_cast<uint32_t>(buf) * 8u);
+            } else {
+              mbar_arrive(&tmem_empty_bar[buf]);
+            }
+          }
         if (trace_block) a.trace[kTraceBlockBase + acc_it * 8 + 2] = clock64();
         #pragma unroll
         for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(sc1, __uint_as_float(tb[i]), acc[96 + i]);
@@ -570,6 +669,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         }
         const uint32_t col0 = static_cast<uint32_t>(n_tile * kBN + h * 128) * 2u;
         const unsigned long long mine = reinterpret_cast<unsigned long long>(row_ptr);
+        if constexpr (kCtas == 1) {
+          // the lone-CTA kernel stages 64-byte chunks (its stages leave no room for more)
+          #pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t w[16];
+            #pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[c * 32 + 2 * j], acc[c * 32 + 2 * j + 1]);
+              w[j] = *reinterpret_cast<const uint32_t*>(&p2);
+            }
+            store_rows_64B_fn(warp_stage, lane, w, true, [&](int r) {
+              uint8_t* const base = reinterpret_cast<uint8_t*>(__shfl_sync(0xffffffffu, mine, r));
+              return base == nullptr ? base : base + col0 + c * 64;
+            });
+          }
+        } else {
         #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t w[32];
@@ -599,8 +714,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             });
           }
         }
+        }
       } else {
         uint8_t* dst = a.out + warp_row0 * a.out_stride + (static_cast<int64_t>(n_tile) * kBN + h * 128) * 2;
+        if constexpr (kCtas == 1) {
+          #pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t w[16];
+            #pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[c * 32 + 2 * j], acc[c * 32 + 2 * j + 1]);
+              w[j] = *reinterpret_cast<const uint32_t*>(&p2);
+            }
+            store_rows_64B_fn(warp_stage, lane, w, false, [&](int r) {
+              return ((valid_mask >> r) & 1u) ? dst + r * a.out_stride + c * 64 : static_cast<uint8_t*>(nullptr);
+            });
+          }
+        } else {
         #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t w[32];
@@ -613,6 +743,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             return ((valid_mask >> r) & 1u) ? dst + r * a.out_stride + c * 128 : static_cast<uint8_t*>(nullptr);
           });
         }
+        }
       }
       if (trace_row >= 0) a.trace[trace_row * 8 + 3] = clock64();
       if (failed) break;
@@ -621,13 +752,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       a.wait_cycles[blockIdx.x * 4 + 3] = static_cast<unsigned long long>(waited_acc);
     }
     // bulk copies this thread handed over must have been performed before the arrival signal
-    if (a.mode == kBf16Scatter && a.scatter.bulk) bulk_wait0();
+    if (kCtas == 2 && a.mode == kBf16Scatter && a.scatter.bulk) bulk_wait0();
   }
 
   // Neither CTA may leave, or give its tensor memory back, while the other can still signal its
   // barriers or write its accumulators.
   fence_before_thread_sync();
-  cluster_sync_all();
+  if constexpr (kCtas == 2) {
+    cluster_sync_all();
+  } else {
+    __syncthreads();
+  }
   if (a.mode == kBf16Scatter && threadIdx.x == 0) {
     // The last CTA to get here tells every GPU that this rank's rows have been written. Each CTA's
     // stores are ordered before its increment (system fence after the barrier above), the last
@@ -649,8 +784,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   }
   if (warp == 1) {
     fence_after_thread_sync();
-    tmem_dealloc_pair(tmem_base, kTmemCols);
+    if constexpr (kCtas == 2) {
+      tmem_dealloc_pair(tmem_base, kTmemCols);
+    } else {
+      tmem_dealloc(tmem_base, kTmemCols);
+    }
   }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+    grouped_fp8_gemm_kernel(const __grid_constant__ KernelArgs a) {
+  grouped_fp8_gemm_body<2>(a);
+}
+
+// One CTA per 128-row tile: for experts with so few rows that the second CTA of a pair would idle.
+__global__ void __launch_bounds__(kThreads, 1) grouped_fp8_gemm_kernel_1cta(const __grid_constant__ KernelArgs a) {
+  grouped_fp8_gemm_body<1>(a);
 }
 
 CUtensorMap make_map(const void* base, uint64_t rows, uint64_t cols_bytes, uint64_t row_stride_bytes,
@@ -727,11 +876,27 @@ void grouped_fp8_gemm(const GroupedGemmParams& p, cudaStream_t stream) {
   int device = 0, sms = 0;
   PPLX_CUDA_CHECK(cudaGetDevice(&device));
   PPLX_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-  const size_t smem = static_cast<size_t>(kStages) * kStageBytes + (kEpilogueThreads / 32) * kWarpStageBytes + 1024;
-  PPLX_CUDA_CHECK(cudaFuncSetAttribute(grouped_fp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem)));
-  const int grid = std::max(2, (p.num_ctas > 0 ? p.num_ctas : sms) & ~1);   // whole CTA pairs
-  grouped_fp8_gemm_kernel<<<grid, kThreads, smem, stream>>>(a);
+  // Pairs of CTAs on 256-row tiles unless the experts are small: with no more than 192 rows per
+  // expert on average (by capacity; the counts themselves stay on the device) the second CTA of a
+  // pair would mostly idle, and single CTAs on 128-row tiles do the same work with half the waste.
+  const bool wants_pairs = p.mode == kBf16Scatter && p.scatter.bulk;   // the bulk-copy sender stages 128-byte rows
+  const int tile_rows =
+      p.tile_rows != 0 ? p.tile_rows : ((wants_pairs || p.max_rows / p.num_experts > 192) ? 256 : 128);
+  PPLX_REQUIRE(tile_rows == 128 || tile_rows == 256, "tile_rows must be 0 (automatic), 128 or 256");
+  const int ctas = p.num_ctas > 0 ? p.num_ctas : sms;
+  if (tile_rows == 256) {
+    const size_t smem = static_cast<size_t>(kStages) * kStageBytesOf<2> + (kEpilogueThreads / 32) * kWarpStageBytesOf<2> + 1024;
+    PPLX_CUDA_CHECK(cudaFuncSetAttribute(grouped_fp8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem)));
+    const int grid = std::max(2, ctas & ~1);   // whole CTA pairs
+    grouped_fp8_gemm_kernel<<<grid, kThreads, smem, stream>>>(a);
+  } else {
+    PPLX_REQUIRE(!(p.mode == kBf16Scatter && p.scatter.bulk), "the bulk-copy sender needs 256-row tiles");
+    const size_t smem = static_cast<size_t>(kStages) * kStageBytesOf<1> + (kEpilogueThreads / 32) * kWarpStageBytesOf<1> + 1024;
+    PPLX_CUDA_CHECK(cudaFuncSetAttribute(grouped_fp8_gemm_kernel_1cta, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem)));
+    grouped_fp8_gemm_kernel_1cta<<<std::max(1, ctas), kThreads, smem, stream>>>(a);
+  }
   PPLX_CUDA_CHECK(cudaGetLastError());
 }
 

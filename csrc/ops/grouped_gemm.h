@@ -62,6 +62,9 @@ struct GroupedGemmParams {
   int max_rows = 0;
   int mode = kBf16;
   int num_ctas = 0;                 // 0: one per SM
+  // Rows per tile: 256 = pairs of CTAs (each loads half of B), 128 = one CTA per tile (for experts
+  // with few rows), 0 = choose from max_rows / num_experts.
+  int tile_rows = 0;
   // Profiling aid, 0 in production (results are wrong otherwise). Bit 0: the epilogue leaves the
   // partial sums unread; bit 1: no MMAs are issued; bit 2: no TMA loads;
   // bit 3: every MMA is issued twice. Timing the kernel with

@@ -61,6 +61,7 @@ def grouped_fp8_gemm(
     debug_skip: int = 0,
     trace: Optional[torch.Tensor] = None,
     scatter: Optional[tuple] = None,
+    tile_rows: int = 0,
 ) -> None:
     """``out[rows of expert e] = epilogue(dequant(a rows) @ dequant(b[e]).T)``.
 
@@ -72,6 +73,8 @@ def grouped_fp8_gemm(
     mode MODE_BF16_SCATTER: no ``out``; ``scatter`` is the descriptor from
     ``P2PAllToAll.combine_send_external()``: every bf16 row goes straight into the combine receive
     buffer of the GPU its token came from (peer stores), and the kernel signals the receivers.
+    ``tile_rows``: 256 = pairs of CTAs per tile (each CTA loads half of B), 128 = one CTA per tile,
+    better for experts with few rows; 0 picks by ``rows / experts`` (capacity, not the counts).
     ``wait_cycles`` (int64 [num CTAs, 4], optional) receives the cycles each pipeline role spent
     waiting: producer for a free stage, MMA for a free accumulator, MMA for operands, epilogue
     for partial sums. ``debug_skip`` (profiling only, wrong results) removes a stage: 1 the
@@ -104,4 +107,4 @@ def grouped_fp8_gemm(
         0 if out_scale is None else out_scale.stride(0), error_flag.data_ptr(), e, n, k, expert_padding, rows, mode,
         num_ctas, torch.cuda.current_stream().cuda_stream,
         0 if wait_cycles is None else wait_cycles.data_ptr(), debug_skip,
-        0 if trace is None else trace.data_ptr(), scatter)
+        0 if trace is None else trace.data_ptr(), scatter, tile_rows)

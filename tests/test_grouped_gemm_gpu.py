@@ -58,11 +58,13 @@ def _make(counts, K, N, padding, seed=0, unit_scales=False):
     ([(7 * i) % 40 for i in range(100)], 256, 256, 1, False),   # many small experts, several per lane of the scan
     ([3] * 128, 128, 256, 4, False),
 ])
-def test_bf16_epilogue(counts, K, N, padding, unit) -> None:
+@pytest.mark.parametrize("tile_rows", [128, 256])
+def test_bf16_epilogue(counts, K, N, padding, unit, tile_rows) -> None:
     aq, a_s, bq, b_s, cnt, starts, rows = _make(counts, K, N, padding, unit_scales=unit)
     out = torch.full((rows, N), float("nan"), dtype=torch.bfloat16, device=aq.device)
     flag = torch.zeros(1, dtype=torch.int32, device=aq.device)
-    grouped_fp8_gemm(aq, a_s, bq, b_s, cnt, out, mode=MODE_BF16, expert_padding=padding, error_flag=flag)
+    grouped_fp8_gemm(aq, a_s, bq, b_s, cnt, out, mode=MODE_BF16, expert_padding=padding, error_flag=flag,
+                     tile_rows=tile_rows)
     torch.cuda.synchronize()
     assert flag.item() == 0, f"kernel reported a wait that ran out (code {flag.item()})"
     a = dequantize_1x128(aq, a_s)
@@ -81,14 +83,15 @@ def test_bf16_epilogue(counts, K, N, padding, unit) -> None:
     ([90, 0, 260], 1024, 256, 1),
     ([64, 512, 3], 2048, 768, 8),
 ])
-def test_swiglu_quant_epilogue(counts, K, I, padding) -> None:
+@pytest.mark.parametrize("tile_rows", [128, 256])
+def test_swiglu_quant_epilogue(counts, K, I, padding, tile_rows) -> None:
     N = 2 * I
     aq, a_s, bq, b_s, cnt, starts, rows = _make(counts, K, N, padding, seed=1)
     out = torch.zeros((rows, I), dtype=torch.uint8, device=aq.device).view(torch.float8_e4m3fn)
     out_s = torch.zeros((rows, I // 128), dtype=torch.float32, device=aq.device)
     flag = torch.zeros(1, dtype=torch.int32, device=aq.device)
     grouped_fp8_gemm(aq, a_s, bq, b_s, cnt, out, out_s, mode=MODE_SWIGLU_QUANT, expert_padding=padding,
-                     error_flag=flag)
+                     error_flag=flag, tile_rows=tile_rows)
     torch.cuda.synchronize()
     assert flag.item() == 0
     a = dequantize_1x128(aq, a_s)
