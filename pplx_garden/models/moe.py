@@ -85,6 +85,11 @@ class ExpertParallelMoE:
         self.act_scale = torch.zeros((rows, intermediate_dim // 128), dtype=torch.float32, device=dev)
         self.expert_y = torch.zeros((rows, hidden_dim), dtype=torch.bfloat16, device=dev)
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        # Tile shape of the expert GEMMs from the rows an expert can expect (the capacity of the
+        # receive buffer is a worst case and would always say "large"): 256-row CTA-pair tiles for
+        # big experts, 128-row single-CTA tiles when an expert sees fewer than about 192 rows.
+        expected_rows = max_num_tokens * num_experts_per_token * world / max(num_experts, 1)
+        self.tile_rows = 256 if expected_rows > 192 else 128
         # fused_combine: the down projection writes its rows into the peers' combine buffers itself
         self.fused_combine = fused_combine
         self.fused_bulk = fused_bulk   # fused_combine through the bulk-copy engine
@@ -109,19 +114,21 @@ class ExpertParallelMoE:
     def gate_up(self) -> None:
         """act = quantise(silu(x W_gate^T) * (x W_up^T)) on the rows dispatch delivered."""
         grouped_fp8_gemm(self.expert_x, self.expert_x_scale, self.w13, self.w13_scale, self.expert_num_tokens,
-                         self.act, self.act_scale, mode=MODE_SWIGLU_QUANT, error_flag=self.error_flag)
+                         self.act, self.act_scale, mode=MODE_SWIGLU_QUANT, error_flag=self.error_flag,
+                         tile_rows=self.tile_rows)
 
     def down_and_send(self) -> None:
         """The down projection and the combine's send phase in one kernel: every output row is
         written over NVLink into the combine receive buffer of the GPU its token came from."""
         grouped_fp8_gemm(self.act, self.act_scale, self.w2, self.w2_scale, self.expert_num_tokens, None,
                          mode=MODE_BF16_SCATTER, error_flag=self.error_flag,
-                         scatter=self.a2a.combine_send_external(self.fused_bulk))
+                         scatter=self.a2a.combine_send_external(self.fused_bulk),
+                         tile_rows=256 if self.fused_bulk else self.tile_rows)
 
     def down(self) -> None:
         """expert_y = act W_down^T in bf16: the rows combine sends home."""
         grouped_fp8_gemm(self.act, self.act_scale, self.w2, self.w2_scale, self.expert_num_tokens,
-                         self.expert_y, mode=MODE_BF16, error_flag=self.error_flag)
+                         self.expert_y, mode=MODE_BF16, error_flag=self.error_flag, tile_rows=self.tile_rows)
 
     __call__ = forward
 
