@@ -328,15 +328,34 @@ void Engine::encode_segment(std::string_view text, EncodeState* st) const {
   // of the running sum decides; sums that restart at every word round as the original's do.
   // (The reference runs one pass over the whole segment: pplx-unigram/src/engine.rs:88-165.)
   const size_t rl = replacement_.size();
+  if (st->words_owner != this) {   // a state that served another engine starts over
+    st->words = WordCache();
+    st->words_owner = this;
+  }
+  auto encode_word = [&](size_t begin, size_t len) {
+    if (len > WordCache::kMaxWordBytes) {
+      viterbi(bytes + begin, len, st);
+      return;
+    }
+    const uint64_t h = WordCache::hash_bytes(bytes + begin, len);
+    if (const WordCache::Entry* hit = st->words.find(bytes + begin, len, h)) {
+      const TokenId* t = st->words.tokens_of(*hit);
+      st->tokens.insert(st->tokens.end(), t, t + hit->num_tokens);
+      return;
+    }
+    const size_t first = st->tokens.size();
+    viterbi(bytes + begin, len, st);
+    st->words.insert(bytes + begin, len, h, st->tokens.data() + first, st->tokens.size() - first);
+  };
   size_t word = 0;
   for (size_t i = rl > 0 ? 1 : n; i + rl <= n; ++i) {
     if (prep.compare(i, rl, replacement_) == 0) {
-      viterbi(bytes + word, i - word, st);
+      encode_word(word, i - word);
       word = i;
       i += rl - 1;
     }
   }
-  viterbi(bytes + word, n - word, st);
+  encode_word(word, n - word);
 }
 
 void Engine::viterbi(const uint8_t* prep, size_t n, EncodeState* st) const {

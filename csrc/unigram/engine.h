@@ -13,6 +13,7 @@
 #include <cstdint>
 #include <memory>
 #include <stdexcept>
+#include <cstring>
 #include <string>
 #include <string_view>
 #include <vector>
@@ -50,6 +51,65 @@ struct SpecialToken {
   bool rstrip = false;
 };
 
+// Words seen before and their token ids, per encoding thread. Natural text repeats its words
+// (Zipf), and with the text cut into words the best path of a word never depends on its
+// neighbours, so a hit replaces the whole Viterbi pass over the word. Open addressing over
+// 64-bit hashes with the bytes kept in one arena; bounded: once full, new words are simply
+// not remembered.
+class WordCache {
+ public:
+  static constexpr size_t kSlots = 1u << 16;       // power of two
+  static constexpr size_t kMaxEntries = kSlots / 2;
+  static constexpr size_t kMaxWordBytes = 64;
+  static constexpr size_t kMaxArenaBytes = 4u << 20;
+
+  struct Entry {
+    uint64_t hash = 0;      // 0 = empty slot
+    uint32_t key_off = 0;
+    uint16_t key_len = 0;
+    uint16_t num_tokens = 0;
+    uint32_t tok_off = 0;
+  };
+
+  // Returns the entry of `word` or nullptr.
+  const Entry* find(const uint8_t* word, size_t len, uint64_t hash) const {
+    if (slots_.empty()) return nullptr;
+    for (size_t i = hash & (kSlots - 1);; i = (i + 1) & (kSlots - 1)) {
+      const Entry& e = slots_[i];
+      if (e.hash == 0) return nullptr;
+      if (e.hash == hash && e.key_len == len && std::memcmp(keys_.data() + e.key_off, word, len) == 0) return &e;
+    }
+  }
+  const TokenId* tokens_of(const Entry& e) const { return toks_.data() + e.tok_off; }
+  void insert(const uint8_t* word, size_t len, uint64_t hash, const TokenId* toks, size_t n) {
+    if (count_ >= kMaxEntries || keys_.size() + len > kMaxArenaBytes || n > 0xffff) return;
+    if (slots_.empty()) slots_.resize(kSlots);
+    size_t i = hash & (kSlots - 1);
+    while (slots_[i].hash != 0) i = (i + 1) & (kSlots - 1);
+    Entry& e = slots_[i];
+    e.hash = hash;
+    e.key_off = static_cast<uint32_t>(keys_.size());
+    e.key_len = static_cast<uint16_t>(len);
+    e.num_tokens = static_cast<uint16_t>(n);
+    e.tok_off = static_cast<uint32_t>(toks_.size());
+    keys_.insert(keys_.end(), word, word + len);
+    toks_.insert(toks_.end(), toks, toks + n);
+    ++count_;
+  }
+  static uint64_t hash_bytes(const uint8_t* p, size_t n) {   // FNV-1a, never 0
+    uint64_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < n; ++i) h = (h ^ p[i]) * 1099511628211ull;
+    return h | 1ull;
+  }
+  size_t size() const { return count_; }
+
+ private:
+  std::vector<Entry> slots_;
+  std::vector<uint8_t> keys_;
+  std::vector<TokenId> toks_;
+  size_t count_ = 0;
+};
+
 // Scratch buffers of one encoding thread; grow to the longest input seen and are reused.
 struct EncodeState {
   std::vector<TokenId> tokens;  // result of the last encode()
@@ -60,6 +120,8 @@ struct EncodeState {
   std::vector<uint32_t> best_start;
   std::vector<TokenId> best_id;
   std::vector<TokenId> backtrack;
+  WordCache words;          // belongs to one engine: do not share a state between engines
+  const void* words_owner = nullptr;
 };
 
 class SpecialTokenMatcher {

@@ -176,3 +176,15 @@ def test_flat_batch_equals_list_batch(pair) -> None:
     assert offsets.tolist() == [0] + [sum(len(l) for l in lists[:i + 1]) for i in range(len(lists))]
     for i, want in enumerate(lists):
         assert ids[offsets[i]:offsets[i + 1]].tolist() == want
+
+
+def test_word_cache_does_not_change_results(pair) -> None:
+    # the same words again and again, in different neighbourhoods and beside special tokens: hits of
+    # the per-thread word cache must give what a first encounter gives
+    engine, hf = pair
+    texts = ["the cat and the hat and the cat", "cat the", "the", " the  the", "x" * 100 + " the " + "x" * 100]
+    first = [engine.encode(t) for t in texts]
+    again = [engine.encode(t) for t in texts]
+    assert first == again
+    for t, ids in zip(texts, first):
+        assert ids == hf.encode(t, add_special_tokens=False).ids
