@@ -57,23 +57,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// ---- packed fp32 pairs (the two-wide FMA of sm_100 halves the issue slots of the fold) ----
-__device__ __forceinline__ uint64_t pack_f32x2(uint32_t lo, uint32_t hi) {
-  uint64_t v;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(lo), "r"(hi));
-  return v;
-}
-__device__ __forceinline__ void unpack_f32x2(uint64_t v, float* lo, float* hi) {
-  uint32_t a, b;
-  asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
-  *lo = __uint_as_float(a);
-  *hi = __uint_as_float(b);
-}
-// acc = scale * x + acc on both halves.
-__device__ __forceinline__ void fma_f32x2(uint64_t& acc, uint64_t scale, uint64_t x) {
-  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(scale), "l"(x));
-}
-
 // ---- descriptors ----
 // K-major operand tile in shared memory with the 128-byte swizzle: rows of 128 bytes,
 // 8-row groups 1024 bytes apart (what a TMA box of 128-byte rows with SWIZZLE_128B writes).

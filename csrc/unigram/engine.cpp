@@ -348,11 +348,21 @@ void Engine::encode_segment(std::string_view text, EncodeState* st) const {
     st->words.insert(bytes + begin, len, h, st->tokens.data() + first, st->tokens.size() - first);
   };
   size_t word = 0;
-  for (size_t i = rl > 0 ? 1 : n; i + rl <= n; ++i) {
-    if (prep.compare(i, rl, replacement_) == 0) {
-      encode_word(word, i - word);
-      word = i;
-      i += rl - 1;
+  if (rl > 0) {
+    // jump from one candidate first byte of the replacement character to the next
+    const uint8_t first = static_cast<uint8_t>(replacement_[0]);
+    size_t i = 1;
+    while (i + rl <= n) {
+      const void* hit = std::memchr(bytes + i, first, n - rl + 1 - i);
+      if (hit == nullptr) break;
+      i = static_cast<size_t>(static_cast<const uint8_t*>(hit) - bytes);
+      if (std::memcmp(bytes + i, replacement_.data(), rl) == 0) {
+        encode_word(word, i - word);
+        word = i;
+        i += rl;
+      } else {
+        ++i;
+      }
     }
   }
   encode_word(word, n - word);
