@@ -61,7 +61,7 @@ A2AConfig a2a_make_config(const A2AParams& p, int num_sms, int virtual_ranks) {
   if (blocks <= 0) blocks = std::max(1, num_sms / virtual_ranks);
   c.num_blocks = blocks;
 
-  c.d_header_bytes = round_up_u32(4u * (1 + 2 * p.topk), 16);
+  c.d_header_bytes = round_up_u32(4u * (2 + 2 * p.topk), 16);
   c.d_payload_bytes = static_cast<uint32_t>(p.hidden_dim) * p.in_elemsize;
   c.d_scale_bytes = round_up_u32(static_cast<uint32_t>(p.hidden_dim_scale) * 4u, 16);
   c.d_stride = round_up_u32(c.d_header_bytes + c.d_payload_bytes + c.d_scale_bytes, 128);
@@ -76,9 +76,12 @@ A2AConfig a2a_make_config(const A2AParams& p, int num_sms, int virtual_ranks) {
   PPLX_REQUIRE(rows < (1ull << 31), "receive row count overflows 31 bits");
   c.max_recv_rows = static_cast<uint32_t>(rows);
 
-  const uint64_t flag_bytes = 2ull * kMaxRanks * kFlagStrideWords * sizeof(uint32_t);
+  const uint64_t flag_bytes =
+      static_cast<uint64_t>(kNumFlagRows) * kMaxRanks * kFlagStrideWords * sizeof(uint32_t);
   c.off_counts = flag_bytes;
-  c.sync_bytes = round_up_u64(flag_bytes + 4ull * c.num_groups * c.counts_stride, 4096);
+  c.counts_bank_words = static_cast<uint32_t>(c.num_groups) * c.counts_stride;
+  c.off_tok_arrive = round_up_u64(c.off_counts + 2ull * 4ull * c.counts_bank_words, 128);
+  c.sync_bytes = round_up_u64(c.off_tok_arrive + 4ull * p.max_num_tokens, 4096);
 
   c.off_drecv = 0;
   c.drecv_group_stride = static_cast<uint64_t>(p.max_num_tokens) * c.d_stride;
@@ -166,8 +169,9 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
       off += (bytes + 255) / 256 * 256;
       return at;
     };
-    const size_t o_epochs = take(sizeof(uint32_t) * 2);
+    const size_t o_epochs = take(sizeof(uint32_t) * 4);
     const size_t o_done = take(sizeof(uint32_t) * 2);
+    const size_t o_send_cursor = take(sizeof(uint32_t) * 2 * kMaxRanks);
     const size_t o_place_cursor = take(sizeof(uint32_t) * 2 * GL);
     const size_t o_row_src = take(sizeof(uint32_t) * rows);
     const size_t o_row_tk = take(sizeof(uint32_t) * rows);
@@ -186,6 +190,7 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
     uint8_t* b = static_cast<uint8_t*>(base);
     st.local.epochs = reinterpret_cast<uint32_t*>(b + o_epochs);
     st.local.done = reinterpret_cast<uint32_t*>(b + o_done);
+    st.local.send_cursor = reinterpret_cast<uint32_t*>(b + o_send_cursor);
     st.local.place_cursor = reinterpret_cast<uint32_t*>(b + o_place_cursor);
     st.local.row_src = reinterpret_cast<uint32_t*>(b + o_row_src);
     st.local.row_tk = reinterpret_cast<uint32_t*>(b + o_row_tk);
@@ -228,9 +233,9 @@ bool A2AContext::failed() const {
   return false;
 }
 
-void A2AContext::advance_phase(int first, int last) {
-  // The device protocol counts arrivals cumulatively and tags records with the dispatch
-  // number, so the four phases must be issued in order, each exactly once per layer.
+void A2AContext::require_phase(int first) const {
+  // The device protocol tags records with the dispatch number and counts arrivals, so the
+  // four phases must be issued in order, each exactly once per layer.
   static const char* names[] = {"dispatch_send", "dispatch_recv", "combine_send", "combine_recv"};
   if (first != next_phase_) {
     throw Error(ErrorKind::kInvalidArgument,
@@ -238,8 +243,9 @@ void A2AContext::advance_phase(int first, int last) {
                     " but the next phase of this context is " + names[next_phase_] +
                     " (sequence: dispatch_send, dispatch_recv, combine_send, combine_recv)");
   }
-  next_phase_ = (last + 1) % kNumPhases;
 }
+
+void A2AContext::commit_phase(int last) { next_phase_ = (last + 1) % kNumPhases; }
 
 int A2AContext::pick(int64_t items, int64_t vectors_per_item) const {
   if (team_override_ == 32 || team_override_ == 128 || team_override_ == 512) return team_override_;
@@ -249,8 +255,9 @@ int A2AContext::pick(int64_t items, int64_t vectors_per_item) const {
 void A2AContext::dispatch(const DispatchSendArgs* send, const DispatchRecvArgs* recv, bool do_send,
                           bool do_recv, cudaStream_t stream) {
   PPLX_REQUIRE(do_send || do_recv, "dispatch: nothing to do");
-  advance_phase(do_send ? kPhaseDispatchSend : kPhaseDispatchRecv,
-                do_recv ? kPhaseDispatchRecv : kPhaseDispatchSend);
+  // Nothing is committed before the launch went through: a rejected call leaves the context
+  // where it was, so a corrected call may follow.
+  require_phase(do_send ? kPhaseDispatchSend : kPhaseDispatchRecv);
   NvtxRange range(do_send && do_recv ? "a2a_dispatch" : do_send ? "a2a_dispatch_send" : "a2a_dispatch_recv");
   PerRank<DispatchSendArgs> s{};
   PerRank<DispatchRecvArgs> r{};
@@ -284,13 +291,13 @@ void A2AContext::dispatch(const DispatchSendArgs* send, const DispatchRecvArgs* 
   const int send_team = do_send ? pick(last_tokens_, vectors) : 0;
   const int recv_team = do_recv ? pick(last_tokens_ * cfg_.num_groups, vectors) : 0;
   PPLX_CUDA_CHECK(a2a_launch_dispatch(cfg_, states_, n, s, r, send_team, recv_team, stream));
+  commit_phase(do_recv ? kPhaseDispatchRecv : kPhaseDispatchSend);
 }
 
 void A2AContext::combine(const CombineSendArgs* send, const CombineRecvArgs* recv, bool do_send,
                          bool do_recv, int y_dtype, int out_dtype, cudaStream_t stream) {
   PPLX_REQUIRE(do_send || do_recv, "combine: nothing to do");
-  advance_phase(do_send ? kPhaseCombineSend : kPhaseCombineRecv,
-                do_recv ? kPhaseCombineRecv : kPhaseCombineSend);
+  require_phase(do_send ? kPhaseCombineSend : kPhaseCombineRecv);
   NvtxRange range(do_send && do_recv ? "a2a_combine" : do_send ? "a2a_combine_send" : "a2a_combine_recv");
   PerRank<CombineSendArgs> s{};
   PerRank<CombineRecvArgs> r{};
@@ -305,6 +312,7 @@ void A2AContext::combine(const CombineSendArgs* send, const CombineRecvArgs* rec
     }
     if (do_recv) {
       r.r[i] = recv[i];
+      r.r[i].external = (!do_send && external_send_) ? 1 : 0;
       PPLX_REQUIRE(recv[i].num_tokens >= 0 && recv[i].num_tokens <= cfg_.max_num_tokens,
                    "combine: num_tokens exceeds max_num_tokens");
       tokens = std::max<int64_t>(recv[i].num_tokens, 1);
@@ -326,13 +334,24 @@ void A2AContext::combine(const CombineSendArgs* send, const CombineRecvArgs* rec
   if (do_recv) recv_team = pick(tokens, static_cast<int64_t>(cfg_.hidden_dim / 8) * 8);
   PPLX_CUDA_CHECK(a2a_launch_combine(cfg_, states_, n, s, r, send_team, recv_team, y_dtype,
                                      out_dtype, stream));
+  if (do_send) external_send_ = false;
+  if (do_recv) external_send_ = false;
+  commit_phase(do_recv ? kPhaseCombineRecv : kPhaseCombineSend);
+}
+
+void A2AContext::barrier(cudaStream_t stream) {
+  NvtxRange range("a2a_barrier");
+  PPLX_CUDA_CHECK(cudaSetDevice(device_));
+  PPLX_CUDA_CHECK(a2a_launch_barrier(cfg_, states_, num_local_ranks(), stream));
 }
 
 std::vector<A2AScatterInfo> A2AContext::combine_send_external() {
   PPLX_REQUIRE(cfg_.combine_mode == kCombinePerRoute, "an external combine send needs the per_route mode");
   PPLX_REQUIRE(cfg_.dp_size == 1, "an external combine send does not replicate to dp peers");
   PPLX_REQUIRE(cfg_.out_elemsize == 2, "an external combine send writes 2-byte elements");
-  advance_phase(kPhaseCombineSend, kPhaseCombineSend);
+  require_phase(kPhaseCombineSend);
+  commit_phase(kPhaseCombineSend);
+  external_send_ = true;
   std::vector<A2AScatterInfo> out(ranks_.size());
   for (size_t i = 0; i < ranks_.size(); ++i) {
     const A2ARankState& st = states_.r[i];
@@ -342,12 +361,13 @@ std::vector<A2AScatterInfo> A2AContext::combine_send_external() {
     s.row_tk = st.local.row_tk;
     for (int p = 0; p < cfg_.world; ++p) {
       s.peer_recv[p] = st.recv[p] + cfg_.off_crecv;
-      // combine arrivals live in flag row 1, indexed by the sending rank
-      s.peer_flag[p] = reinterpret_cast<uint32_t*>(st.sync[p]) + (1 * kMaxRanks + st.rank) * kFlagStrideWords;
+      // one counter per sending rank: externally sent combines that have fully landed
+      s.peer_flag[p] = reinterpret_cast<uint32_t*>(st.sync[p]) +
+                       (kFlagExternalCombine * kMaxRanks + st.rank) * kFlagStrideWords;
     }
     s.slot_stride = cfg_.c_stride;
     s.world = cfg_.world;
-    s.signal_value = static_cast<uint32_t>(cfg_.num_blocks);   // what num_blocks sending blocks would add
+    s.signal_value = 1;
     s.done_counter = scatter_done_ptrs_[i];
     s.status = st.local.status;
   }

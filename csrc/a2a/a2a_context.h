@@ -52,7 +52,7 @@ struct A2AScatterInfo {
   uint64_t slot_stride;            // bytes per (token, k) slot
   uint32_t* peer_flag[kMaxRanks];  // this rank's combine arrival counter at every rank
   int world;
-  uint32_t signal_value;           // arrivals a receiver expects from one sender per combine
+  uint32_t signal_value;           // what the sender adds to each flag once all its rows are written
   uint32_t* done_counter;          // scratch word, zero between launches
   const uint32_t* status;          // this rank's status word
 };
@@ -76,6 +76,10 @@ class A2AContext {
                 bool do_recv, cudaStream_t stream);
   void combine(const CombineSendArgs* send, const CombineRecvArgs* recv, bool do_send,
                bool do_recv, int y_dtype, int out_dtype, cudaStream_t stream);
+
+  // All ranks of the context meet on the device: returns (in stream order) once every rank has
+  // entered. Bounded like every other wait. Collective; may be called between any two phases.
+  void barrier(cudaStream_t stream);
 
   // The send phase of a combine done by somebody else's kernel (the down projection's epilogue
   // writes the rows into the peers' buffers and signals): advances the phase order as
@@ -103,7 +107,8 @@ class A2AContext {
 
  private:
   int pick(int64_t items, int64_t vectors_per_item) const;
-  void advance_phase(int first, int last);
+  void require_phase(int first) const;
+  void commit_phase(int last);
 
   A2AConfig cfg_{};
   int device_;
@@ -119,6 +124,7 @@ class A2AContext {
   int next_phase_ = kPhaseDispatchSend;
   int64_t last_tokens_ = 0;
   int team_override_ = 0;
+  bool external_send_ = false;  // the pending combine's send phase was played by another kernel
 };
 
 }  // namespace pplx

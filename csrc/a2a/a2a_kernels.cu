@@ -2,12 +2,16 @@
 //
 // Four phases, launched separately or fused pairwise (send+recv in one launch):
 //
-//   dispatch_send  tokens -> peer receive regions (16-byte peer stores over NVLink),
-//                  per-expert counts -> peers, arrival signal per destination
-//   dispatch_recv  wait for every source, build the expert-major layout from the
-//                  counts, replicate each record into the rows of its local experts
-//   combine_send   expert outputs -> origin ranks' combine regions, arrival signal
-//   combine_recv   wait, top-k weighted reduction into the caller's tensor
+//   dispatch_send  per-expert counts -> peers first; then tokens -> peer receive regions
+//                  (16-byte peer stores over NVLink), each record published by writing its
+//                  tag last with release semantics
+//   dispatch_recv  wait for the counts only, build the expert-major layout, then take the
+//                  records one by one as their tags appear and replicate each into the
+//                  rows of its local experts
+//   combine_send   expert outputs -> origin ranks' combine regions; each row bumps the
+//                  arrival counter of its token at the origin (release)
+//   combine_recv   per token: wait for its rows, top-k weighted reduction into the
+//                  caller's tensor
 //
 // They cover what the reference does with four cooperative kernels plus a host proxy
 // thread (p2p-all-to-all/a2a-kernels/src/a2a/a2a_dispatch_send.cu:112-536,
@@ -17,6 +21,8 @@
 //   * a token crosses NVLink once per destination *rank*, not once per route,
 //   * receive regions are sized for the worst case, so there is no overflow/pull path,
 //   * no grid-wide barrier: a block never waits for another block of its own GPU,
+//   * arrival is per record and per token, never "everything from everybody": the receive
+//     side works while the rest of the payload is still on the wire,
 //   * every wait on a remote flag is bounded in time and reports through a status word.
 //
 // blockIdx.y selects a *virtual rank*: with gridDim.y == 1 the launch serves the one
@@ -79,11 +85,9 @@ __device__ __forceinline__ void report(const A2ALocal& ws, uint32_t code, uint32
   }
 }
 
-__device__ __forceinline__ uint32_t* flag_ptr(uint8_t* sync_base, int phase_slot, int src) {
-  // phase_slot 0: dispatch arrivals (indexed by source dp group)
-  // phase_slot 1: combine arrivals (indexed by source rank)
-  return reinterpret_cast<uint32_t*>(sync_base) +
-         (phase_slot * kMaxRanks + src) * kFlagStrideWords;
+__device__ __forceinline__ uint32_t* flag_ptr(uint8_t* sync_base, int row, int src) {
+  // row: see A2AFlagRow; src: the rank that writes the word
+  return reinterpret_cast<uint32_t*>(sync_base) + (row * kMaxRanks + src) * kFlagStrideWords;
 }
 
 // Bounded wait until a cumulative arrival counter reaches `expected`.
@@ -114,7 +118,7 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t expecte
 // dispatch after next will use. Every block read the epoch before it got here, so the
 // increment cannot be observed by a block of the same launch.
 __device__ __forceinline__ void finish_recv(const A2AConfig& cfg, const A2ALocal& ws, int which,
-                                            uint32_t epoch, int trace_slot) {
+                                            uint32_t epoch, int trace_slot, bool external) {
   __syncthreads();
   __shared__ uint32_t s_last;
   if (threadIdx.x == 0) {
@@ -132,6 +136,7 @@ __device__ __forceinline__ void finish_recv(const A2AConfig& cfg, const A2ALocal
     if (threadIdx.x == 0) {
       ws.done[which] = 0;
       ws.epochs[which] = epoch + 1;
+      if (external) ws.epochs[2] = ws.epochs[2] + 1;
       if (cfg.trace) ws.trace[trace_slot] = globaltimer_ns();
     }
   }
@@ -191,7 +196,9 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
   const int L = cfg.experts_per_rank;
   const int my_group = st.rank / cfg.dp_size;
   const int my_tp = st.rank % cfg.dp_size;
-  const uint32_t tag = read_epoch(ws, 0) + 1;
+  const uint32_t epoch = read_epoch(ws, 0);
+  const uint32_t tag = epoch + 1;
+  const uint32_t par = epoch & 1u;
   trace_mark(cfg, ws, kTraceSendStart);
 
   int T = a.num_tokens;
@@ -200,19 +207,33 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
 
   __shared__ uint32_t s_idx[kMaxTeams][kMaxTopK];
   __shared__ float s_w[kMaxTeams][kMaxTopK];
+  __shared__ uint32_t s_slot[kMaxTeams][kMaxRanks];
 
-  // ---- the last block counts routes per expert and pushes the counts ----
+  // ---- counts message: leaves before any payload, from the block with the fewest tokens ----
+  // Per destination: how many records it will get from this rank and how many of them each
+  // of its experts takes. The "dispatch started" word goes to every rank (also to those this
+  // rank serves no records): a rank that has seen it from everybody knows that all ranks
+  // have left their previous combine, so the combine buffers may be written again.
   if (blockIdx.x == gridDim.x - 1) {
-    uint32_t* hist = dyn_smem;  // [num_experts]
-    for (int i = threadIdx.x; i < cfg.num_experts; i += blockDim.x) hist[i] = 0;
+    uint32_t* hist = dyn_smem;                // [num_experts]
+    uint32_t* nrec = hist + cfg.num_experts;  // [kMaxRanks]
+    for (int i = threadIdx.x; i < cfg.num_experts + kMaxRanks; i += blockDim.x) hist[i] = 0;
+    // the slot cursors of the next dispatch; nobody touches that bank during this launch
+    if (threadIdx.x < kMaxRanks) ws.send_cursor[(par ^ 1u) * kMaxRanks + threadIdx.x] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < T * K; i += blockDim.x) {
-      const int t = i / K, k = i - t * K;
-      const uint32_t e = a.indices[t * a.indices_stride + k];
-      if (e < static_cast<uint32_t>(cfg.num_experts)) {
-        atomicAdd(&hist[e], 1u);
-      } else {
-        report(ws, kStatusBadExpertIndex, kPhaseDispatchSend, t, e);
+    for (int t = threadIdx.x; t < T; t += blockDim.x) {
+      uint32_t mask = 0;
+      for (int k = 0; k < K; ++k) {
+        const uint32_t e = a.indices[t * a.indices_stride + k];
+        if (e < static_cast<uint32_t>(cfg.num_experts)) {
+          atomicAdd(&hist[e], 1u);
+          mask |= 1u << (e / L);
+        } else {
+          report(ws, kStatusBadExpertIndex, kPhaseDispatchSend, t, e);
+        }
+      }
+      for (int d = 0; d < world; ++d) {
+        if ((mask >> d) & 1u) atomicAdd(&nrec[d], 1u);
       }
     }
     __syncthreads();
@@ -223,18 +244,23 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
       if (d % cfg.dp_size != my_tp) continue;
       uint32_t v;
       if (j == 0) {
-        v = static_cast<uint32_t>(T);
+        v = nrec[d];
       } else {
         const int e = d * L + (j - 1);
         v = e < cfg.num_experts ? hist[e] : 0u;
       }
       uint32_t* dst = reinterpret_cast<uint32_t*>(st.sync[d] + cfg.off_counts) +
-                      my_group * cfg.counts_stride + j;
+                      par * cfg.counts_bank_words + my_group * cfg.counts_stride + j;
       st_stream_u32(dst, v);
     }
+    __syncthreads();
+    if (threadIdx.x < world) {
+      st_release_sys(flag_ptr(st.sync[threadIdx.x], kFlagDispatchStarted, st.rank), tag);
+    }
+    if (cfg.trace && threadIdx.x == 0) ws.trace[kTraceSendSignalled] = globaltimer_ns();
   }
 
-  // ---- token loop: one team per token; the record of token t goes to slot t ----
+  // ---- token loop: one team per token ----
   const uint32_t nvec = cfg.d_payload_bytes / 16;
   const int hs = cfg.hidden_dim_scale;
   constexpr int U = kCopyUnroll;
@@ -254,22 +280,39 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
       s_w[team.in_block][team.lane] = a.weights[t * a.weights_stride + team.lane];
     }
     team.sync();
-    uint32_t dst_mask = 0;
-    for (int k = 0; k < K; ++k) {
-      const uint32_t e = s_idx[team.in_block][k];
-      if (e < static_cast<uint32_t>(cfg.num_experts)) dst_mask |= 1u << (e / L);
+    // one slot per destination rank that owns at least one of the token's experts
+    uint32_t my_slot = kNoSlot;
+    if (team.lane < kMaxRanks) {
+      const int d = team.lane;
+      bool hit = false;
+      if (d < world && d % cfg.dp_size == my_tp) {
+        for (int k = 0; k < K; ++k) {
+          const uint32_t e = s_idx[team.in_block][k];
+          hit |= e < static_cast<uint32_t>(cfg.num_experts) && e / L == static_cast<uint32_t>(d);
+        }
+      }
+      if (hit) {
+        my_slot = atom_relaxed_gpu_add(&ws.send_cursor[par * kMaxRanks + d], 1u);
+        if (my_slot >= static_cast<uint32_t>(cfg.max_num_tokens)) {
+          report(ws, kStatusRecordOverflow, kPhaseDispatchSend, d, my_slot);
+          my_slot = kNoSlot;
+        }
+      }
+      s_slot[team.in_block][d] = my_slot;
     }
+    team.sync();
     uint8_t* rec[kMaxRanks];
     #pragma unroll
     for (int d = 0; d < kMaxRanks; ++d) {
-      const bool hit = d < world && ((dst_mask >> d) & 1u) && (d % cfg.dp_size == my_tp);
-      rec[d] = hit ? st.recv[d] + cfg.off_drecv + my_group * cfg.drecv_group_stride +
-                         static_cast<uint64_t>(t) * cfg.d_stride
+      const uint32_t slot = s_slot[team.in_block][d];
+      rec[d] = (d < world && slot != kNoSlot)
+                   ? st.recv[d] + cfg.off_drecv + my_group * cfg.drecv_group_stride +
+                         static_cast<uint64_t>(slot) * cfg.d_stride
                    : nullptr;
     }
 
-    // header (and, when the caller supplies them, the scales) as 16-byte stores: small
-    // stores cost a full NVLink packet each
+    // header (without its tag) and, when the caller supplies them, the scales as 16-byte
+    // stores: small stores cost a full NVLink packet each
     {
       const int hdr_vecs = cfg.d_header_bytes / 16;
       const int scale_vecs = (!a.quantize && hs > 0) ? cfg.d_scale_bytes / 16 : 0;
@@ -281,9 +324,10 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
           #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const int wi = 4 * vi + c;
-            if (wi == 0) word[c] = tag;
-            else if (wi <= K) word[c] = s_idx[team.in_block][wi - 1];
-            else if (wi <= 2 * K) word[c] = __float_as_uint(s_w[team.in_block][wi - 1 - K]);
+            if (wi == 0) word[c] = 0;  // the tag is written last, by the release below
+            else if (wi == 1) word[c] = static_cast<uint32_t>(t);
+            else if (wi < 2 + K) word[c] = s_idx[team.in_block][wi - 2];
+            else if (wi < 2 + 2 * K) word[c] = __float_as_uint(s_w[team.in_block][wi - 2 - K]);
             else word[c] = 0;
           }
           at = 16u * vi;
@@ -353,18 +397,17 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
         }
       }
     }
+    // The record is complete once every lane's stores are: the barrier makes them all
+    // "observed" by the lane that publishes the tag, and the release orders them before it.
     team.sync();
+    if (team.lane < kMaxRanks && my_slot != kNoSlot) {
+      uint8_t* mine = st.recv[team.lane] + cfg.off_drecv + my_group * cfg.drecv_group_stride +
+                      static_cast<uint64_t>(my_slot) * cfg.d_stride;
+      st_release_sys(reinterpret_cast<uint32_t*>(mine), tag);
+    }
   }
   trace_mark(cfg, ws, kTraceSendLoopDone);
-
-  // ---- arrival signal: one increment per block and destination ----
-  __syncthreads();
-  if (threadIdx.x < world && threadIdx.x % cfg.dp_size == my_tp) {
-    fence_acq_rel_sys();
-    red_release_sys_add(flag_ptr(st.sync[threadIdx.x], 0, my_group), 1u);
-  }
   if (threadIdx.x == 0 && blockIdx.x == 0) atomicAdd(&ws.stats[0], static_cast<unsigned long long>(T));
-  trace_mark(cfg, ws, kTraceSendSignalled);
 }
 
 // ---------------------------------------------------------------------------
@@ -386,6 +429,26 @@ __device__ __forceinline__ void compact_warp(bool valid, uint32_t va, uint32_t v
   if (lane == 0) *out_n = __popc(mask);
 }
 
+// Bounded wait until the word at `p` equals `want` (exact = true) or has reached it as a
+// counter (exact = false). Gives up when the time limit runs out or when another team of this
+// rank has already reported a failure.
+__device__ __forceinline__ bool wait_word(const uint32_t* p, uint32_t want, bool exact,
+                                          uint64_t limit_ns, const uint32_t* status) {
+  auto ok = [&](uint32_t v) { return exact ? v == want : static_cast<int32_t>(v - want) >= 0; };
+  if (ok(ld_acquire_sys(p))) return true;
+  const uint64_t start = globaltimer_ns();
+  for (;;) {
+    #pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      if (ok(ld_acquire_sys(p))) return true;
+    }
+    if (*reinterpret_cast<const volatile uint32_t*>(status) != 0) return false;
+    if (globaltimer_ns() - start > limit_ns) return false;
+  }
+}
+
+constexpr uint32_t kTeamAbort = 0xfffffffeu;
+
 __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
                                     const DispatchRecvArgs& a, uint32_t* dyn_smem, const int TEAM) {
   const A2ALocal& ws = st.local;
@@ -397,23 +460,24 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
   const uint32_t epoch = read_epoch(ws, 0);
   const uint32_t tag = epoch + 1;
   const uint32_t par = epoch & 1u;
-  const uint32_t expected = tag * gridDim.x;
   trace_mark(cfg, ws, kTraceRecvStart);
 
   __shared__ uint32_t s_abort;
-  __shared__ uint32_t s_slot_prefix[kMaxRanks + 1];
+  __shared__ uint32_t s_rec_prefix[kMaxRanks + 1];
   __shared__ uint32_t s_rows[kMaxTeams][kMaxTopK];
   __shared__ uint32_t s_unused[kMaxTeams][kMaxTopK];
   __shared__ uint32_t s_nrows[kMaxTeams];
 
   if (threadIdx.x == 0) s_abort = ws.status[0] != 0 ? 1u : 0u;
   __syncthreads();
-  if (threadIdx.x < G) {
+  // the counts message of this dispatch from every rank (ranks of another tensor-parallel
+  // lane send no counts here, only the word)
+  if (threadIdx.x < cfg.world) {
     uint64_t waited;
-    const bool ok = wait_flag(flag_ptr(st.sync[rank], 0, threadIdx.x), expected,
+    const bool ok = wait_flag(flag_ptr(st.sync[rank], kFlagDispatchStarted, threadIdx.x), tag,
                               cfg.wait_limit_ns, &waited);
     if (!ok) {
-      report(ws, kStatusWaitTimeout, kPhaseDispatchRecv, threadIdx.x, expected);
+      report(ws, kStatusWaitTimeout, kPhaseDispatchRecv, threadIdx.x, tag);
       s_abort = 1;
     }
     if (blockIdx.x == 0) atomicMax(&ws.stats[2], static_cast<unsigned long long>(waited));
@@ -428,7 +492,8 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
   uint32_t* total = base + G * L;     // [L]
   uint32_t* pad_off = total + L;      // [L]
   uint32_t* misc = pad_off + L;       // [0] padded row count
-  const uint32_t* counts = reinterpret_cast<const uint32_t*>(st.sync[rank] + cfg.off_counts);
+  const uint32_t* counts = reinterpret_cast<const uint32_t*>(st.sync[rank] + cfg.off_counts) +
+                           par * cfg.counts_bank_words;
   const uint32_t pad = static_cast<uint32_t>(cfg.expert_padding);
   if (!abort) {
     for (int i = threadIdx.x; i < G * L; i += blockDim.x) {
@@ -438,17 +503,15 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
     if (threadIdx.x == 0) {
       uint32_t acc = 0;
       for (int g = 0; g < G; ++g) {
-        s_slot_prefix[g] = acc;
+        s_rec_prefix[g] = acc;
         acc += min(ld_relaxed_sys(counts + g * cfg.counts_stride),
                    static_cast<uint32_t>(cfg.max_num_tokens));
       }
-      for (int g = G; g <= kMaxRanks; ++g) s_slot_prefix[g] = acc;
+      for (int g = G; g <= kMaxRanks; ++g) s_rec_prefix[g] = acc;
     }
     __syncthreads();
     // Warp 0 owns the layout: lane j covers a contiguous chunk of experts, sums the groups,
     // scans the padded totals across lanes and writes every (group, expert) base row.
-    // (With many experts per rank the per-lane chunks get long, but that is the
-    // small-world case where nothing else is latency critical.)
     if (threadIdx.x < 32) {
       const int per = (L + 31) / 32;
       const int lo = threadIdx.x * per;
@@ -496,48 +559,47 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
       }
       if (threadIdx.x == 0) {
         ws.expert_meta[0] = min(padded_rows, row_cap);
-        ws.expert_meta[1] = s_slot_prefix[G];
+        ws.expert_meta[1] = s_rec_prefix[G];
         if (padded_rows > row_cap) {
           report(ws, kStatusRowOverflow, kPhaseDispatchRecv, padded_rows, row_cap);
         }
       }
     }
 
-    // ---- slot loop: one team per (source group, source token) ----
+    // ---- record loop: one team per record, each consumed as soon as its tag is there ----
     const uint32_t nvec = cfg.d_payload_bytes / 16;
     const int hs = cfg.hidden_dim_scale;
-    const uint32_t total_slots = s_slot_prefix[G];
+    const uint32_t total_recs = s_rec_prefix[G];
     const uint8_t* drecv = st.recv[rank] + cfg.off_drecv;
     constexpr int U = kCopyUnroll;
-    // Wide teams have few slots each: fetch the payload together with the header
-    // instead of after it (a slot that turns out to be stale costs one wasted read).
-    const bool kSpeculate = TEAM >= 128;
-    for (uint32_t s = team.id; s < total_slots; s += team.count) {
+    for (uint32_t r = team.id; r < total_recs; r += team.count) {
       int g = 0;
       #pragma unroll
       for (int j = 1; j < kMaxRanks; ++j) {
-        if (j < G && s >= s_slot_prefix[j]) g = j;
+        if (j < G && r >= s_rec_prefix[j]) g = j;
       }
-      const uint32_t t = s - s_slot_prefix[g];
+      const uint32_t s = r - s_rec_prefix[g];
       const uint8_t* rec =
-          drecv + g * cfg.drecv_group_stride + static_cast<uint64_t>(t) * cfg.d_stride;
+          drecv + g * cfg.drecv_group_stride + static_cast<uint64_t>(s) * cfg.d_stride;
       const uint32_t* hdr = reinterpret_cast<const uint32_t*>(rec);
-      Vec16 v[U];
-      if (kSpeculate) {
-        #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const uint32_t i = team.lane + u * TEAM;
-          if (i < nvec) v[u] = ld_stream_v4(rec + cfg.d_header_bytes + 16ull * i);
-        }
-      }
       if (team.lane < 32) {
+        uint32_t ok = 1;
+        if (team.lane == 0) {
+          ok = wait_word(hdr, tag, true, cfg.wait_limit_ns, ws.status) ? 1u : 0u;
+          if (!ok) report(ws, kStatusWaitTimeout, kPhaseDispatchRecv, g, r);
+        }
+        __syncwarp();  // lane 0's acquire now covers the whole warp's reads of the record
+        ok = __shfl_sync(0xffffffffu, ok, 0);
         const int k = team.lane;
         uint32_t row = kNoSlot;
-        if (k < K) {
-          const uint32_t e = ld_relaxed_sys(hdr + 1 + k);
-          const bool fresh = ld_relaxed_sys(hdr) == tag;
-          if (fresh && e < static_cast<uint32_t>(cfg.num_experts) &&
-              e / L == static_cast<uint32_t>(rank)) {
+        const uint32_t t = ok ? ld_relaxed_sys(hdr + 1) : 0u;
+        if (ok && t >= static_cast<uint32_t>(cfg.max_num_tokens)) {
+          if (k == 0) report(ws, kStatusBadRecord, kPhaseDispatchRecv, g, t);
+          ok = 0;
+        }
+        if (ok && k < K) {
+          const uint32_t e = ld_relaxed_sys(hdr + 2 + k);
+          if (e < static_cast<uint32_t>(cfg.num_experts) && e / L == static_cast<uint32_t>(rank)) {
             const int le = e - rank * L;
             row = base[g * L + le] +
                   atom_relaxed_gpu_add(&ws.place_cursor[par * (G * L) + g * L + le], 1u);
@@ -549,29 +611,30 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
             }
           }
           if (cfg.combine_mode == kCombinePreReduce) {
-            ws.rec_rows[static_cast<uint64_t>(s) * K + k] = row;
-            ws.rec_weights[static_cast<uint64_t>(s) * K + k] =
-                __uint_as_float(ld_relaxed_sys(hdr + 1 + K + k));
+            ws.rec_rows[static_cast<uint64_t>(r) * K + k] = row;
+            ws.rec_weights[static_cast<uint64_t>(r) * K + k] =
+                __uint_as_float(ld_relaxed_sys(hdr + 2 + K + k));
             if (k == 0) {
-              ws.rec_token[2 * s] = t;
-              ws.rec_token[2 * s + 1] = g;
+              ws.rec_token[2 * r] = t;
+              ws.rec_token[2 * r + 1] = g;
             }
           }
         }
         compact_warp(row != kNoSlot, row, 0u, s_rows[team.in_block], s_unused[team.in_block],
                      &s_nrows[team.in_block]);
+        if (!ok && team.lane == 0) s_nrows[team.in_block] = kTeamAbort;
       }
       team.sync();
 
       const uint32_t nrows = s_nrows[team.in_block];
+      if (nrows == kTeamAbort) break;  // uniform across the team
       if (nrows != 0) {
         for (uint32_t i0 = team.lane; i0 < nvec; i0 += TEAM * U) {
-          if (!kSpeculate || i0 != static_cast<uint32_t>(team.lane)) {
-            #pragma unroll
-            for (int u = 0; u < U; ++u) {
-              const uint32_t i = i0 + u * TEAM;
-              if (i < nvec) v[u] = ld_stream_v4(rec + cfg.d_header_bytes + 16ull * i);
-            }
+          Vec16 v[U];
+          #pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const uint32_t i = i0 + u * TEAM;
+            if (i < nvec) v[u] = ld_stream_v4(rec + cfg.d_header_bytes + 16ull * i);
           }
           for (uint32_t j = 0; j < nrows; ++j) {
             uint8_t* dst =
@@ -599,7 +662,7 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
     }
   }
   trace_mark(cfg, ws, kTraceRecvLoopDone);
-  finish_recv(cfg, ws, 0, epoch, kTraceRecvAllDone);
+  finish_recv(cfg, ws, 0, epoch, kTraceRecvAllDone, false);
 }
 
 // ---------------------------------------------------------------------------
@@ -701,8 +764,15 @@ __device__ __forceinline__ void weighted_gather8(float (&acc)[8], const uint8_t*
   }
 }
 
+__device__ __forceinline__ uint32_t* tok_arrive_ptr(const A2AConfig& cfg, uint8_t* sync_base,
+                                                    uint32_t t) {
+  return reinterpret_cast<uint32_t*>(sync_base + cfg.off_tok_arrive) + t;
+}
+
 // Per-route mode: plain byte copy of each valid expert row to every member of the
-// origin dp group. Pre-reduce mode: weighted partial sum per received record.
+// origin dp group. Pre-reduce mode: weighted partial sum per received record. Either way
+// the team that wrote a row announces it at once on the arrival counter of the row's token
+// at the origin, so the origin reduces token by token while other rows are still in flight.
 template <typename Y>
 __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
                                    const CombineSendArgs& a, const int TEAM) {
@@ -734,7 +804,7 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
       }
       const uint32_t g = ws.row_src[row];
       const uint32_t tk = ws.row_tk[row];
-      if (g == kNoSlot) continue;
+      if (g == kNoSlot) continue;  // padding row; uniform across the team
       uint8_t* dst[kMaxRanks];
       #pragma unroll
       for (int m = 0; m < kMaxRanks; ++m) {
@@ -761,6 +831,10 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
           }
         }
       }
+      team.sync();
+      if (team.lane < cfg.dp_size) {
+        red_release_sys_add(tok_arrive_ptr(cfg, st.sync[g * cfg.dp_size + team.lane], tk / K), 1u);
+      }
     }
   } else if (healthy) {
     const uint32_t recs = ws.expert_meta[1];
@@ -780,58 +854,54 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
       }
       team.sync();
       const uint32_t n = s_n[team.in_block];
-      if (n != 0) {
-        const uint64_t slot = static_cast<uint64_t>(t) * cfg.world + st.rank;
-        constexpr int GB = 4;  // granules a thread carries at once: GB independent loads per row
-        for (uint32_t i0 = team.lane; i0 < ngran; i0 += TEAM * GB) {
-          float acc[GB][8];
+      // A record always yields a partial (zeros if none of its rows fitted): the origin counts
+      // one arrival per rank it sent the token to.
+      const uint64_t slot = static_cast<uint64_t>(t) * cfg.world + st.rank;
+      constexpr int GB = 4;  // granules a thread carries at once: GB independent loads per row
+      for (uint32_t i0 = team.lane; i0 < ngran; i0 += TEAM * GB) {
+        float acc[GB][8];
+        #pragma unroll
+        for (int u = 0; u < GB; ++u) {
+          #pragma unroll
+          for (int q = 0; q < 8; ++q) acc[u][q] = 0.f;
+        }
+        for (uint32_t j = 0; j < n; ++j) {
+          const uint8_t* row = a.expert_y + static_cast<uint64_t>(s_rows[team.in_block][j]) * a.expert_y_stride;
+          const float w = __uint_as_float(s_wbits[team.in_block][j]);
+          float f[GB][8];
           #pragma unroll
           for (int u = 0; u < GB; ++u) {
-            #pragma unroll
-            for (int q = 0; q < 8; ++q) acc[u][q] = 0.f;
-          }
-          for (uint32_t j = 0; j < n; ++j) {
-            const uint8_t* row = a.expert_y + static_cast<uint64_t>(s_rows[team.in_block][j]) * a.expert_y_stride;
-            const float w = __uint_as_float(s_wbits[team.in_block][j]);
-            float f[GB][8];
-            #pragma unroll
-            for (int u = 0; u < GB; ++u) {
-              const uint32_t i = i0 + u * TEAM;
-              if (i < ngran) Elem8<Y>::load(row + static_cast<uint64_t>(i) * Elem8<Y>::kBytes, f[u], false);
-            }
-            #pragma unroll
-            for (int u = 0; u < GB; ++u) {
-              const uint32_t i = i0 + u * TEAM;
-              if (i < ngran) {
-                #pragma unroll
-                for (int q = 0; q < 8; ++q) acc[u][q] = fmaf(w, f[u][q], acc[u][q]);
-              }
-            }
+            const uint32_t i = i0 + u * TEAM;
+            if (i < ngran) Elem8<Y>::load(row + static_cast<uint64_t>(i) * Elem8<Y>::kBytes, f[u], false);
           }
           #pragma unroll
           for (int u = 0; u < GB; ++u) {
             const uint32_t i = i0 + u * TEAM;
             if (i < ngran) {
-              for (int m = 0; m < cfg.dp_size; ++m) {
-                Elem8<Y>::store(st.recv[g * cfg.dp_size + m] + cfg.off_crecv + slot * cfg.c_stride +
-                                    static_cast<uint64_t>(i) * Elem8<Y>::kBytes,
-                                acc[u]);
-              }
+              #pragma unroll
+              for (int q = 0; q < 8; ++q) acc[u][q] = fmaf(w, f[u][q], acc[u][q]);
+            }
+          }
+        }
+        #pragma unroll
+        for (int u = 0; u < GB; ++u) {
+          const uint32_t i = i0 + u * TEAM;
+          if (i < ngran) {
+            for (int m = 0; m < cfg.dp_size; ++m) {
+              Elem8<Y>::store(st.recv[g * cfg.dp_size + m] + cfg.off_crecv + slot * cfg.c_stride +
+                                  static_cast<uint64_t>(i) * Elem8<Y>::kBytes,
+                              acc[u]);
             }
           }
         }
       }
       team.sync();
+      if (team.lane < cfg.dp_size) {
+        red_release_sys_add(tok_arrive_ptr(cfg, st.sync[g * cfg.dp_size + team.lane], t), 1u);
+      }
     }
   }
   trace_mark(cfg, ws, kTraceCSendLoopDone);
-
-  __syncthreads();
-  if (threadIdx.x < cfg.world) {
-    fence_acq_rel_sys();
-    red_release_sys_add(flag_ptr(st.sync[threadIdx.x], 1, st.rank), 1u);
-  }
-  trace_mark(cfg, ws, kTraceCSendSignalled);
 }
 
 // ---------------------------------------------------------------------------
@@ -839,7 +909,7 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
 // ---------------------------------------------------------------------------
 
 // Source slots (and weights) of token t, compacted into shared memory by the first warp
-// of the team.
+// of the team. *out_n is also the number of arrivals the token waits for.
 __device__ __forceinline__ void combine_sources(const A2AConfig& cfg, const CombineRecvArgs& a,
                                                 int t, uint32_t* out_slot, uint32_t* out_wbits,
                                                 uint32_t* out_n) {
@@ -878,7 +948,6 @@ __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
   const A2ALocal& ws = st.local;
   const Team team(TEAM);
   const uint32_t epoch = read_epoch(ws, 1);
-  const uint32_t expected = (epoch + 1) * gridDim.x;
   trace_mark(cfg, ws, kTraceCRecvStart);
 
   __shared__ uint32_t s_abort;
@@ -892,37 +961,48 @@ __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
 
   if (threadIdx.x == 0) s_abort = ws.status[0] != 0 ? 1u : 0u;
   __syncthreads();
-  // The routing of the first token is local input: read it while the flags are polled.
-  const int t_first = team.id;
-  if (team.lane < 32 && t_first < T) {
-    combine_sources(cfg, a, t_first, s_slot[team.in_block], s_wbits[team.in_block],
-                    &s_n[team.in_block]);
-  }
-  if (threadIdx.x < cfg.world) {
-    uint64_t waited;
-    const bool ok = wait_flag(flag_ptr(st.sync[st.rank], 1, threadIdx.x), expected,
-                              cfg.wait_limit_ns, &waited);
-    if (!ok) {
-      report(ws, kStatusWaitTimeout, kPhaseCombineRecv, threadIdx.x, expected);
-      s_abort = 1;
+  if (a.external) {
+    // the sending kernels announce a whole rank's rows at once
+    const uint32_t expected = read_epoch(ws, 2) + 1;
+    if (threadIdx.x < cfg.world) {
+      uint64_t waited;
+      const bool ok = wait_flag(flag_ptr(st.sync[st.rank], kFlagExternalCombine, threadIdx.x),
+                                expected, cfg.wait_limit_ns, &waited);
+      if (!ok) {
+        report(ws, kStatusWaitTimeout, kPhaseCombineRecv, threadIdx.x, expected);
+        s_abort = 1;
+      }
+      if (blockIdx.x == 0) atomicMax(&ws.stats[3], static_cast<unsigned long long>(waited));
     }
-    if (blockIdx.x == 0) atomicMax(&ws.stats[3], static_cast<unsigned long long>(waited));
+    __syncthreads();
   }
-  __syncthreads();
   trace_mark(cfg, ws, kTraceCRecvWaitDone);
 
   if (s_abort == 0) {
     const uint8_t* crecv = st.recv[st.rank] + cfg.off_crecv;
     const uint32_t ngran = cfg.hidden_dim / 8;
-    for (int t = t_first; t < T; t += team.count) {
-      if (t != t_first) {
-        if (team.lane < 32) {
-          combine_sources(cfg, a, t, s_slot[team.in_block], s_wbits[team.in_block],
-                          &s_n[team.in_block]);
+    for (int t = team.id; t < T; t += team.count) {
+      if (team.lane < 32) {
+        combine_sources(cfg, a, t, s_slot[team.in_block], s_wbits[team.in_block],
+                        &s_n[team.in_block]);
+        __syncwarp();
+        if (team.lane == 0 && !a.external) {
+          const uint32_t n = s_n[team.in_block];
+          uint32_t* counter = tok_arrive_ptr(cfg, st.sync[st.rank], static_cast<uint32_t>(t));
+          if (n != 0) {
+            if (wait_word(counter, n, false, cfg.wait_limit_ns, ws.status)) {
+              // the next rows for this token come after this rank's next dispatch
+              *reinterpret_cast<volatile uint32_t*>(counter) = 0;
+            } else {
+              report(ws, kStatusWaitTimeout, kPhaseCombineRecv, t, n);
+              s_n[team.in_block] = kTeamAbort;
+            }
+          }
         }
-        team.sync();
       }
+      team.sync();
       const uint32_t n = s_n[team.in_block];
+      if (n == kTeamAbort) break;  // uniform across the team
       uint8_t* out_row = a.out_tokens + static_cast<uint64_t>(t) * a.out_tokens_stride * sizeof(O);
       for (uint32_t i = team.lane; i < ngran; i += TEAM) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -938,7 +1018,7 @@ __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
     }
   }
   trace_mark(cfg, ws, kTraceCRecvLoopDone);
-  finish_recv(cfg, ws, 1, epoch, kTraceCRecvAllDone);
+  finish_recv(cfg, ws, 1, epoch, kTraceCRecvAllDone, a.external != 0);
 }
 
 // ---------------------------------------------------------------------------
@@ -984,8 +1064,29 @@ combine_kernel(const __grid_constant__ A2AConfig cfg, const __grid_constant__ A2
   combine_recv_phase<Y, O>(cfg, states.r[blockIdx.y], recv.r[blockIdx.y], recv_team);
 }
 
+// Every rank announces itself on every rank's barrier counters and waits until it has heard
+// from all of them. One block per rank; used to line ranks up (benchmarks, tests, teardown),
+// never inside dispatch or combine.
+__global__ void __launch_bounds__(32, 1)
+barrier_kernel(const __grid_constant__ A2AConfig cfg, const __grid_constant__ A2ARankStates states) {
+  const A2ARankState& st = states.r[blockIdx.y];
+  const A2ALocal& ws = st.local;
+  const uint32_t expected = read_epoch(ws, 3) + 1;
+  __syncwarp();
+  if (threadIdx.x < cfg.world) {
+    red_release_sys_add(flag_ptr(st.sync[threadIdx.x], kFlagBarrier, st.rank), 1u);
+    uint64_t waited;
+    if (!wait_flag(flag_ptr(st.sync[st.rank], kFlagBarrier, threadIdx.x), expected,
+                   cfg.wait_limit_ns, &waited)) {
+      report(ws, kStatusWaitTimeout, kNumPhases, threadIdx.x, expected);
+    }
+  }
+  __syncwarp();
+  if (threadIdx.x == 0) ws.epochs[3] = expected;
+}
+
 size_t dispatch_smem_bytes(const A2AConfig& cfg) {
-  const size_t send = cfg.num_experts * sizeof(uint32_t);
+  const size_t send = (cfg.num_experts + kMaxRanks) * sizeof(uint32_t);
   const size_t gl = static_cast<size_t>(cfg.num_groups) * cfg.experts_per_rank;
   const size_t recv = (2 * gl + 2 * cfg.experts_per_rank + 32) * sizeof(uint32_t);
   return send > recv ? send : recv;
@@ -1052,6 +1153,19 @@ cudaError_t a2a_launch_dispatch(const A2AConfig& cfg, const A2ARankStates& state
   const bool cooperative = nranks > 1 && send_team && recv_team;
   return launch(dispatch_kernel, grid, smem, stream, cooperative, cfg, states, send, recv,
                 send_team, recv_team);
+}
+
+cudaError_t a2a_launch_barrier(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
+                               cudaStream_t stream) {
+  void* params[] = {const_cast<void*>(static_cast<const void*>(&cfg)),
+                    const_cast<void*>(static_cast<const void*>(&states))};
+  const dim3 grid(1, nranks);
+  if (nranks > 1) {
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(barrier_kernel), grid, dim3(32),
+                                       params, 0, stream);
+  }
+  return cudaLaunchKernel(reinterpret_cast<const void*>(barrier_kernel), grid, dim3(32), params, 0,
+                          stream);
 }
 
 cudaError_t a2a_launch_combine(const A2AConfig& cfg, const A2ARankStates& states, int nranks,

@@ -20,6 +20,10 @@ cudaError_t a2a_launch_dispatch(const A2AConfig& cfg, const A2ARankStates& state
                                 const PerRank<DispatchRecvArgs>& recv, int send_team, int recv_team,
                                 cudaStream_t stream);
 
+// All ranks of the context meet on the device (bounded wait, reported through the status word).
+cudaError_t a2a_launch_barrier(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
+                               cudaStream_t stream);
+
 cudaError_t a2a_launch_combine(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
                                const PerRank<CombineSendArgs>& send,
                                const PerRank<CombineRecvArgs>& recv, int send_team, int recv_team,

@@ -3,8 +3,11 @@
 // The protocol is device-only: every rank owns a *symmetric* region (same layout
 // on every rank, mapped into every peer over NVLink) made of
 //
-//   flags    one 128-byte line per (phase, source): cumulative arrival counters
-//   counts   per source dp-group: {#records, per-local-expert token counts}
+//   flags    one 128-byte line per (kind, source rank): "dispatch n has started here"
+//            words, arrival counters of externally sent combines, barrier counters
+//   counts   two banks (dispatch parity) x source dp-group: {#records for this rank,
+//            per-local-expert token counts}
+//   tokens   one arrival counter per local token: combine rows that have landed
 //   drecv    dispatch records, one fixed-capacity region per source dp-group
 //   crecv    combine records, indexed by the origin's (token, k) or (token, rank)
 //
@@ -12,11 +15,15 @@
 // the experts of that rank on arrival:
 //
 //   [ header | payload (hidden * in_elemsize, 16-byte padded) | scales ]
-//   header words: [0] epoch tag (dispatch number + 1), [1..K] expert ids, [1+K..2K]
-//   fp32 routing weights; padded to 16 bytes.
-// The record of source token t always lives in slot t of its source's region, so the
-// sender needs no slot allocation; the tag tells the receiver which slots were written
-// by the current dispatch (regions are zero-filled once, tags start at 1).
+//   header words: [0] epoch tag (dispatch number + 1), [1] source token, [2..2+K) expert
+//   ids, [2+K..2+2K) fp32 routing weights; padded to 16 bytes.
+// The sender packs the records for one destination densely (slot = an atomic cursor per
+// destination) and tells the destination how many there are in the counts message, which
+// leaves before any payload. The tag is the last word of a record to be written, with
+// release semantics: a receiver that sees the current tag in a slot may read that record
+// at once, without waiting for any other (regions are zero-filled once, tags start at 1).
+// A combine row is announced the same way, by a release-scoped increment of the arrival
+// counter of its token at the origin, so token t is reduced as soon as its rows are in.
 //
 // The reference sends one copy per route and keeps a 16-byte reserved trailer
 // instead (p2p-all-to-all/a2a-kernels/src/a2a/a2a_dispatch_send.cu:586-588,
@@ -54,6 +61,14 @@ enum A2ATrace : int {
   kTraceSlots = 16,
 };
 
+// Rows of the flag table at the start of the sync region (one 128-byte line per source rank).
+enum A2AFlagRow : int {
+  kFlagDispatchStarted = 0,  // tag of the newest dispatch whose counts message rank s sent here
+  kFlagExternalCombine = 1,  // combines whose send phase another kernel of rank s played
+  kFlagBarrier = 2,          // barriers rank s has entered
+  kNumFlagRows = 3,
+};
+
 // Values of status[0]. status[1] = phase, status[2] = peer/group, status[3] = detail.
 enum A2AStatus : uint32_t {
   kStatusOk = 0,
@@ -61,6 +76,7 @@ enum A2AStatus : uint32_t {
   kStatusRowOverflow = 2,     // more expert rows than the output tensor holds
   kStatusBadExpertIndex = 3,  // indices[t][k] >= num_experts
   kStatusRecordOverflow = 4,  // more records than a source region holds
+  kStatusBadRecord = 5,       // a record header names a token or count outside its limits
 };
 
 enum A2ACombineMode : int {
@@ -98,7 +114,10 @@ struct A2AConfig {
 
   // symmetric layout, byte offsets
   uint64_t sync_bytes;
-  uint64_t off_counts;          // inside the sync region
+  uint64_t off_counts;          // inside the sync region; two banks of counts_bank_words
+  uint64_t off_tok_arrive;      // inside the sync region; [max_num_tokens] u32
+  uint32_t counts_bank_words;   // num_groups * counts_stride
+  uint32_t pad0_;
   uint64_t recv_bytes;
   uint64_t off_drecv;           // inside the recv region
   uint64_t drecv_group_stride;
@@ -109,9 +128,11 @@ struct A2AConfig {
 
 // Device-local (not peer visible) workspace of one rank.
 struct A2ALocal {
-  uint32_t* epochs;        // [0] completed dispatches, [1] completed combines; advanced by
-                           // the last block of the respective *recv* phase
+  uint32_t* epochs;        // [0] completed dispatches, [1] completed combines, [2] of those the
+                           // ones whose send was external; advanced by the last block of the
+                           // respective *recv* phase. [3] barriers entered.
   uint32_t* done;          // [2] blocks that finished the current recv phase
+  uint32_t* send_cursor;   // [2][kMaxRanks] next free record slot per destination, by parity
   uint32_t* place_cursor;  // [2][num_groups * experts_per_rank], indexed by epoch parity
   uint32_t* row_src;       // [max_recv_rows] source dp group of a row, kNoSlot = padding
   uint32_t* row_tk;        // [max_recv_rows] token * topk + k at the source
@@ -180,6 +201,9 @@ struct CombineRecvArgs {
   const int32_t* bound_m;
   int32_t num_tokens;
   int32_t accumulate;
+  int32_t external;  // 1: the rows were written by another kernel, which announced them per
+                     // source rank (kFlagExternalCombine) instead of per token
+  int32_t pad_;
 };
 
 template <typename T>

@@ -71,6 +71,8 @@ py::dict config_dict(const A2AConfig& c) {
   d["max_recv_rows"] = c.max_recv_rows;
   d["sync_bytes"] = c.sync_bytes;
   d["off_counts"] = c.off_counts;
+  d["off_tok_arrive"] = c.off_tok_arrive;
+  d["counts_bank_words"] = c.counts_bank_words;
   d["recv_bytes"] = c.recv_bytes;
   d["off_drecv"] = c.off_drecv;
   d["drecv_group_stride"] = c.drecv_group_stride;
@@ -423,6 +425,13 @@ void bind_a2a(py::module_& m) {
              s.after_launch();
            },
            py::arg("send"), py::arg("recv"), py::arg("expert_y_dtype"), py::arg("stream"))
+      .def("barrier",
+           [](PyA2A& s, uint64_t stream) {
+             s.ctx->barrier(as_stream(stream));
+             s.after_launch();
+           },
+           py::arg("stream"),
+           "Device-side barrier over all ranks of the context (collective, stream ordered).")
       .def("failed", [](const PyA2A& s) { return s.ctx->failed(); })
       .def("check", [](const PyA2A& s) { s.ctx->check(); })
       .def("status",

@@ -37,7 +37,8 @@ namespace {
 struct FdServer {
   std::mutex mu;
   std::set<int> fds;
-  std::string name;
+  std::string name;    // bound (abstract) socket name; visible to every local user
+  uint64_t token = 0;  // secret of this process: travels only inside export handles
   int listen_fd = -1;
   int stop_fd = -1;
   std::thread thread;
@@ -67,6 +68,7 @@ struct FdServer {
     if (started) return;
     std::random_device rd;
     name = "pplx-cumem-" + std::to_string(getpid()) + "-" + std::to_string(rd());
+    token = (static_cast<uint64_t>(rd()) << 32) ^ rd();
     listen_fd = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
     if (listen_fd < 0) throw Error::from_errno("socket(AF_UNIX)");
     sockaddr_un addr;
@@ -86,13 +88,26 @@ struct FdServer {
     started = true;
   }
 
+  // The name of an abstract socket can be read from /proc/net/unix by any local user, so a
+  // connection proves nothing. A descriptor is handed out only to a peer that runs under this
+  // process's user id (SO_PEERCRED, filled in by the kernel) and that presents the token carried
+  // by the export handle; everybody else gets payload 0 and no descriptor.
   void serve_one(int conn) {
-    int32_t wanted = -1;
-    if (recv(conn, &wanted, sizeof(wanted), MSG_WAITALL) != sizeof(wanted)) return;
+    struct Request {
+      int32_t wanted;
+      uint32_t pad;
+      uint64_t token;
+    } req{-1, 0, 0};
+    if (recv(conn, &req, sizeof(req), MSG_WAITALL) != sizeof(req)) return;
+    const int32_t wanted = req.wanted;
+    ucred cred{};
+    socklen_t cred_len = sizeof(cred);
+    const bool same_user = getsockopt(conn, SOL_SOCKET, SO_PEERCRED, &cred, &cred_len) == 0 &&
+                           cred.uid == geteuid();
     bool known;
     {
       std::lock_guard<std::mutex> lock(mu);
-      known = fds.count(wanted) != 0;
+      known = same_user && req.token == token && fds.count(wanted) != 0;
     }
     char payload = known ? 1 : 0;
     iovec iov{&payload, 1};
@@ -150,7 +165,12 @@ int fetch_by_pidfd(int pid, int fd) {
   return got < 0 ? -err : got;
 }
 
-int fetch_by_socket(int fd, const std::string& socket_name) {
+int fetch_by_socket(int fd, const std::string& name_and_token) {
+  // "<socket name>:<token in hex>", as fd_server_name() returns it
+  const size_t colon = name_and_token.rfind(':');
+  const std::string socket_name = name_and_token.substr(0, colon);
+  uint64_t token = 0;
+  if (colon != std::string::npos) token = std::strtoull(name_and_token.c_str() + colon + 1, nullptr, 16);
   const int s = socket(AF_UNIX, SOCK_STREAM | SOCK_CLOEXEC, 0);
   if (s < 0) return -errno;
   sockaddr_un addr;
@@ -163,7 +183,11 @@ int fetch_by_socket(int fd, const std::string& socket_name) {
     close(s);
     return -e;
   }
-  const int32_t wanted = fd;
+  struct Request {
+    int32_t wanted;
+    uint32_t pad;
+    uint64_t token;
+  } wanted{fd, 0, token};
   if (send(s, &wanted, sizeof(wanted), MSG_NOSIGNAL) != sizeof(wanted)) {
     const int e = errno;
     close(s);
@@ -196,7 +220,9 @@ int fetch_by_socket(int fd, const std::string& socket_name) {
 
 std::string fd_server_name() {
   fd_server().start();
-  return fd_server().name;
+  char hex[32];
+  std::snprintf(hex, sizeof(hex), ":%016llx", static_cast<unsigned long long>(fd_server().token));
+  return fd_server().name + hex;
 }
 
 void fd_server_register(int fd) {

@@ -368,7 +368,15 @@ void LocalDomain::handle(Message& msg, std::vector<DomainCompletion>* out) {
           c.error = failure;
           out->push_back(std::move(c));
         } else {
-          run_write(w, rr, out);
+          try {
+            run_write(w, rr, out);
+          } catch (const std::exception& e) {
+            DomainCompletion c;
+            c.kind = DomainCompletion::Kind::kError;
+            c.transfer_id = w.id;
+            c.error = e.what();
+            out->push_back(std::move(c));
+          }
         }
       }
       if (!failure.empty()) remotes_.erase(key);
@@ -564,20 +572,52 @@ void LocalDomain::run_write(const PendingWrite& w, RemoteRegion& rr, std::vector
   const size_t num_pages = page_end - page_begin;
   auto src_page = [&](size_t i) { return src_pages ? (*src_pages)[page_begin + i] : 0u; };
   auto dst_page = [&](size_t i) { return dst_pages ? (*dst_pages)[page_begin + i] : 0u; };
-  // bounds of the destination
+  // Bounds of both sides, checked on the host before anything is enqueued: an index, stride
+  // or offset that leaves a registered region would otherwise become an out-of-range device
+  // access (the RDMA providers of the reference get this check from the lkey / rkey).
+  auto span_end = [](uint64_t page, uint64_t stride, uint64_t offset, uint64_t len, uint64_t* end) {
+    unsigned __int128 e = static_cast<unsigned __int128>(page) * stride;
+    e += offset;
+    e += len;
+    if (e > UINT64_MAX) return false;
+    *end = static_cast<uint64_t>(e);
+    return true;
+  };
   for (size_t i = 0; i < num_pages && length > 0; ++i) {
-    const uint64_t end = dst_page(i) * dst_stride + dst_offset + length;
-    if (end > rr.len) throw Error(ErrorKind::kDomain, "write past the end of the destination region");
+    uint64_t end = 0;
+    if (!span_end(dst_page(i), dst_stride, dst_offset, length, &end) || end > rr.len) {
+      throw Error(ErrorKind::kDomain, "write past the end of the destination region");
+    }
   }
 
-  // source region (for its device)
+  // source region: its device, and its extent
   int src_device = -1;
   {
-    std::lock_guard<std::mutex> lock(regions_mu_);
-    auto it = regions_.upper_bound(src_base);
-    if (it != regions_.begin()) {
-      --it;
-      if (src_base < it->second.ptr + it->second.len) src_device = it->second.device;
+    uint64_t region_ptr = 0, region_len = 0;
+    bool found = false;
+    {
+      std::lock_guard<std::mutex> lock(regions_mu_);
+      auto it = regions_.upper_bound(src_base);
+      if (it != regions_.begin()) {
+        --it;
+        if (src_base < it->second.ptr + it->second.len) {
+          src_device = it->second.device;
+          region_ptr = it->second.ptr;
+          region_len = it->second.len;
+          found = true;
+        }
+      }
+    }
+    if (!found && length > 0 && num_pages > 0) {
+      throw Error(ErrorKind::kDomain, "the source of a write is not inside a registered region");
+    }
+    const uint64_t base_off = src_base - region_ptr;
+    for (size_t i = 0; i < num_pages && length > 0; ++i) {
+      uint64_t end = 0;
+      if (!span_end(src_page(i), src_stride, src_offset, length, &end) || end > region_len ||
+          base_off > region_len - end) {
+        throw Error(ErrorKind::kDomain, "read past the end of the source region");
+      }
     }
   }
 

@@ -173,6 +173,9 @@ class LocalAllToAllGroup:
         so they may run one after the other on this GPU."""
         return [(*d, 1) if bulk else d for d in self.context.combine_send_external()]
 
+    def barrier(self) -> None:
+        self.context.barrier(torch.cuda.current_stream().cuda_stream)
+
     def check(self) -> None:
         if self.context.failed():
             self.context.check()

@@ -349,6 +349,15 @@ class P2PAllToAll(AllToAllKernel):
             a2a.combine_recv(num_tokens, expert_y.shape[0], expert_y.dtype, *recv)
 
     # ------------------------------------------------------------------
+    def barrier(self) -> None:
+        """Device-side barrier of all ranks on the current stream: a one-block kernel that
+        announces this rank on every peer and waits (bounded) for all of them. Collective.
+        Cheaper and much tighter than an NCCL all-reduce for lining ranks up."""
+        a2a = self._all_to_all
+        assert a2a is not None
+        a2a.barrier(torch.cuda.current_stream().cuda_stream)
+
+    # ------------------------------------------------------------------
     def combine_send_external(self, bulk: bool = False) -> tuple:
         """Let another kernel play the combine's send phase. Returns the descriptor that
         ``pplx_garden.ops.grouped_fp8_gemm(..., mode=MODE_BF16_SCATTER, scatter=...)`` takes: the

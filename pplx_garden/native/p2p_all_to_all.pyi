@@ -115,6 +115,7 @@ class AllToAllContext:
     def combine_multi(
         self, send: list[tuple] | None, recv: list[tuple] | None, expert_y_dtype: torch.dtype, stream: int
     ) -> None: ...
+    def barrier(self, stream: int) -> None: ...
     def failed(self) -> bool: ...
     def check(self) -> None: ...
     def status(self, local_rank: int = 0) -> tuple[int, int, int, int, str]: ...

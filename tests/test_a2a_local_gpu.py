@@ -337,3 +337,29 @@ def test_cuda_graph_replay_of_a_whole_layer() -> None:
         assert list(group.context.iterations(0)) == [5, 5]   # 1 eager + 4 replays (capturing runs nothing)
     finally:
         group.destroy()
+
+
+def test_barrier_and_rejected_call_leaves_phase_order_intact() -> None:
+    """The device barrier returns on every emulated rank; a dispatch that the host rejects
+    (too many tokens) does not advance the phase order, so a corrected call may follow."""
+    cfg = Cfg(world=4, tokens=8, experts=8, hidden=64, topk=2)
+    device = torch.device("cuda", 0)
+    group = _make_group(cfg, device)
+    try:
+        for _ in range(3):
+            group.barrier()
+        torch.cuda.synchronize()
+        group.check()
+        data = _inputs(cfg, device)
+        num, ox, os_, out = _outputs(cfg, group, device)
+        too_many = [torch.zeros((cfg.tokens + 1, cfg.hidden), device=device) for _ in range(cfg.world)]
+        with pytest.raises((ValueError, RuntimeError)):
+            group.dispatch(num, ox, os_, too_many, None, [d.indices for d in data],
+                           [d.weights for d in data])
+        num, ox, os_, out = _run_once(cfg, group, data, device)
+        _verify(cfg, data, num, ox, os_, out)
+        group.barrier()
+        torch.cuda.synchronize()
+        group.check()
+    finally:
+        group.destroy()

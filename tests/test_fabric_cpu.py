@@ -147,6 +147,30 @@ def test_out_of_bounds_write_is_an_error(pair) -> None:
     assert w.event.wait(5) and w.errors and "past the end" in w.errors[0]
 
 
+def test_out_of_bounds_source_is_an_error(pair) -> None:
+    """The source side is range-checked on the host too: an offset, a page index or a stride
+    that leaves the registered source region ends in the error callback and copies nothing."""
+    a, b = pair
+    src = torch.full((4096,), 5, dtype=torch.uint8)
+    dst = torch.zeros(16384, dtype=torch.uint8)
+    hs, _ = a.register_tensor(src)
+    _, dd = b.register_tensor(dst)
+    w = Waiter()
+    a.submit_write(hs, 4096 - 32, 64, None, dd, 0, w.done, w.error, 1)          # offset + length
+    assert w.event.wait(5) and w.errors and "source region" in w.errors[0]
+    w = Waiter()
+    a.submit_paged_writes(1024, hs, PageIndices([0, 4]), 1024, 0, dd, PageIndices([0, 1]), 1024, 0,
+                          None, w.done, w.error)                                # page index
+    assert w.event.wait(5) and w.errors and "source region" in w.errors[0]
+    w = Waiter()
+    a.submit_paged_writes(1024, hs, PageIndices([1]), 1 << 63, 0, dd, PageIndices([0]), 1024, 0,
+                          None, w.done, w.error)                                # stride overflow
+    assert w.event.wait(5) and w.errors
+    # pages are spread over the domains: the valid page of the second request may have been
+    # copied by its domain, nothing else
+    assert int(dst[1024:].count_nonzero()) == 0
+
+
 def test_paged_write_with_counted_immediates(pair) -> None:
     a, b = pair
     page, n_pages = 4096, 64

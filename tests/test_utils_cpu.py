@@ -120,6 +120,31 @@ def test_fd_fetch_refuses_an_unregistered_descriptor():
         proc.join(timeout=20)
 
 
+def test_fd_fetch_refuses_a_peer_without_the_token():
+    """The socket's name is public (/proc/net/unix); the descriptor server only answers a peer
+    that presents the secret carried by the export handle (and runs under the same user)."""
+    ctx = mp.get_context("spawn")
+    parent, child = ctx.Pipe()
+    proc = ctx.Process(target=_exporter, args=(child,))
+    proc.start()
+    try:
+        pid, fd, name = parent.recv()
+        public_name, token = name.rsplit(":", 1)
+        _native._fd_fetch_set_mode("socket")
+        for forged in (public_name, public_name + ":0", public_name + ":" + "f" * 16):
+            if forged.endswith(token):
+                continue
+            with pytest.raises(Exception):
+                _native._fd_fetch(pid, fd, forged)
+        got = _native._fd_fetch(pid, fd, name)    # the real handle still works afterwards
+        assert os.read(got, 64) == b"through the fence"
+        os.close(got)
+    finally:
+        _native._fd_fetch_set_mode("auto")
+        parent.send("done")
+        proc.join(timeout=20)
+
+
 def test_fd_fetch_inside_one_process_duplicates():
     r, w = os.pipe()
     os.write(w, b"x")
