@@ -31,8 +31,12 @@
 //     Nothing in it has to start out zeroed: a call overwrites the entries it reads before
 //     the kernel runs. Two calls that may overlap on the GPU (different streams without an
 //     ordering between them) race on the array; order them, e.g. by using one stream.
-//   * The work is enqueued on `stream` and is asynchronous like any kernel launch; the host
-//     page tables may be reused as soon as the call returns.
+//   * The work is enqueued on `stream` and is asynchronous like any kernel launch. The two
+//     host page tables are read by two cudaMemcpyAsync calls on `stream`. Tables in pageable
+//     memory (malloc, a Python list turned into a ctypes array) are staged by the runtime
+//     before the call returns and may be reused at once. Tables in pinned or registered host
+//     memory are read when the stream reaches the copies: keep them unchanged until then
+//     (an event or a stream synchronisation after the call tells you).
 //   * No cudaMalloc, cudaFree or other allocating routine is called.
 //
 // Returns 0 on success, a cudaError_t value when a CUDA call failed, -1 for invalid

@@ -93,3 +93,27 @@ def test_no_alloc_paged_copy_rejects_oversized_requests() -> None:
     pages = (ctypes.c_uint32 * 1)(0)
     rc = lib.pplx_paged_copy_noalloc(buf.data_ptr(), buf.data_ptr(), pages, pages, limit + 1, 0, 0, 0, 0, 16, None)
     assert rc == -1 and b"exceed the limit" in lib.pplx_noalloc_last_error()
+
+
+def test_no_alloc_paged_copy_with_pinned_page_tables() -> None:
+    """Page tables in pinned host memory are read when the stream gets to them, not when the
+    call returns: the caller keeps them unchanged until a synchronisation, as the header says."""
+    lib = _load()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    page, n = 4096, 24
+    src = torch.randint(0, 255, (n * page,), dtype=torch.uint8, device=dev)
+    got = torch.zeros(n * page, dtype=torch.uint8, device=dev)
+    order = torch.randperm(n, generator=torch.Generator().manual_seed(3)).to(torch.int32)
+    src_tab = torch.arange(n, dtype=torch.int32).pin_memory()
+    dst_tab = order.clone().pin_memory()
+    u32p = ctypes.POINTER(ctypes.c_uint32)
+    rc = lib.pplx_paged_copy_noalloc(src.data_ptr(), got.data_ptr(),
+                                     ctypes.cast(src_tab.data_ptr(), u32p),
+                                     ctypes.cast(dst_tab.data_ptr(), u32p), n, page, page, 0, 0, page,
+                                     torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.pplx_noalloc_last_error().decode()
+    torch.cuda.synchronize()        # only now may src_tab / dst_tab change
+    want = torch.zeros_like(got)
+    want.view(n, page)[order.long().to(dev)] = src.view(n, page)
+    assert torch.equal(got, want)
