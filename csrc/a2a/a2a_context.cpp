@@ -61,11 +61,29 @@ A2AConfig a2a_make_config(const A2AParams& p, int num_sms, int virtual_ranks) {
   if (blocks <= 0) blocks = std::max(1, num_sms / virtual_ranks);
   c.num_blocks = blocks;
 
+  int wire = p.wire;
+  if (wire == kWireAuto) {
+    const char* env = std::getenv("PPLX_A2A_WIRE");
+    if (env != nullptr && std::strcmp(env, "ll") == 0) wire = kWireLL;
+    else if (env != nullptr && std::strcmp(env, "plain") == 0) wire = kWirePlain;
+    else wire = p.max_num_tokens <= 512 ? kWireLL : kWirePlain;
+  }
+  PPLX_REQUIRE(wire == kWirePlain || wire == kWireLL, "wire must be 'plain' or 'll'");
+  c.wire = wire;
+
   c.d_header_bytes = round_up_u32(4u * (2 + 2 * p.topk), 16);
   c.d_payload_bytes = static_cast<uint32_t>(p.hidden_dim) * p.in_elemsize;
   c.d_scale_bytes = round_up_u32(static_cast<uint32_t>(p.hidden_dim_scale) * 4u, 16);
-  c.d_stride = round_up_u32(c.d_header_bytes + c.d_payload_bytes + c.d_scale_bytes, 128);
-  c.c_stride = round_up_u32(static_cast<uint32_t>(p.hidden_dim) * p.out_elemsize, 16);
+  const uint32_t c_row_bytes = round_up_u32(static_cast<uint32_t>(p.hidden_dim) * p.out_elemsize, 16);
+  if (wire == kWireLL) {
+    // seven data vectors per 128-byte line
+    const uint32_t d_vecs = (c.d_header_bytes + c.d_payload_bytes + c.d_scale_bytes) / 16;
+    c.d_stride = (d_vecs + 6) / 7 * 128;
+    c.c_stride = (c_row_bytes / 16 + 6) / 7 * 128;
+  } else {
+    c.d_stride = round_up_u32(c.d_header_bytes + c.d_payload_bytes + c.d_scale_bytes, 128);
+    c.c_stride = c_row_bytes;
+  }
   c.c_records_per_token = p.combine_mode == kCombinePreReduce ? p.world : p.topk;
   c.counts_stride = round_up_u32(1 + c.experts_per_rank, 4);
 
@@ -216,9 +234,10 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
   }
   PPLX_CUDA_CHECK(cudaDeviceSynchronize());
   PPLX_INFO("a2a context: world=%d dp=%d experts=%d topk=%d hidden=%d record=%uB/%uB blocks=%d "
-            "local_ranks=%zu recv=%.1f MiB",
+            "local_ranks=%zu recv=%.1f MiB wire=%s",
             cfg_.world, cfg_.dp_size, cfg_.num_experts, cfg_.topk, cfg_.hidden_dim, cfg_.d_stride,
-            cfg_.c_stride, cfg_.num_blocks, ranks.size(), cfg_.recv_bytes / 1048576.0);
+            cfg_.c_stride, cfg_.num_blocks, ranks.size(), cfg_.recv_bytes / 1048576.0,
+            cfg_.wire == kWireLL ? "ll" : "plain");
 }
 
 A2AContext::~A2AContext() {
@@ -349,6 +368,7 @@ std::vector<A2AScatterInfo> A2AContext::combine_send_external() {
   PPLX_REQUIRE(cfg_.combine_mode == kCombinePerRoute, "an external combine send needs the per_route mode");
   PPLX_REQUIRE(cfg_.dp_size == 1, "an external combine send does not replicate to dp peers");
   PPLX_REQUIRE(cfg_.out_elemsize == 2, "an external combine send writes 2-byte elements");
+  PPLX_REQUIRE(cfg_.wire == kWirePlain, "an external combine send needs the plain wire format (wire='plain')");
   require_phase(kPhaseCombineSend);
   commit_phase(kPhaseCombineSend);
   external_send_ = true;

@@ -31,6 +31,8 @@ struct A2AParams {
   int scale_elemsize = 4;
   int expert_padding = 1;
   int combine_mode = kCombinePerRoute;
+  int wire = kWireAuto;        // auto: flagged lines up to 512 tokens per call, plain above;
+                               // PPLX_A2A_WIRE=ll|plain overrides an automatic choice
   int num_blocks = 0;          // 0: one block per SM (divided among virtual ranks)
   int64_t wait_limit_ms = 0;   // 0: PPLX_A2A_TIMEOUT_MS or 10 s
 };

@@ -35,158 +35,32 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <type_traits>
 
 #include "a2a_kernels.h"
 #include "a2a_types.h"
 #include "ptx.cuh"
+#include "a2a_device.cuh"
+#include "a2a_ll.cuh"
 
 namespace pplx {
 namespace {
 
-constexpr int kMaxTeams = kA2AThreads / 32;
-// 16-byte vectors each thread keeps in flight in the copy loops: 512 threads x 8 x 16 B
-// = 64 KiB per SM, about what it takes to cover HBM / NVLink latency at full rate.
-constexpr int kCopyUnroll = 8;
-
-// A team is a power-of-two group of 32..512 consecutive threads of a block that works on
-// one token / record / row at a time. Its size is a launch parameter, chosen per phase.
-struct Team {
-  int size;
-  int id;         // global team index inside this virtual rank
-  int count;      // teams inside this virtual rank
-  int in_block;   // team index inside the block
-  int lane;       // thread index inside the team
-  __device__ __forceinline__ explicit Team(int team_size) : size(team_size) {
-    in_block = threadIdx.x / size;
-    lane = threadIdx.x % size;
-    // consecutive work items land on different SMs
-    id = in_block * gridDim.x + blockIdx.x;
-    count = gridDim.x * (kA2AThreads / size);
-  }
-  __device__ __forceinline__ void sync() const {
-    if (size == 32) {
-      __syncwarp();
-    } else {
-      bar_sync(1 + in_block, size);
-    }
-  }
-};
-
-__device__ __forceinline__ void report(const A2ALocal& ws, uint32_t code, uint32_t phase,
-                                       uint32_t who, uint32_t detail) {
-  if (atomicCAS(&ws.status[0], 0u, code) == 0u) {
-    ws.status[1] = phase;
-    ws.status[2] = who;
-    ws.status[3] = detail;
-    *reinterpret_cast<volatile uint32_t*>(ws.host_flag) = code;
-    __threadfence_system();
-  }
-}
-
-__device__ __forceinline__ uint32_t* flag_ptr(uint8_t* sync_base, int row, int src) {
-  // row: see A2AFlagRow; src: the rank that writes the word
-  return reinterpret_cast<uint32_t*>(sync_base) + (row * kMaxRanks + src) * kFlagStrideWords;
-}
-
-// Bounded wait until a cumulative arrival counter reaches `expected`.
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t expected,
-                                          uint64_t limit_ns, uint64_t* waited_ns) {
-  if (static_cast<int32_t>(ld_acquire_sys(flag) - expected) >= 0) {
-    *waited_ns = 0;
-    return true;
-  }
-  const uint64_t start = globaltimer_ns();
-  for (;;) {
-    #pragma unroll 1
-    for (int i = 0; i < 64; ++i) {
-      if (static_cast<int32_t>(ld_acquire_sys(flag) - expected) >= 0) {
-        *waited_ns = globaltimer_ns() - start;
-        return true;
-      }
-    }
-    if (globaltimer_ns() - start > limit_ns) {
-      *waited_ns = limit_ns;
-      return false;
-    }
-  }
-}
-
-// Marks this block as finished with a *recv* phase (which = 0 dispatch, 1 combine). The
-// last block of the launch advances the epoch and clears the placement cursors that the
-// dispatch after next will use. Every block read the epoch before it got here, so the
-// increment cannot be observed by a block of the same launch.
-__device__ __forceinline__ void finish_recv(const A2AConfig& cfg, const A2ALocal& ws, int which,
-                                            uint32_t epoch, int trace_slot, bool external) {
-  __syncthreads();
-  __shared__ uint32_t s_last;
-  if (threadIdx.x == 0) {
-    __threadfence();
-    const uint32_t old = atom_acq_rel_gpu_add(&ws.done[which], 1u);
-    s_last = (old == gridDim.x - 1) ? 1u : 0u;
-  }
-  __syncthreads();
-  if (s_last) {
-    if (which == 0) {
-      const int n = cfg.num_groups * cfg.experts_per_rank;
-      const uint32_t next_par = (epoch + 1) & 1u;
-      for (int i = threadIdx.x; i < n; i += blockDim.x) ws.place_cursor[next_par * n + i] = 0;
-    }
-    if (threadIdx.x == 0) {
-      ws.done[which] = 0;
-      ws.epochs[which] = epoch + 1;
-      if (external) ws.epochs[2] = ws.epochs[2] + 1;
-      if (cfg.trace) ws.trace[trace_slot] = globaltimer_ns();
-    }
-  }
-}
-
-__device__ __forceinline__ uint32_t read_epoch(const A2ALocal& ws, int which) {
-  return *reinterpret_cast<volatile const uint32_t*>(&ws.epochs[which]);
-}
-
-__device__ __forceinline__ void trace_mark(const A2AConfig& cfg, const A2ALocal& ws, int slot) {
-  if (cfg.trace && blockIdx.x == 0 && threadIdx.x == 0) ws.trace[slot] = globaltimer_ns();
-}
-
 // ---------------------------------------------------------------------------
 // dispatch_send
 // ---------------------------------------------------------------------------
-
-// Quantises 16 consecutive bf16 values (two 16-byte vectors) held by one lane to e4m3;
-// eight neighbouring lanes share one 1x128 block and therefore one scale.
-__device__ __forceinline__ Vec16 quantize16(const Vec16& a, const Vec16& b, float* scale_out) {
-  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-  const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
-  float2 f[8];
-  float amax = 0.f;
-  #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f[i] = __bfloat1622float2(pa[i]);
-    f[4 + i] = __bfloat1622float2(pb[i]);
-  }
-  #pragma unroll
-  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fmaxf(fabsf(f[i].x), fabsf(f[i].y)));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-  const float scale = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
-  const float inv = 1.0f / scale;
-  *scale_out = scale;
-  Vec16 out;
-  uint32_t* o = reinterpret_cast<uint32_t*>(&out);
-  #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 lo = make_float2(f[2 * i].x * inv, f[2 * i].y * inv);
-    const float2 hi = make_float2(f[2 * i + 1].x * inv, f[2 * i + 1].y * inv);
-    const uint32_t l = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3);
-    const uint32_t h = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3);
-    o[i] = l | (h << 16);
-  }
-  return out;
+// Dynamic shared memory of the dispatch kernel: [histogram / layout tables | staging of one
+// quantised token per team (flagged-line format with fused quantisation only)].
+__host__ __device__ inline size_t dispatch_stage_offset(const A2AConfig& cfg) {
+  const size_t send = (cfg.num_experts + kMaxRanks) * sizeof(uint32_t);
+  const size_t gl = static_cast<size_t>(cfg.num_groups) * cfg.experts_per_rank;
+  const size_t recv = (2 * gl + 2 * cfg.experts_per_rank + 32) * sizeof(uint32_t);
+  return ((send > recv ? send : recv) + 15) / 16 * 16;
 }
 
+template <int WIRE>
 __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st,
                                     const DispatchSendArgs& a, uint32_t* dyn_smem, const int TEAM) {
   const A2ALocal& ws = st.local;
@@ -204,10 +78,6 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
   int T = a.num_tokens;
   if (a.bound_m != nullptr) T = min(T, *a.bound_m);
   T = max(0, min(T, cfg.max_num_tokens));
-
-  __shared__ uint32_t s_idx[kMaxTeams][kMaxTopK];
-  __shared__ float s_w[kMaxTeams][kMaxTopK];
-  __shared__ uint32_t s_slot[kMaxTeams][kMaxRanks];
 
   // ---- counts message: leaves before any payload, from the block with the fewest tokens ----
   // Per destination: how many records it will get from this rank and how many of them each
@@ -261,6 +131,13 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
   }
 
   // ---- token loop: one team per token ----
+  if constexpr (WIRE == kWireLL) {
+    uint8_t* side = reinterpret_cast<uint8_t*>(dyn_smem) + dispatch_stage_offset(cfg);
+    dispatch_send_tokens_ll(cfg, st, a, T, tag, par, TEAM, side);
+  } else {
+  __shared__ uint32_t s_idx[kMaxTeams][kMaxTopK];
+  __shared__ float s_w[kMaxTeams][kMaxTopK];
+  __shared__ uint32_t s_slot[kMaxTeams][kMaxRanks];
   const uint32_t nvec = cfg.d_payload_bytes / 16;
   const int hs = cfg.hidden_dim_scale;
   constexpr int U = kCopyUnroll;
@@ -301,6 +178,7 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
       s_slot[team.in_block][d] = my_slot;
     }
     team.sync();
+    if (t == 0) trace_mark(cfg, ws, kTraceSendSlots);
     uint8_t* rec[kMaxRanks];
     #pragma unroll
     for (int d = 0; d < kMaxRanks; ++d) {
@@ -399,56 +277,25 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
     }
     // The record is complete once every lane's stores are: the barrier makes them all
     // "observed" by the lane that publishes the tag, and the release orders them before it.
+    if (t == 0) trace_mark(cfg, ws, kTraceSendStored);
     team.sync();
     if (team.lane < kMaxRanks && my_slot != kNoSlot) {
       uint8_t* mine = st.recv[team.lane] + cfg.off_drecv + my_group * cfg.drecv_group_stride +
                       static_cast<uint64_t>(my_slot) * cfg.d_stride;
       st_release_sys(reinterpret_cast<uint32_t*>(mine), tag);
     }
+    if (t == 0) trace_mark(cfg, ws, kTraceSendPublished);
   }
+  }  // plain wire
   trace_mark(cfg, ws, kTraceSendLoopDone);
+  trace_max(cfg, ws, kTraceSendLoopLast);
   if (threadIdx.x == 0 && blockIdx.x == 0) atomicAdd(&ws.stats[0], static_cast<unsigned long long>(T));
 }
 
 // ---------------------------------------------------------------------------
 // dispatch_recv
 // ---------------------------------------------------------------------------
-
-// Compacts the entries of the team's first warp for which `valid` holds into
-// out_a/out_b (shared memory) and returns their number in *out_n. Must be called by
-// all 32 lanes of that warp.
-__device__ __forceinline__ void compact_warp(bool valid, uint32_t va, uint32_t vb, uint32_t* out_a,
-                                             uint32_t* out_b, uint32_t* out_n) {
-  const uint32_t lane = threadIdx.x & 31u;
-  const uint32_t mask = __ballot_sync(0xffffffffu, valid);
-  if (valid) {
-    const uint32_t pos = __popc(mask & ((1u << lane) - 1u));
-    out_a[pos] = va;
-    out_b[pos] = vb;
-  }
-  if (lane == 0) *out_n = __popc(mask);
-}
-
-// Bounded wait until the word at `p` equals `want` (exact = true) or has reached it as a
-// counter (exact = false). Gives up when the time limit runs out or when another team of this
-// rank has already reported a failure.
-__device__ __forceinline__ bool wait_word(const uint32_t* p, uint32_t want, bool exact,
-                                          uint64_t limit_ns, const uint32_t* status) {
-  auto ok = [&](uint32_t v) { return exact ? v == want : static_cast<int32_t>(v - want) >= 0; };
-  if (ok(ld_acquire_sys(p))) return true;
-  const uint64_t start = globaltimer_ns();
-  for (;;) {
-    #pragma unroll 1
-    for (int i = 0; i < 32; ++i) {
-      if (ok(ld_acquire_sys(p))) return true;
-    }
-    if (*reinterpret_cast<const volatile uint32_t*>(status) != 0) return false;
-    if (globaltimer_ns() - start > limit_ns) return false;
-  }
-}
-
-constexpr uint32_t kTeamAbort = 0xfffffffeu;
-
+template <int WIRE>
 __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
                                     const DispatchRecvArgs& a, uint32_t* dyn_smem, const int TEAM) {
   const A2ALocal& ws = st.local;
@@ -567,6 +414,11 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
     }
 
     // ---- record loop: one team per record, each consumed as soon as its tag is there ----
+    if constexpr (WIRE == kWireLL) {
+      RecvLayout lay{base, s_rec_prefix, row_cap};
+      uint8_t* side = reinterpret_cast<uint8_t*>(dyn_smem) + dispatch_stage_offset(cfg);
+      dispatch_recv_records_ll(cfg, st, a, lay, tag, par, TEAM, s_rows, s_unused, s_nrows, side);
+    } else {
     const uint32_t nvec = cfg.d_payload_bytes / 16;
     const int hs = cfg.hidden_dim_scale;
     const uint32_t total_recs = s_rec_prefix[G];
@@ -625,6 +477,7 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
         if (!ok && team.lane == 0) s_nrows[team.in_block] = kTeamAbort;
       }
       team.sync();
+      if (r == 0) trace_mark(cfg, ws, kTraceRecvFirstTag);
 
       const uint32_t nrows = s_nrows[team.in_block];
       if (nrows == kTeamAbort) break;  // uniform across the team
@@ -660,8 +513,10 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
       }
       team.sync();
     }
+    }  // plain wire
   }
   trace_mark(cfg, ws, kTraceRecvLoopDone);
+  trace_max(cfg, ws, kTraceRecvLoopLast);
   finish_recv(cfg, ws, 0, epoch, kTraceRecvAllDone, false);
 }
 
@@ -669,111 +524,11 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
 // combine_send
 // ---------------------------------------------------------------------------
 
-template <typename T>
-struct Elem8;  // 8 consecutive elements as fp32
-
-template <>
-struct Elem8<__nv_bfloat16> {
-  static constexpr int kBytes = 16;
-  __device__ static __forceinline__ void load(const uint8_t* p, float (&f)[8], bool stream) {
-    const Vec16 v = stream ? ld_stream_v4(p) : ld_input_v4(p);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
-    #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 x = __bfloat1622float2(h[i]);
-      f[2 * i] = x.x;
-      f[2 * i + 1] = x.y;
-    }
-  }
-  __device__ static __forceinline__ void store(uint8_t* p, const float (&f)[8]) {
-    Vec16 v;
-    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
-    #pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
-    st_stream_v4(p, v);
-  }
-};
-
-template <>
-struct Elem8<__half> {
-  static constexpr int kBytes = 16;
-  __device__ static __forceinline__ void load(const uint8_t* p, float (&f)[8], bool stream) {
-    const Vec16 v = stream ? ld_stream_v4(p) : ld_input_v4(p);
-    const __half2* h = reinterpret_cast<const __half2*>(&v);
-    #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 x = __half22float2(h[i]);
-      f[2 * i] = x.x;
-      f[2 * i + 1] = x.y;
-    }
-  }
-  __device__ static __forceinline__ void store(uint8_t* p, const float (&f)[8]) {
-    Vec16 v;
-    __half2* h = reinterpret_cast<__half2*>(&v);
-    #pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
-    st_stream_v4(p, v);
-  }
-};
-
-template <>
-struct Elem8<float> {
-  static constexpr int kBytes = 32;
-  __device__ static __forceinline__ void load(const uint8_t* p, float (&f)[8], bool stream) {
-    const Vec16 a = stream ? ld_stream_v4(p) : ld_input_v4(p);
-    const Vec16 b = stream ? ld_stream_v4(p + 16) : ld_input_v4(p + 16);
-    f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y);
-    f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
-    f[4] = __uint_as_float(b.x); f[5] = __uint_as_float(b.y);
-    f[6] = __uint_as_float(b.z); f[7] = __uint_as_float(b.w);
-  }
-  __device__ static __forceinline__ void store(uint8_t* p, const float (&f)[8]) {
-    Vec16 a, b;
-    a.x = __float_as_uint(f[0]); a.y = __float_as_uint(f[1]);
-    a.z = __float_as_uint(f[2]); a.w = __float_as_uint(f[3]);
-    b.x = __float_as_uint(f[4]); b.y = __float_as_uint(f[5]);
-    b.z = __float_as_uint(f[6]); b.w = __float_as_uint(f[7]);
-    st_stream_v4(p, a);
-    st_stream_v4(p + 16, b);
-  }
-};
-
-// acc += sum_j w[j] * rows[j][granule], eight independent 16/32-byte loads in flight.
-template <typename Y>
-__device__ __forceinline__ void weighted_gather8(float (&acc)[8], const uint8_t* base,
-                                                 uint64_t row_stride, const uint32_t* rows,
-                                                 const uint32_t* weights_bits, uint32_t n,
-                                                 uint64_t byte_off, bool stream) {
-  for (uint32_t j0 = 0; j0 < n; j0 += 8) {
-    float f[8][8];
-    #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      if (j0 + u < n) {
-        Elem8<Y>::load(base + static_cast<uint64_t>(rows[j0 + u]) * row_stride + byte_off, f[u],
-                       stream);
-      }
-    }
-    #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      if (j0 + u < n) {
-        const float w = __uint_as_float(weights_bits[j0 + u]);
-        #pragma unroll
-        for (int q = 0; q < 8; ++q) acc[q] = fmaf(w, f[u][q], acc[q]);
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ uint32_t* tok_arrive_ptr(const A2AConfig& cfg, uint8_t* sync_base,
-                                                    uint32_t t) {
-  return reinterpret_cast<uint32_t*>(sync_base + cfg.off_tok_arrive) + t;
-}
-
 // Per-route mode: plain byte copy of each valid expert row to every member of the
 // origin dp group. Pre-reduce mode: weighted partial sum per received record. Either way
 // the team that wrote a row announces it at once on the arrival counter of the row's token
 // at the origin, so the origin reduces token by token while other rows are still in flight.
-template <typename Y>
+template <int WIRE, typename Y>
 __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
                                    const CombineSendArgs& a, const int TEAM) {
   const A2ALocal& ws = st.local;
@@ -789,7 +544,9 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
   __syncthreads();
   const bool healthy = s_healthy != 0;
 
-  if (healthy && cfg.combine_mode == kCombinePerRoute) {
+  if constexpr (WIRE == kWireLL) {
+    if (healthy) combine_send_rows_ll<Y>(cfg, st, a, read_epoch(ws, 1) + 1, TEAM, s_rows, s_wbits, s_n);
+  } else if (healthy && cfg.combine_mode == kCombinePerRoute) {
     const uint32_t rows = ws.expert_meta[0];
     const uint32_t nvec = cfg.c_stride / 16;
     constexpr int U = kCopyUnroll;
@@ -831,10 +588,12 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
           }
         }
       }
+      if (row == 0) trace_mark(cfg, ws, kTraceCSendStored);
       team.sync();
       if (team.lane < cfg.dp_size) {
         red_release_sys_add(tok_arrive_ptr(cfg, st.sync[g * cfg.dp_size + team.lane], tk / K), 1u);
       }
+      if (row == 0) trace_mark(cfg, ws, kTraceCSendPublished);
     }
   } else if (healthy) {
     const uint32_t recs = ws.expert_meta[1];
@@ -902,47 +661,14 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
     }
   }
   trace_mark(cfg, ws, kTraceCSendLoopDone);
+  trace_max(cfg, ws, kTraceCSendLoopLast);
 }
 
 // ---------------------------------------------------------------------------
 // combine_recv
 // ---------------------------------------------------------------------------
 
-// Source slots (and weights) of token t, compacted into shared memory by the first warp
-// of the team. *out_n is also the number of arrivals the token waits for.
-__device__ __forceinline__ void combine_sources(const A2AConfig& cfg, const CombineRecvArgs& a,
-                                                int t, uint32_t* out_slot, uint32_t* out_wbits,
-                                                uint32_t* out_n) {
-  const int K = cfg.topk;
-  const int L = cfg.experts_per_rank;
-  const int k = threadIdx.x & 31;
-  bool valid = false;
-  uint32_t slot = 0, wb = 0;
-  if (k < K) {
-    const uint32_t e = a.indices[t * a.indices_stride + k];
-    if (e < static_cast<uint32_t>(cfg.num_experts)) {
-      if (cfg.combine_mode == kCombinePerRoute) {
-        valid = true;
-        slot = static_cast<uint32_t>(t) * K + k;
-        wb = __float_as_uint(a.weights[t * a.weights_stride + k]);
-      } else {
-        // one partial per distinct destination rank; weights were applied remotely
-        const uint32_t d = e / L;
-        bool first = true;
-        for (int q = 0; q < k; ++q) {
-          const uint32_t eq = a.indices[t * a.indices_stride + q];
-          first &= !(eq < static_cast<uint32_t>(cfg.num_experts) && eq / L == d);
-        }
-        valid = first;
-        slot = static_cast<uint32_t>(t) * cfg.world + d;
-        wb = __float_as_uint(1.0f);
-      }
-    }
-  }
-  compact_warp(valid, slot, wb, out_slot, out_wbits, out_n);
-}
-
-template <typename Y, typename O>
+template <int WIRE, typename Y, typename O>
 __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
                                    const CombineRecvArgs& a, const int TEAM) {
   const A2ALocal& ws = st.local;
@@ -978,7 +704,9 @@ __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
   }
   trace_mark(cfg, ws, kTraceCRecvWaitDone);
 
-  if (s_abort == 0) {
+  if constexpr (WIRE == kWireLL) {
+    if (s_abort == 0) combine_recv_tokens_ll<Y, O>(cfg, st, a, T, epoch + 1, TEAM, s_slot, s_wbits, s_n);
+  } else if (s_abort == 0) {
     const uint8_t* crecv = st.recv[st.rank] + cfg.off_crecv;
     const uint32_t ngran = cfg.hidden_dim / 8;
     for (int t = team.id; t < T; t += team.count) {
@@ -1001,6 +729,7 @@ __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
         }
       }
       team.sync();
+      if (t == 0) trace_mark(cfg, ws, kTraceCRecvFirstToken);
       const uint32_t n = s_n[team.in_block];
       if (n == kTeamAbort) break;  // uniform across the team
       uint8_t* out_row = a.out_tokens + static_cast<uint64_t>(t) * a.out_tokens_stride * sizeof(O);
@@ -1018,6 +747,7 @@ __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
     }
   }
   trace_mark(cfg, ws, kTraceCRecvLoopDone);
+  trace_max(cfg, ws, kTraceCRecvLoopLast);
   finish_recv(cfg, ws, 1, epoch, kTraceCRecvAllDone, a.external != 0);
 }
 
@@ -1025,6 +755,7 @@ __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
 // kernels
 // ---------------------------------------------------------------------------
 
+template <int WIRE>
 __global__ void __launch_bounds__(kA2AThreads, 1)
 dispatch_kernel(const __grid_constant__ A2AConfig cfg, const __grid_constant__ A2ARankStates states,
                 const __grid_constant__ PerRank<DispatchSendArgs> send,
@@ -1032,36 +763,36 @@ dispatch_kernel(const __grid_constant__ A2AConfig cfg, const __grid_constant__ A
                 int recv_team) {
   extern __shared__ __align__(16) uint32_t dyn_smem[];
   const A2ARankState& st = states.r[blockIdx.y];
-  if (send_team) dispatch_send_phase(cfg, st, send.r[blockIdx.y], dyn_smem, send_team);
+  if (send_team) dispatch_send_phase<WIRE>(cfg, st, send.r[blockIdx.y], dyn_smem, send_team);
   if (send_team && recv_team) __syncthreads();
-  if (recv_team) dispatch_recv_phase(cfg, st, recv.r[blockIdx.y], dyn_smem, recv_team);
+  if (recv_team) dispatch_recv_phase<WIRE>(cfg, st, recv.r[blockIdx.y], dyn_smem, recv_team);
 }
 
-template <typename Y>
+template <int WIRE, typename Y>
 __global__ void __launch_bounds__(kA2AThreads, 1)
 combine_send_kernel(const __grid_constant__ A2AConfig cfg,
                     const __grid_constant__ A2ARankStates states,
                     const __grid_constant__ PerRank<CombineSendArgs> send, int send_team) {
-  combine_send_phase<Y>(cfg, states.r[blockIdx.y], send.r[blockIdx.y], send_team);
+  combine_send_phase<WIRE, Y>(cfg, states.r[blockIdx.y], send.r[blockIdx.y], send_team);
 }
 
-template <typename Y, typename O>
+template <int WIRE, typename Y, typename O>
 __global__ void __launch_bounds__(kA2AThreads, 1)
 combine_recv_kernel(const __grid_constant__ A2AConfig cfg,
                     const __grid_constant__ A2ARankStates states,
                     const __grid_constant__ PerRank<CombineRecvArgs> recv, int recv_team) {
-  combine_recv_phase<Y, O>(cfg, states.r[blockIdx.y], recv.r[blockIdx.y], recv_team);
+  combine_recv_phase<WIRE, Y, O>(cfg, states.r[blockIdx.y], recv.r[blockIdx.y], recv_team);
 }
 
-template <typename Y, typename O>
+template <int WIRE, typename Y, typename O>
 __global__ void __launch_bounds__(kA2AThreads, 1)
 combine_kernel(const __grid_constant__ A2AConfig cfg, const __grid_constant__ A2ARankStates states,
                const __grid_constant__ PerRank<CombineSendArgs> send,
                const __grid_constant__ PerRank<CombineRecvArgs> recv, int send_team,
                int recv_team) {
-  combine_send_phase<Y>(cfg, states.r[blockIdx.y], send.r[blockIdx.y], send_team);
+  combine_send_phase<WIRE, Y>(cfg, states.r[blockIdx.y], send.r[blockIdx.y], send_team);
   __syncthreads();
-  combine_recv_phase<Y, O>(cfg, states.r[blockIdx.y], recv.r[blockIdx.y], recv_team);
+  combine_recv_phase<WIRE, Y, O>(cfg, states.r[blockIdx.y], recv.r[blockIdx.y], recv_team);
 }
 
 // Every rank announces itself on every rank's barrier counters and waits until it has heard
@@ -1085,11 +816,15 @@ barrier_kernel(const __grid_constant__ A2AConfig cfg, const __grid_constant__ A2
   if (threadIdx.x == 0) ws.epochs[3] = expected;
 }
 
-size_t dispatch_smem_bytes(const A2AConfig& cfg) {
-  const size_t send = (cfg.num_experts + kMaxRanks) * sizeof(uint32_t);
-  const size_t gl = static_cast<size_t>(cfg.num_groups) * cfg.experts_per_rank;
-  const size_t recv = (2 * gl + 2 * cfg.experts_per_rank + 32) * sizeof(uint32_t);
-  return send > recv ? send : recv;
+size_t dispatch_smem_bytes(const A2AConfig& cfg, int send_team, int recv_team, bool quantize) {
+  size_t bytes = dispatch_stage_offset(cfg);
+  if (cfg.wire == kWireLL) {
+    size_t side = 0;
+    if (send_team > 0) side = (kA2AThreads / send_team) * ll_side_bytes(cfg, quantize);
+    if (recv_team > 0) side = std::max(side, (kA2AThreads / recv_team) * ll_side_bytes(cfg, false));
+    bytes += side;
+  }
+  return bytes;
 }
 
 template <typename F>
@@ -1147,11 +882,17 @@ cudaError_t a2a_launch_dispatch(const A2AConfig& cfg, const A2ARankStates& state
                                 const PerRank<DispatchRecvArgs>& recv, int send_team, int recv_team,
                                 cudaStream_t stream) {
   const dim3 grid(cfg.num_blocks, nranks);
-  const size_t smem = dispatch_smem_bytes(cfg);
+  bool quantize = false;
+  for (int i = 0; i < nranks; ++i) quantize |= send_team && send.r[i].quantize != 0;
+  const size_t smem = dispatch_smem_bytes(cfg, send_team, recv_team, quantize);
   // One launch that plays several ranks contains blocks that wait for one another:
   // co-residency must be guaranteed (or the launch refused) by the driver.
   const bool cooperative = nranks > 1 && send_team && recv_team;
-  return launch(dispatch_kernel, grid, smem, stream, cooperative, cfg, states, send, recv,
+  if (cfg.wire == kWireLL) {
+    return launch(dispatch_kernel<kWireLL>, grid, smem, stream, cooperative, cfg, states, send, recv,
+                  send_team, recv_team);
+  }
+  return launch(dispatch_kernel<kWirePlain>, grid, smem, stream, cooperative, cfg, states, send, recv,
                 send_team, recv_team);
 }
 
@@ -1168,25 +909,39 @@ cudaError_t a2a_launch_barrier(const A2AConfig& cfg, const A2ARankStates& states
                           stream);
 }
 
-cudaError_t a2a_launch_combine(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
-                               const PerRank<CombineSendArgs>& send,
-                               const PerRank<CombineRecvArgs>& recv, int send_team, int recv_team,
-                               int y_dtype, int out_dtype, cudaStream_t stream) {
+template <int WIRE>
+cudaError_t launch_combine_wire(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
+                                const PerRank<CombineSendArgs>& send,
+                                const PerRank<CombineRecvArgs>& recv, int send_team, int recv_team,
+                                int y_dtype, int out_dtype, cudaStream_t stream) {
   const dim3 grid(cfg.num_blocks, nranks);
   return with_dtype(y_dtype, [&](auto* yp) {
     using Y = std::remove_pointer_t<decltype(yp)>;
     if (send_team && !recv_team) {
-      return launch(combine_send_kernel<Y>, grid, 0, stream, false, cfg, states, send, send_team);
+      return launch(combine_send_kernel<WIRE, Y>, grid, 0, stream, false, cfg, states, send, send_team);
     }
     return with_dtype(out_dtype, [&](auto* op) {
       using O = std::remove_pointer_t<decltype(op)>;
       if (send_team) {
-        return launch(combine_kernel<Y, O>, grid, 0, stream, nranks > 1, cfg, states, send, recv,
+        return launch(combine_kernel<WIRE, Y, O>, grid, 0, stream, nranks > 1, cfg, states, send, recv,
                       send_team, recv_team);
       }
-      return launch(combine_recv_kernel<Y, O>, grid, 0, stream, false, cfg, states, recv, recv_team);
+      return launch(combine_recv_kernel<WIRE, Y, O>, grid, 0, stream, false, cfg, states, recv, recv_team);
     });
   });
 }
 
+cudaError_t a2a_launch_combine(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
+                               const PerRank<CombineSendArgs>& send,
+                               const PerRank<CombineRecvArgs>& recv, int send_team, int recv_team,
+                               int y_dtype, int out_dtype, cudaStream_t stream) {
+  if (cfg.wire == kWireLL) {
+    return launch_combine_wire<kWireLL>(cfg, states, nranks, send, recv, send_team, recv_team, y_dtype,
+                                        out_dtype, stream);
+  }
+  return launch_combine_wire<kWirePlain>(cfg, states, nranks, send, recv, send_team, recv_team, y_dtype,
+                                         out_dtype, stream);
+}
+
 }  // namespace pplx
+

@@ -58,7 +58,19 @@ enum A2ATrace : int {
   kTraceCSendStart = 8, kTraceCSendLoopDone = 9, kTraceCSendSignalled = 10,
   kTraceCRecvStart = 11, kTraceCRecvWaitDone = 12, kTraceCRecvLoopDone = 13,
   kTraceCRecvAllDone = 14,
-  kTraceSlots = 16,
+  // finer points, block 0 / first item unless stated otherwise
+  kTraceSendSlots = 15,        // record slots of the first token allocated
+  kTraceSendStored = 16,       // its stores issued
+  kTraceSendPublished = 17,    // its tag released
+  kTraceRecvFirstTag = 18,     // first record's tag seen
+  kTraceSendLoopLast = 19,     // latest block to leave the send loop
+  kTraceRecvLoopLast = 20,     // latest block to leave the record loop
+  kTraceCSendStored = 21,      // first row's stores issued
+  kTraceCSendPublished = 22,   // first row announced
+  kTraceCRecvFirstToken = 23,  // first token's rows all in
+  kTraceCSendLoopLast = 24,    // latest block to leave the combine send loop
+  kTraceCRecvLoopLast = 25,    // latest block to leave the reduction loop
+  kTraceSlots = 32,
 };
 
 // Rows of the flag table at the start of the sync region (one 128-byte line per source rank).
@@ -77,6 +89,12 @@ enum A2AStatus : uint32_t {
   kStatusBadExpertIndex = 3,  // indices[t][k] >= num_experts
   kStatusRecordOverflow = 4,  // more records than a source region holds
   kStatusBadRecord = 5,       // a record header names a token or count outside its limits
+};
+
+enum A2AWire : int {
+  kWireAuto = 0,
+  kWirePlain = 1,  // contiguous records; arrival announced by release stores / counters
+  kWireLL = 2,     // 128-byte lines of 112 data bytes + a 16-byte flag vector (see a2a_ll.cuh)
 };
 
 enum A2ACombineMode : int {
@@ -101,6 +119,7 @@ struct A2AConfig {
   int combine_mode;
   int num_blocks;        // grid.x of every a2a kernel (arrival counters depend on it)
   int trace;             // 1: kernels record a coarse timeline into A2ALocal::trace
+  int wire;              // A2AWire, never kWireAuto here
 
   // wire format
   uint32_t d_header_bytes;

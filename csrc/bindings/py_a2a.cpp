@@ -27,11 +27,21 @@ int combine_mode_from(const py::object& mode) {
   throw Error(ErrorKind::kInvalidArgument, "combine_mode must be 'per_route' or 'pre_reduce'");
 }
 
+int wire_from(const py::object& wire) {
+  if (wire.is_none()) return kWireAuto;
+  if (py::isinstance<py::int_>(wire)) return wire.cast<int>();
+  const std::string s = wire.cast<std::string>();
+  if (s == "auto") return kWireAuto;
+  if (s == "plain") return kWirePlain;
+  if (s == "ll") return kWireLL;
+  throw Error(ErrorKind::kInvalidArgument, "wire must be 'auto', 'plain' or 'll'");
+}
+
 A2AParams make_params(int hidden_dim, const py::object& hidden_dim_scale, int in_elemsize,
                       int out_elemsize, const py::object& scale_elemsize, int max_num_tokens,
                       int num_experts, int expert_padding, int num_experts_per_token, int dp_size,
                       int world_size, const py::object& combine_mode, int num_blocks,
-                      int64_t wait_limit_ms) {
+                      int64_t wait_limit_ms, const py::object& wire = py::none()) {
   A2AParams p;
   p.world = world_size;
   p.dp_size = dp_size;
@@ -47,6 +57,7 @@ A2AParams make_params(int hidden_dim, const py::object& hidden_dim_scale, int in
   p.combine_mode = combine_mode_from(combine_mode);
   p.num_blocks = num_blocks;
   p.wait_limit_ms = wait_limit_ms;
+  p.wire = wire_from(wire);
   return p;
 }
 
@@ -61,6 +72,7 @@ py::dict config_dict(const A2AConfig& c) {
   d["max_num_tokens"] = c.max_num_tokens;
   d["num_blocks"] = c.num_blocks;
   d["combine_mode"] = c.combine_mode;
+  d["wire"] = c.wire == kWireLL ? "ll" : "plain";
   d["dispatch_header_bytes"] = c.d_header_bytes;
   d["dispatch_payload_bytes"] = c.d_payload_bytes;
   d["dispatch_scale_bytes"] = c.d_scale_bytes;
@@ -180,11 +192,12 @@ void bind_a2a(py::module_& m) {
           [](int hidden_dim, const py::object& hidden_dim_scale, int in_elemsize, int out_elemsize,
              const py::object& scale_elemsize, int max_num_tokens, int num_experts,
              int expert_padding, int num_experts_per_token, int dp_size, int world_size,
-             const py::object& combine_mode, int num_blocks, int num_sms, int virtual_ranks) {
+             const py::object& combine_mode, int num_blocks, int num_sms, int virtual_ranks,
+             const py::object& wire) {
             const A2AParams p = make_params(hidden_dim, hidden_dim_scale, in_elemsize, out_elemsize,
                                             scale_elemsize, max_num_tokens, num_experts,
                                             expert_padding, num_experts_per_token, dp_size,
-                                            world_size, combine_mode, num_blocks, 0);
+                                            world_size, combine_mode, num_blocks, 0, wire);
             return config_dict(a2a_make_config(p, num_sms, virtual_ranks));
           },
           py::kw_only(), py::arg("hidden_dim"), py::arg("hidden_dim_scale") = py::none(),
@@ -192,7 +205,7 @@ void bind_a2a(py::module_& m) {
           py::arg("max_num_tokens"), py::arg("num_experts"), py::arg("expert_padding") = 1,
           py::arg("num_experts_per_token"), py::arg("dp_size") = 1, py::arg("world_size"),
           py::arg("combine_mode") = py::none(), py::arg("num_blocks") = 0,
-          py::arg("num_sms") = 148, py::arg("virtual_ranks") = 1,
+          py::arg("num_sms") = 148, py::arg("virtual_ranks") = 1, py::arg("wire") = py::none(),
           "Wire format and symmetric-buffer layout for a configuration (no GPU needed).")
       .def_static(
           "create",
@@ -208,7 +221,7 @@ void bind_a2a(py::module_& m) {
              const py::object& recv_ptrs, int device, const py::object& /*imm_base*/,
              const py::object& /*ranks*/, const py::object& /*transfer_engine*/,
              const py::object& /*worker_cpu*/, const py::object& combine_mode, int num_blocks,
-             int64_t wait_limit_ms) {
+             int64_t wait_limit_ms, const py::object& wire) {
             std::vector<int> local_ranks;
             if (py::isinstance<py::int_>(rank)) {
               local_ranks.push_back(rank.cast<int>());
@@ -218,7 +231,7 @@ void bind_a2a(py::module_& m) {
             const A2AParams p = make_params(hidden_dim, hidden_dim_scale, in_elemsize, out_elemsize,
                                             scale_elemsize, max_num_tokens, num_experts,
                                             expert_padding, num_experts_per_token, dp_size,
-                                            world_size, combine_mode, num_blocks, wait_limit_ms);
+                                            world_size, combine_mode, num_blocks, wait_limit_ms, wire);
             auto self = std::make_unique<PyA2A>();
             self->out_dtype = dtype_code(out_dtype);
             self->ctx = std::make_unique<A2AContext>(p, device, local_ranks,
@@ -240,7 +253,7 @@ void bind_a2a(py::module_& m) {
           py::arg("imm_base") = py::none(), py::arg("ranks") = py::none(),
           py::arg("transfer_engine") = py::none(), py::arg("worker_cpu") = py::none(),
           py::arg("combine_mode") = py::none(), py::arg("num_blocks") = 0,
-          py::arg("wait_limit_ms") = 0,
+          py::arg("wait_limit_ms") = 0, py::arg("wire") = py::none(),
           "Create a context. `rank` may be a list: the context then plays several ranks on one "
           "GPU and sync_ptrs / recv_ptrs hold one pointer table per local rank.")
       .def("config", [](const PyA2A& s) { return config_dict(s.ctx->config()); })

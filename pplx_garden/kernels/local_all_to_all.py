@@ -40,6 +40,7 @@ class LocalAllToAllGroup:
         combine_mode: str = "per_route",
         num_blocks: int = 0,
         wait_limit_ms: int = 0,
+        wire: Optional[str] = None,
     ) -> None:
         device = torch.device(device)
         if device.index is None:
@@ -71,7 +72,8 @@ class LocalAllToAllGroup:
             num_blocks=num_blocks,
         )
         self.layout = AllToAllContext.layout(num_sms=props.multi_processor_count,
-                                             virtual_ranks=world_size, **common)
+                                             virtual_ranks=world_size, wire=wire, **common)
+        common["wire"] = self.layout["wire"]
         self.max_recv_rows: int = self.layout["max_recv_rows"]
         # torch's caching allocator returns 512-byte aligned blocks, which satisfies the
         # 128-byte alignment the kernels ask of the symmetric regions.

@@ -19,7 +19,11 @@ Extensions (keyword-only, all optional): ``combine_mode="pre_reduce"`` makes the
 ranks apply the routing weights given at dispatch time and send one partial sum per
 (token, expert rank) instead of one row per route; passing bf16 ``dp_x`` to a context
 whose ``in_dtype`` is ``float8_e4m3fn`` with ``hidden_dim_scale = hidden_dim // 128`` and
-``dp_x_scale=None`` quantises on the fly (one fp32 scale per 1x128 block).
+``dp_x_scale=None`` quantises on the fly (one fp32 scale per 1x128 block); ``wire`` picks
+the format on the wire: ``"ll"`` (128-byte lines that carry their own arrival flag, no fences,
+one eighth more bytes: best for decode-sized calls), ``"plain"`` (contiguous records announced
+by release stores: best for prefill-sized calls) or ``None`` (``"ll"`` up to 512 tokens per
+call, the environment variable ``PPLX_A2A_WIRE`` overrides).
 """
 
 from __future__ import annotations
@@ -81,6 +85,7 @@ class P2PAllToAll(AllToAllKernel):
         combine_mode: str = "per_route",
         num_blocks: int = 0,
         wait_limit_ms: int = 0,
+        wire: Optional[str] = None,
     ) -> None:
         device = torch.device(device)
         if device.type != "cuda":
@@ -135,6 +140,7 @@ class P2PAllToAll(AllToAllKernel):
             combine_mode=combine_mode,
             num_blocks=num_blocks,
             num_sms=props.multi_processor_count,
+            wire=wire,
         )
         self._layout = layout
         self.max_recv_rows: int = layout["max_recv_rows"]
@@ -193,6 +199,7 @@ class P2PAllToAll(AllToAllKernel):
             combine_mode=combine_mode,
             num_blocks=num_blocks,
             wait_limit_ms=wait_limit_ms,
+            wire=layout["wire"],
         )
         self._check_every = int(os.environ.get("PPLX_A2A_CHECK_EVERY", "0"))
         self._calls = 0

@@ -75,7 +75,9 @@ class ExpertParallelMoE:
             hidden_dim=hidden_dim, hidden_dim_scale=hidden_dim // 128, in_dtype=torch.float8_e4m3fn,
             out_dtype=torch.bfloat16, scale_dtype=torch.float32,
             num_experts_per_token=num_experts_per_token, device=self.device, dp_group=None,
-            node_group=None, global_group=global_group, combine_mode=combine_mode)
+            node_group=None, global_group=global_group, combine_mode=combine_mode,
+            # a down projection that sends its own rows writes them in the plain row format
+            wire="plain" if fused_combine else None)
         rows = self.a2a.max_recv_rows
         dev = self.device
         self.expert_num_tokens = torch.zeros(L, dtype=torch.int32, device=dev)

@@ -30,6 +30,7 @@ class Cfg:
     out_dtype: torch.dtype = torch.float32
     padding: int = 1
     combine_mode: str = "per_route"
+    wire: Optional[str] = None
 
 
 CONFIGS = {
@@ -70,7 +71,7 @@ def _make_group(cfg: Cfg, device, **kw):
         hidden_dim_scale=cfg.hidden_scale, in_dtype=cfg.in_dtype, out_dtype=cfg.out_dtype,
         scale_dtype=torch.float32 if cfg.hidden_scale else None,
         num_experts_per_token=cfg.topk, device=device, combine_mode=cfg.combine_mode,
-        wait_limit_ms=2000, **kw)
+        wait_limit_ms=2000, wire=cfg.wire, **kw)
 
 
 def _inputs(cfg: Cfg, device, seed_offset: int = 0):
@@ -157,9 +158,13 @@ def _verify(cfg: Cfg, data, num, ox, os_, out, *, bound=None, out_prev=None):
         torch.testing.assert_close(got, want, **tol, msg=lambda m, r=r: f"rank {r} combine: {m}")
 
 
+@pytest.mark.parametrize("wire", ["ll", "plain"])
 @pytest.mark.parametrize("name", list(CONFIGS))
-def test_dispatch_combine(name: str) -> None:
-    cfg = CONFIGS[name]
+def test_dispatch_combine(name: str, wire: str) -> None:
+    """Every shape in both wire formats: flagged 128-byte lines and plain records."""
+    from dataclasses import replace
+
+    cfg = replace(CONFIGS[name], wire=wire)
     device = torch.device("cuda", 0)
     group = _make_group(cfg, device)
     try:
@@ -170,11 +175,12 @@ def test_dispatch_combine(name: str) -> None:
         group.destroy()
 
 
-def test_repeated_iterations_and_split_phases() -> None:
-    """Flags are cumulative and cursors double-buffered: many iterations with new routing
+@pytest.mark.parametrize("wire", ["ll", "plain"])
+def test_repeated_iterations_and_split_phases(wire: str) -> None:
+    """Tags advance and cursors are double-buffered: many iterations with new routing
     each time, alternating fused and split launches, must all be exact."""
     cfg = Cfg(world=4, tokens=48, experts=32, hidden=512, topk=4, in_dtype=torch.bfloat16,
-              out_dtype=torch.bfloat16, padding=8)
+              out_dtype=torch.bfloat16, padding=8, wire=wire)
     device = torch.device("cuda", 0)
     group = _make_group(cfg, device)
     try:
@@ -188,8 +194,9 @@ def test_repeated_iterations_and_split_phases() -> None:
         group.destroy()
 
 
-def test_bound_m_and_accumulate() -> None:
-    cfg = Cfg(world=2, tokens=64, experts=16, hidden=256, topk=4)
+@pytest.mark.parametrize("wire", ["ll", "plain"])
+def test_bound_m_and_accumulate(wire: str) -> None:
+    cfg = Cfg(world=2, tokens=64, experts=16, hidden=256, topk=4, wire=wire)
     device = torch.device("cuda", 0)
     group = _make_group(cfg, device)
     try:
@@ -218,10 +225,11 @@ def test_zero_tokens() -> None:
         group.destroy()
 
 
-def test_fused_quantisation_matches_reference_quantiser() -> None:
+@pytest.mark.parametrize("wire", ["ll", "plain"])
+def test_fused_quantisation_matches_reference_quantiser(wire: str) -> None:
     """bf16 tokens in, e4m3 + one fp32 scale per 1x128 block at the experts."""
     cfg = Cfg(world=4, tokens=32, experts=32, hidden=1024, hidden_scale=8, topk=4,
-              in_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16)
+              in_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16, wire=wire)
     device = torch.device("cuda", 0)
     group = _make_group(cfg, device)
     try:
@@ -263,7 +271,8 @@ def test_fused_quantisation_matches_reference_quantiser() -> None:
         group.destroy()
 
 
-def test_wait_timeout_reports_status_without_hanging() -> None:
+@pytest.mark.parametrize("wire", ["ll", "plain"])
+def test_wait_timeout_reports_status_without_hanging(wire: str) -> None:
     """A receive whose sources never signalled must give up after the configured limit,
     leave the context marked failed and keep the CUDA context usable."""
     cfg = Cfg(world=2, tokens=4, experts=8, hidden=64, topk=2)
@@ -274,7 +283,7 @@ def test_wait_timeout_reports_status_without_hanging() -> None:
         world_size=cfg.world, max_num_tokens=cfg.tokens, num_experts=cfg.experts,
         expert_padding=1, hidden_dim=cfg.hidden, hidden_dim_scale=None, in_dtype=torch.float32,
         out_dtype=torch.float32, scale_dtype=None, num_experts_per_token=cfg.topk, device=device,
-        wait_limit_ms=200)
+        wait_limit_ms=200, wire=wire)
     try:
         num, ox, os_, out = _outputs(cfg, group, device)
         # recv without any send: the arrival flags stay at zero

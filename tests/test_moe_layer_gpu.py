@@ -95,7 +95,8 @@ def test_fused_combine_with_four_emulated_ranks() -> None:
     group = LocalAllToAllGroup(
         world_size=world, max_num_tokens=T, num_experts=E, expert_padding=1, hidden_dim=H,
         hidden_dim_scale=H // 128, in_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16,
-        scale_dtype=torch.float32, num_experts_per_token=K, device=dev, wait_limit_ms=2000)
+        scale_dtype=torch.float32, num_experts_per_token=K, device=dev, wait_limit_ms=2000,
+        wire="plain")   # the GEMM writes plain rows
     try:
         gen = torch.Generator(device="cpu").manual_seed(9)
         L, rows = group.num_local_experts, group.max_recv_rows
