@@ -20,6 +20,9 @@ constexpr int kMaxTeams = kA2AThreads / 32;
 // 16-byte vectors each thread keeps in flight in the copy loops: 512 threads x 8 x 16 B
 // = 64 KiB per SM, about what it takes to cover HBM / NVLink latency at full rate.
 constexpr int kCopyUnroll = 8;
+// Arrival signals (release stores / reductions) a team holds back and publishes together:
+// one per lane of its first warp.
+constexpr int kMaxPending = 32;
 
 // A team is a power-of-two group of 32..512 consecutive threads of a block that works on
 // one token / record / row at a time. Its size is a launch parameter, chosen per phase.

@@ -138,6 +138,10 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
   __shared__ uint32_t s_idx[kMaxTeams][kMaxTopK];
   __shared__ float s_w[kMaxTeams][kMaxTopK];
   __shared__ uint32_t s_slot[kMaxTeams][kMaxRanks];
+  __shared__ uint32_t* s_pend[kMaxTeams][kMaxPending];   // tags not yet published
+  __shared__ uint32_t s_npend[kMaxTeams];
+  if (threadIdx.x < kMaxTeams) s_npend[threadIdx.x] = 0;
+  __syncthreads();
   const uint32_t nvec = cfg.d_payload_bytes / 16;
   const int hs = cfg.hidden_dim_scale;
   constexpr int U = kCopyUnroll;
@@ -277,12 +281,29 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
     }
     // The record is complete once every lane's stores are: the barrier makes them all
     // "observed" by the lane that publishes the tag, and the release orders them before it.
+    // A release is a fence that waits for everything this SM has in flight, so tags are
+    // published for a few tokens at a time: the first warp keeps the list.
     if (t == 0) trace_mark(cfg, ws, kTraceSendStored);
     team.sync();
-    if (team.lane < kMaxRanks && my_slot != kNoSlot) {
-      uint8_t* mine = st.recv[team.lane] + cfg.off_drecv + my_group * cfg.drecv_group_stride +
-                      static_cast<uint64_t>(my_slot) * cfg.d_stride;
-      st_release_sys(reinterpret_cast<uint32_t*>(mine), tag);
+    if (team.lane < 32) {
+      uint32_t npend = s_npend[team.in_block];
+      uint32_t* mine = nullptr;
+      if (team.lane < kMaxRanks && my_slot != kNoSlot) {
+        mine = reinterpret_cast<uint32_t*>(st.recv[team.lane] + cfg.off_drecv +
+                                           my_group * cfg.drecv_group_stride +
+                                           static_cast<uint64_t>(my_slot) * cfg.d_stride);
+      }
+      const uint32_t mask = __ballot_sync(0xffffffffu, mine != nullptr);
+      if (mine != nullptr) s_pend[team.in_block][npend + __popc(mask & ((1u << team.lane) - 1u))] = mine;
+      npend += __popc(mask);
+      __syncwarp();
+      const bool last = t + team.count >= T;
+      if (last || npend + kMaxRanks > kMaxPending) {
+        if (team.lane < npend) st_release_sys(s_pend[team.in_block][team.lane], tag);
+        npend = 0;
+        __syncwarp();
+      }
+      if (team.lane == 0) s_npend[team.in_block] = npend;
     }
     if (t == 0) trace_mark(cfg, ws, kTraceSendPublished);
   }
@@ -347,29 +368,40 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
       const int g = i / L, le = i % L;
       cnt[i] = ld_relaxed_sys(counts + g * cfg.counts_stride + 1 + le);
     }
-    if (threadIdx.x == 0) {
-      uint32_t acc = 0;
-      for (int g = 0; g < G; ++g) {
-        s_rec_prefix[g] = acc;
-        acc += min(ld_relaxed_sys(counts + g * cfg.counts_stride),
-                   static_cast<uint32_t>(cfg.max_num_tokens));
+    // records per source group, prefix-summed by the first warp (the loads run in parallel)
+    if (threadIdx.x < 32) {
+      uint32_t n = 0;
+      if (threadIdx.x < G) {
+        n = min(ld_relaxed_sys(counts + threadIdx.x * cfg.counts_stride),
+                static_cast<uint32_t>(cfg.max_num_tokens));
       }
-      for (int g = G; g <= kMaxRanks; ++g) s_rec_prefix[g] = acc;
+      uint32_t incl = n;
+      #pragma unroll
+      for (int o = 1; o < kMaxRanks; o <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (threadIdx.x >= o) incl += up;
+      }
+      if (threadIdx.x <= kMaxRanks) {
+        // lane g holds the inclusive sum up to group g; entry g + 1 is "records before g + 1"
+        if (threadIdx.x == 0) s_rec_prefix[0] = 0;
+        if (threadIdx.x < kMaxRanks) s_rec_prefix[threadIdx.x + 1] = incl;
+      }
     }
     __syncthreads();
-    // Warp 0 owns the layout: lane j covers a contiguous chunk of experts, sums the groups,
-    // scans the padded totals across lanes and writes every (group, expert) base row.
+    // totals per expert, in parallel over the experts
+    for (int j = threadIdx.x; j < L; j += blockDim.x) {
+      uint32_t tot = 0;
+      for (int g = 0; g < G; ++g) tot += cnt[g * L + j];
+      total[j] = tot;
+    }
+    __syncthreads();
+    // exclusive scan of the padded totals: the first warp, each lane a contiguous chunk
     if (threadIdx.x < 32) {
       const int per = (L + 31) / 32;
       const int lo = threadIdx.x * per;
       const int hi = min(lo + per, L);
       uint32_t sum = 0;
-      for (int j = lo; j < hi; ++j) {
-        uint32_t tot = 0;
-        for (int g = 0; g < G; ++g) tot += cnt[g * L + j];
-        total[j] = tot;
-        sum += (tot + pad - 1) / pad * pad;
-      }
+      for (int j = lo; j < hi; ++j) sum += (total[j] + pad - 1) / pad * pad;
       uint32_t incl = sum;
       #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -379,14 +411,17 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
       uint32_t run = incl - sum;
       for (int j = lo; j < hi; ++j) {
         pad_off[j] = run;
-        uint32_t row = run;
-        for (int g = 0; g < G; ++g) {
-          base[g * L + j] = row;
-          row += cnt[g * L + j];
-        }
         run += (total[j] + pad - 1) / pad * pad;
       }
       if (threadIdx.x == 31) misc[0] = incl;
+    }
+    __syncthreads();
+    // first row of every (group, expert), in parallel over the pairs
+    for (int i = threadIdx.x; i < G * L; i += blockDim.x) {
+      const int g = i / L, j = i % L;
+      uint32_t row = pad_off[j];
+      for (int q = 0; q < g; ++q) row += cnt[q * L + j];
+      base[i] = row;
     }
     __syncthreads();
     trace_mark(cfg, ws, kTraceRecvLayoutDone);
@@ -540,9 +575,38 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
   __shared__ uint32_t s_rows[kMaxTeams][kMaxTopK];
   __shared__ uint32_t s_wbits[kMaxTeams][kMaxTopK];
   __shared__ uint32_t s_n[kMaxTeams];
+  // Plain wire: a row is announced by adding one to its token's arrival counter at the origin,
+  // with release semantics. A release is a fence that waits for everything the SM has in flight,
+  // so the first warp of a team collects the counters of a few rows and releases them together.
+  __shared__ uint32_t* s_pend[kMaxTeams][kMaxPending];
+  __shared__ uint32_t s_npend[kMaxTeams];
+  if (threadIdx.x < kMaxTeams) s_npend[threadIdx.x] = 0;
   if (threadIdx.x == 0) s_healthy = ws.status[0] == 0 ? 1u : 0u;
   __syncthreads();
   const bool healthy = s_healthy != 0;
+  // both are called by the whole team, after the barrier that follows a row's stores
+  auto flush = [&]() {
+    if (team.lane < 32) {
+      const uint32_t npend = s_npend[team.in_block];
+      __syncwarp();
+      if (team.lane < npend) red_release_sys_add(s_pend[team.in_block][team.lane], 1u);
+      if (team.lane == 0) s_npend[team.in_block] = 0;
+      __syncwarp();
+    }
+  };
+  auto announce = [&](uint32_t g, uint32_t t) {
+    if (team.lane < 32) {
+      const uint32_t npend = s_npend[team.in_block];
+      __syncwarp();
+      if (team.lane < cfg.dp_size) {
+        s_pend[team.in_block][npend + team.lane] =
+            tok_arrive_ptr(cfg, st.sync[g * cfg.dp_size + team.lane], t);
+      }
+      if (team.lane == 0) s_npend[team.in_block] = npend + cfg.dp_size;
+      __syncwarp();
+      if (npend + 2 * cfg.dp_size > kMaxPending || npend + cfg.dp_size >= 8u * cfg.dp_size) flush();
+    }
+  };
 
   if constexpr (WIRE == kWireLL) {
     if (healthy) combine_send_rows_ll<Y>(cfg, st, a, read_epoch(ws, 1) + 1, TEAM, s_rows, s_wbits, s_n);
@@ -590,11 +654,10 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
       }
       if (row == 0) trace_mark(cfg, ws, kTraceCSendStored);
       team.sync();
-      if (team.lane < cfg.dp_size) {
-        red_release_sys_add(tok_arrive_ptr(cfg, st.sync[g * cfg.dp_size + team.lane], tk / K), 1u);
-      }
+      announce(g, tk / K);
       if (row == 0) trace_mark(cfg, ws, kTraceCSendPublished);
     }
+    flush();
   } else if (healthy) {
     const uint32_t recs = ws.expert_meta[1];
     const uint32_t ngran = cfg.hidden_dim / 8;
@@ -655,10 +718,9 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
         }
       }
       team.sync();
-      if (team.lane < cfg.dp_size) {
-        red_release_sys_add(tok_arrive_ptr(cfg, st.sync[g * cfg.dp_size + team.lane], t), 1u);
-      }
+      announce(g, t);
     }
+    flush();
   }
   trace_mark(cfg, ws, kTraceCSendLoopDone);
   trace_max(cfg, ws, kTraceCSendLoopLast);

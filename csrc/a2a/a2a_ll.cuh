@@ -166,7 +166,10 @@ __device__ __forceinline__ void load_elems(const uint8_t* row, uint64_t elem, fl
 // Code size matters here: these paths run once per launch on a cold instruction cache, so the
 // loops below keep only the loads unrolled (to have several in flight) and leave everything
 // else rolled.
-constexpr int kLLUnroll = 4;
+// Vectors a lane has in flight per batch: with 128-thread teams one batch covers a DeepSeek-V3
+// dispatch record (536 vectors) and one a combine row (1024 vectors).
+constexpr int kLLUnrollDispatch = 5;
+constexpr int kLLUnrollCombine = 8;
 
 // Per-team scratch in dynamic shared memory: [header | scales | payload (fused quantisation)].
 struct LLSide {
@@ -207,7 +210,7 @@ __device__ void dispatch_send_tokens_ll(const A2AConfig& cfg, const A2ARankState
   const int hs = cfg.hidden_dim_scale;
   const uint32_t scale_vecs = cfg.d_scale_bytes / 16;
   const uint32_t nphys = cfg.d_stride / 16;  // lines * 8
-  constexpr int U = kLLUnroll;
+  constexpr int U = kLLUnrollDispatch;
   const bool quant = a.quantize != 0;
   const LLSide side = ll_side(cfg, side_base, team.in_block, quant);
   __shared__ uint8_t* s_dst[kMaxTeams][kMaxRanks];
@@ -362,7 +365,7 @@ __device__ void dispatch_recv_records_ll(const A2AConfig& cfg, const A2ARankStat
   const uint32_t total_recs = lay.rec_prefix[G];
   const uint8_t* drecv = st.recv[rank] + cfg.off_drecv;
   const uint32_t hdr_phys = min(nphys, 32u);  // the header fits the lines one warp covers
-  constexpr int U = kLLUnroll;
+  constexpr int U = kLLUnrollDispatch;
   const LLSide side = ll_side(cfg, side_base, team.in_block, false);
   float* os = reinterpret_cast<float*>(a.out_x_scale);
 
@@ -491,7 +494,7 @@ __device__ void combine_send_rows_ll(const A2AConfig& cfg, const A2ARankState& s
   const int K = cfg.topk;
   const uint32_t nvec = static_cast<uint32_t>(cfg.hidden_dim) * cfg.out_elemsize / 16;
   const uint32_t nphys = cfg.c_stride / 16;
-  constexpr int U = kLLUnroll;
+  constexpr int U = kLLUnrollCombine;
   const Vec16 flag = {tag, tag, tag, tag};
 
   if (cfg.combine_mode == kCombinePerRoute) {
@@ -499,12 +502,9 @@ __device__ void combine_send_rows_ll(const A2AConfig& cfg, const A2ARankState& s
     #pragma unroll 1
     for (uint32_t row = team.id; row < rows; row += team.count) {
       const uint8_t* src = a.expert_y + static_cast<uint64_t>(row) * a.expert_y_stride;
-      const uint32_t g = ws.row_src[row];
-      const uint32_t tk = ws.row_tk[row];
-      if (g == kNoSlot) continue;  // padding row; uniform across the team
-      #pragma unroll 1
-      for (uint32_t p0 = team.lane; p0 < nphys; p0 += TEAM * U) {
-        Vec16 v[U];
+      // the row's bytes do not depend on where it goes: fetch the first batch with its destination
+      Vec16 v[U];
+      auto fetch = [&](uint32_t p0) {
         #pragma unroll
         for (int u = 0; u < U; ++u) {
           const uint32_t p = p0 + u * TEAM;
@@ -514,6 +514,14 @@ __device__ void combine_send_rows_ll(const A2AConfig& cfg, const A2ARankState& s
             v[u] = lv < nvec ? ld_input_v4(src + 16ull * lv) : Vec16{0, 0, 0, 0};
           }
         }
+      };
+      fetch(team.lane);
+      const uint32_t g = ws.row_src[row];
+      const uint32_t tk = ws.row_tk[row];
+      if (g == kNoSlot) continue;  // padding row; uniform across the team
+      #pragma unroll 1
+      for (uint32_t p0 = team.lane; p0 < nphys; p0 += TEAM * U) {
+        if (p0 != static_cast<uint32_t>(team.lane)) fetch(p0);
         #pragma unroll 1
         for (int m = 0; m < cfg.dp_size; ++m) {
           uint8_t* dst = st.recv[g * cfg.dp_size + m] + cfg.off_crecv + static_cast<uint64_t>(tk) * cfg.c_stride;
@@ -528,6 +536,7 @@ __device__ void combine_send_rows_ll(const A2AConfig& cfg, const A2ARankState& s
     }
   } else {
     constexpr int N = VecElems<Y>::N;
+    constexpr int UP = 4;  // accumulators per lane: UP x 8 floats
     const uint32_t recs = ws.expert_meta[1];
     #pragma unroll 1
     for (uint32_t r = team.id; r < recs; r += team.count) {
@@ -547,10 +556,10 @@ __device__ void combine_send_rows_ll(const A2AConfig& cfg, const A2ARankState& s
       const uint32_t n = s_n[team.in_block];
       const uint64_t slot = static_cast<uint64_t>(t) * cfg.world + st.rank;
       #pragma unroll 1
-      for (uint32_t p0 = team.lane; p0 < nphys; p0 += TEAM * U) {
-        float acc[U][8];
+      for (uint32_t p0 = team.lane; p0 < nphys; p0 += TEAM * UP) {
+        float acc[UP][8];
         #pragma unroll
-        for (int u = 0; u < U; ++u) {
+        for (int u = 0; u < UP; ++u) {
           #pragma unroll
           for (int q = 0; q < 8; ++q) acc[u][q] = 0.f;
         }
@@ -558,15 +567,15 @@ __device__ void combine_send_rows_ll(const A2AConfig& cfg, const A2ARankState& s
         for (uint32_t j = 0; j < n; ++j) {
           const uint8_t* row = a.expert_y + static_cast<uint64_t>(s_rows[team.in_block][j]) * a.expert_y_stride;
           const float w = __uint_as_float(s_wbits[team.in_block][j]);
-          Vec16 x[U];
+          Vec16 x[UP];
           #pragma unroll
-          for (int u = 0; u < U; ++u) {
+          for (int u = 0; u < UP; ++u) {
             const uint32_t p = p0 + u * TEAM;
             x[u] = Vec16{0, 0, 0, 0};
             if (p < nphys && !ll_is_flag(p) && ll_logical(p) < nvec) x[u] = ld_input_v4(row + 16ull * ll_logical(p));
           }
           #pragma unroll
-          for (int u = 0; u < U; ++u) {
+          for (int u = 0; u < UP; ++u) {
             float f[8];
             VecElems<Y>::unpack(x[u], f);
             #pragma unroll
@@ -574,7 +583,7 @@ __device__ void combine_send_rows_ll(const A2AConfig& cfg, const A2ARankState& s
           }
         }
         #pragma unroll
-        for (int u = 0; u < U; ++u) {
+        for (int u = 0; u < UP; ++u) {
           const uint32_t p = p0 + u * TEAM;
           if (p < nphys) {
             Vec16 out = flag;
