@@ -86,6 +86,12 @@ A2AConfig a2a_make_config(const A2AParams& p, int num_sms, int virtual_ranks) {
   }
   c.c_records_per_token = p.combine_mode == kCombinePreReduce ? p.world : p.topk;
   c.counts_stride = round_up_u32(1 + c.experts_per_rank, 4);
+  int count_sources = c.num_groups;
+  if (wire == kWireLL) {
+    // flagged lines, one set per source *rank*: seven data vectors per 128-byte line
+    c.counts_stride = (c.counts_stride / 4 + 6) / 7 * 32;
+    count_sources = p.world;
+  }
 
   const uint64_t rows_per_token = std::min(p.topk, c.experts_per_rank);
   uint64_t rows = static_cast<uint64_t>(c.num_groups) * p.max_num_tokens * rows_per_token +
@@ -97,7 +103,7 @@ A2AConfig a2a_make_config(const A2AParams& p, int num_sms, int virtual_ranks) {
   const uint64_t flag_bytes =
       static_cast<uint64_t>(kNumFlagRows) * kMaxRanks * kFlagStrideWords * sizeof(uint32_t);
   c.off_counts = flag_bytes;
-  c.counts_bank_words = static_cast<uint32_t>(c.num_groups) * c.counts_stride;
+  c.counts_bank_words = static_cast<uint32_t>(count_sources) * c.counts_stride;
   c.off_tok_arrive = round_up_u64(c.off_counts + 2ull * 4ull * c.counts_bank_words, 128);
   c.sync_bytes = round_up_u64(c.off_tok_arrive + 4ull * p.max_num_tokens, 4096);
 

@@ -107,6 +107,29 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
       }
     }
     __syncthreads();
+    if constexpr (WIRE == kWireLL) {
+      // Flagged lines, to every rank (zeros where this rank serves no records): no fence, and
+      // the lines themselves tell the receiver that this rank has started the dispatch.
+      const uint32_t per_dst = cfg.counts_stride / 4;  // physical vectors per (source, destination)
+      for (uint32_t i = threadIdx.x; i < world * per_dst; i += blockDim.x) {
+        const uint32_t d = i / per_dst, pv = i % per_dst;
+        const bool served = static_cast<int>(d % cfg.dp_size) == my_tp;
+        Vec16 v = {tag, tag, tag, tag};
+        if (!ll_is_flag(pv)) {
+          uint32_t word[4];
+          #pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t wi = 4 * ll_logical(pv) + c;
+            const uint32_t e = d * L + (wi - 1);
+            word[c] = !served ? 0u : wi == 0 ? nrec[d] : (wi <= static_cast<uint32_t>(L) && e < static_cast<uint32_t>(cfg.num_experts)) ? hist[e] : 0u;
+          }
+          v = Vec16{word[0], word[1], word[2], word[3]};
+        }
+        uint8_t* dst = st.sync[d] + cfg.off_counts +
+                       4ull * (par * cfg.counts_bank_words + st.rank * cfg.counts_stride) + 16ull * pv;
+        st_stream_v4(dst, v);
+      }
+    } else {
     const int per_dst = L + 1;
     for (int i = threadIdx.x; i < world * per_dst; i += blockDim.x) {
       const int d = i / per_dst;
@@ -127,6 +150,7 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
     if (threadIdx.x < world) {
       st_release_sys(flag_ptr(st.sync[threadIdx.x], kFlagDispatchStarted, st.rank), tag);
     }
+    }  // plain wire
     if (cfg.trace && threadIdx.x == 0) ws.trace[kTraceSendSignalled] = globaltimer_ns();
   }
 
@@ -336,56 +360,93 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
   __shared__ uint32_t s_unused[kMaxTeams][kMaxTopK];
   __shared__ uint32_t s_nrows[kMaxTeams];
 
-  if (threadIdx.x == 0) s_abort = ws.status[0] != 0 ? 1u : 0u;
+  __shared__ uint32_t s_nrec[kMaxRanks];
+  uint32_t* cnt = dyn_smem;           // [G][L]
+  uint32_t* base = cnt + G * L;       // [G][L]  first row of (group, expert)
+  uint32_t* total = base + G * L;     // [L]
+  uint32_t* pad_off = total + L;      // [L]
+  uint32_t* misc = pad_off + L;       // [0] padded row count
+  const uint32_t pad = static_cast<uint32_t>(cfg.expert_padding);
+
+  if (threadIdx.x == 0) s_abort = 0;
   __syncthreads();
-  // the counts message of this dispatch from every rank (ranks of another tensor-parallel
-  // lane send no counts here, only the word)
-  if (threadIdx.x < cfg.world) {
-    uint64_t waited;
-    const bool ok = wait_flag(flag_ptr(st.sync[rank], kFlagDispatchStarted, threadIdx.x), tag,
-                              cfg.wait_limit_ns, &waited);
-    if (!ok) {
-      report(ws, kStatusWaitTimeout, kPhaseDispatchRecv, threadIdx.x, tag);
+  // The counts message of this dispatch from every rank (ranks of another tensor-parallel lane
+  // send no counts here, only the fact that they have started). The status word is fetched
+  // while the wait runs.
+  if constexpr (WIRE == kWireLL) {
+    const uint32_t per_src = cfg.counts_stride / 4;  // physical vectors per source rank
+    const uint32_t total_pv = cfg.world * per_src;
+    const uint8_t* lines = st.sync[rank] + cfg.off_counts + 4ull * par * cfg.counts_bank_words;
+    const uint32_t warp_first = threadIdx.x & ~31u;
+    for (uint32_t w0 = warp_first; w0 < total_pv; w0 += blockDim.x) {
+      const uint32_t i = w0 + (threadIdx.x & 31u);
+      Vec16 v[1];
+      const bool ok = ll_load_lines<1>(
+          v, tag, [&](int) { return lines + 16ull * i; }, [&](int) { return i < total_pv; },
+          cfg.wait_limit_ns, ws.status);
+      if (!ok) {
+        if ((threadIdx.x & 31u) == 0) report(ws, kStatusWaitTimeout, kPhaseDispatchRecv, i / per_src, tag);
+        s_abort = 1;
+      } else if (i < total_pv) {
+        const uint32_t src = i / per_src, pv = i % per_src;
+        if (!ll_is_flag(pv) && static_cast<int>(src % cfg.dp_size) == rank % cfg.dp_size) {
+          const uint32_t g = src / cfg.dp_size;
+          const uint32_t word[4] = {v[0].x, v[0].y, v[0].z, v[0].w};
+          #pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t wi = 4 * ll_logical(pv) + c;
+            if (wi == 0) s_nrec[g] = min(word[c], static_cast<uint32_t>(cfg.max_num_tokens));
+            else if (wi <= static_cast<uint32_t>(L)) cnt[g * L + (wi - 1)] = word[c];
+          }
+        }
+      }
+    }
+    if (threadIdx.x == 0 && ws.status[0] != 0) s_abort = 1;
+  } else {
+    if (threadIdx.x < cfg.world) {
+      uint64_t waited;
+      const bool ok = wait_flag(flag_ptr(st.sync[rank], kFlagDispatchStarted, threadIdx.x), tag,
+                                cfg.wait_limit_ns, &waited);
+      if (!ok) {
+        report(ws, kStatusWaitTimeout, kPhaseDispatchRecv, threadIdx.x, tag);
+        s_abort = 1;
+      }
+      if (blockIdx.x == 0) atomicMax(&ws.stats[2], static_cast<unsigned long long>(waited));
+    } else if (threadIdx.x == 32 && ws.status[0] != 0) {
       s_abort = 1;
     }
-    if (blockIdx.x == 0) atomicMax(&ws.stats[2], static_cast<unsigned long long>(waited));
+    __syncthreads();
+    if (s_abort == 0) {
+      const uint32_t* counts = reinterpret_cast<const uint32_t*>(st.sync[rank] + cfg.off_counts) +
+                               par * cfg.counts_bank_words;
+      for (int i = threadIdx.x; i < G * L; i += blockDim.x) {
+        const int g = i / L, le = i % L;
+        cnt[i] = ld_relaxed_sys(counts + g * cfg.counts_stride + 1 + le);
+      }
+      if (threadIdx.x < G) {
+        s_nrec[threadIdx.x] = min(ld_relaxed_sys(counts + threadIdx.x * cfg.counts_stride),
+                                  static_cast<uint32_t>(cfg.max_num_tokens));
+      }
+    }
   }
   __syncthreads();
   const bool abort = s_abort != 0;  // uniform across the block
   trace_mark(cfg, ws, kTraceRecvWaitDone);
 
   // ---- expert-major layout from the counts (every block computes it privately) ----
-  uint32_t* cnt = dyn_smem;           // [G][L]
-  uint32_t* base = cnt + G * L;       // [G][L]  first row of (group, expert)
-  uint32_t* total = base + G * L;     // [L]
-  uint32_t* pad_off = total + L;      // [L]
-  uint32_t* misc = pad_off + L;       // [0] padded row count
-  const uint32_t* counts = reinterpret_cast<const uint32_t*>(st.sync[rank] + cfg.off_counts) +
-                           par * cfg.counts_bank_words;
-  const uint32_t pad = static_cast<uint32_t>(cfg.expert_padding);
   if (!abort) {
-    for (int i = threadIdx.x; i < G * L; i += blockDim.x) {
-      const int g = i / L, le = i % L;
-      cnt[i] = ld_relaxed_sys(counts + g * cfg.counts_stride + 1 + le);
-    }
-    // records per source group, prefix-summed by the first warp (the loads run in parallel)
+    // records per source group, prefix-summed by the first warp
     if (threadIdx.x < 32) {
-      uint32_t n = 0;
-      if (threadIdx.x < G) {
-        n = min(ld_relaxed_sys(counts + threadIdx.x * cfg.counts_stride),
-                static_cast<uint32_t>(cfg.max_num_tokens));
-      }
+      const uint32_t n = threadIdx.x < G ? s_nrec[threadIdx.x] : 0u;
       uint32_t incl = n;
       #pragma unroll
       for (int o = 1; o < kMaxRanks; o <<= 1) {
         const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
         if (threadIdx.x >= o) incl += up;
       }
-      if (threadIdx.x <= kMaxRanks) {
-        // lane g holds the inclusive sum up to group g; entry g + 1 is "records before g + 1"
-        if (threadIdx.x == 0) s_rec_prefix[0] = 0;
-        if (threadIdx.x < kMaxRanks) s_rec_prefix[threadIdx.x + 1] = incl;
-      }
+      // lane g holds the inclusive sum up to group g; entry g + 1 is "records before g + 1"
+      if (threadIdx.x == 0) s_rec_prefix[0] = 0;
+      if (threadIdx.x < kMaxRanks) s_rec_prefix[threadIdx.x + 1] = incl;
     }
     __syncthreads();
     // totals per expert, in parallel over the experts
@@ -581,6 +642,10 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
   __shared__ uint32_t* s_pend[kMaxTeams][kMaxPending];
   __shared__ uint32_t s_npend[kMaxTeams];
   if (threadIdx.x < kMaxTeams) s_npend[threadIdx.x] = 0;
+  // issued together with the status word, not after it: each is a cold miss
+  const uint32_t tag_c = read_epoch(ws, 1) + 1;
+  const uint32_t meta_rows = ws.expert_meta[0];
+  const uint32_t meta_recs = ws.expert_meta[1];
   if (threadIdx.x == 0) s_healthy = ws.status[0] == 0 ? 1u : 0u;
   __syncthreads();
   const bool healthy = s_healthy != 0;
@@ -609,9 +674,11 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
   };
 
   if constexpr (WIRE == kWireLL) {
-    if (healthy) combine_send_rows_ll<Y>(cfg, st, a, read_epoch(ws, 1) + 1, TEAM, s_rows, s_wbits, s_n);
+    if (healthy) {
+      combine_send_rows_ll<Y>(cfg, st, a, tag_c, meta_rows, meta_recs, TEAM, s_rows, s_wbits, s_n);
+    }
   } else if (healthy && cfg.combine_mode == kCombinePerRoute) {
-    const uint32_t rows = ws.expert_meta[0];
+    const uint32_t rows = meta_rows;
     const uint32_t nvec = cfg.c_stride / 16;
     constexpr int U = kCopyUnroll;
     for (uint32_t row = team.id; row < rows; row += team.count) {
@@ -659,7 +726,7 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
     }
     flush();
   } else if (healthy) {
-    const uint32_t recs = ws.expert_meta[1];
+    const uint32_t recs = meta_recs;
     const uint32_t ngran = cfg.hidden_dim / 8;
     for (uint32_t r = team.id; r < recs; r += team.count) {
       const uint32_t t = ws.rec_token[2 * r];

@@ -378,19 +378,35 @@ __device__ void dispatch_recv_records_ll(const A2AConfig& cfg, const A2ARankStat
     }
     const uint32_t s = r - lay.rec_prefix[g];
     const uint8_t* rec = drecv + g * cfg.drecv_group_stride + static_cast<uint64_t>(s) * cfg.d_stride;
-    if (team.lane < 32) {
-      Vec16 h[1];
-      const uint32_t p = team.lane;
-      bool ok = *reinterpret_cast<const volatile uint32_t*>(ws.status) == 0;
-      ok = __all_sync(0xffffffffu, ok);
-      if (ok) {
-        ok = ll_load_lines<1>(
-            h, tag, [&](int) { return rec + 16ull * p; }, [&](int) { return p < hdr_phys; },
-            cfg.wait_limit_ns, ws.status);
-        if (!ok && p == 0) report(ws, kStatusWaitTimeout, kPhaseDispatchRecv, g, r);
+    // Every warp fetches its share of the record's first batch at once (header lines included):
+    // a line that is not there yet is simply read again. The header only decides where the
+    // payload goes, so nothing waits for it before the payload is in registers.
+    const uint32_t warp_first = team.lane & ~31u;  // a warp's 32 vectors are four whole lines
+    const uint32_t lane32 = team.lane & 31u;
+    Vec16 v[U];
+    bool failed = false;
+    {
+      bool go = true;
+      if (team.lane < 32) {
+        go = *reinterpret_cast<const volatile uint32_t*>(ws.status) == 0;
+        go = __all_sync(0xffffffffu, go);
       }
+      if (go && warp_first < nphys) {
+        const uint32_t p0 = warp_first + lane32;
+        const bool ok = ll_load_lines<U>(
+            v, tag, [&](int u) { return rec + 16ull * (p0 + u * TEAM); },
+            [&](int u) { return p0 + u * TEAM < nphys; }, cfg.wait_limit_ns, ws.status);
+        if (!ok && lane32 == 0) report(ws, kStatusWaitTimeout, kPhaseDispatchRecv, g, r);
+        failed = !ok;
+      } else {
+        failed = !go;
+      }
+    }
+    if (team.lane < 32) {
+      const uint32_t p = team.lane;
+      bool ok = !failed;
       if (ok && p < hdr_phys && !ll_is_flag(p) && ll_logical(p) < hdr_vecs) {
-        *reinterpret_cast<Vec16*>(side.hdr + 4 * ll_logical(p)) = h[0];
+        *reinterpret_cast<Vec16*>(side.hdr + 4 * ll_logical(p)) = v[0];
       }
       __syncwarp();
       const int k = team.lane;
@@ -432,20 +448,18 @@ __device__ void dispatch_recv_records_ll(const A2AConfig& cfg, const A2ARankStat
     const uint32_t nrows = s_nrows[team.in_block];
     if (nrows == kTeamAbort) break;  // uniform across the team
     if (nrows != 0) {
-      // warp-uniform trip count: a warp's 32 vectors are four whole lines
-      const uint32_t warp_first = team.lane & ~31u;
-      bool failed = false;
       #pragma unroll 1
       for (uint32_t w0 = warp_first; w0 < nphys && !failed; w0 += TEAM * U) {
-        const uint32_t p0 = w0 + (team.lane & 31u);
-        Vec16 v[U];
-        const bool ok = ll_load_lines<U>(
-            v, tag, [&](int u) { return rec + 16ull * (p0 + u * TEAM); },
-            [&](int u) { return p0 + u * TEAM < nphys; }, cfg.wait_limit_ns, ws.status);
-        if (!ok) {
-          failed = true;
-          if ((team.lane & 31u) == 0) report(ws, kStatusWaitTimeout, kPhaseDispatchRecv, g, r);
-          break;
+        const uint32_t p0 = w0 + lane32;
+        if (w0 != warp_first) {
+          const bool ok = ll_load_lines<U>(
+              v, tag, [&](int u) { return rec + 16ull * (p0 + u * TEAM); },
+              [&](int u) { return p0 + u * TEAM < nphys; }, cfg.wait_limit_ns, ws.status);
+          if (!ok) {
+            failed = true;
+            if (lane32 == 0) report(ws, kStatusWaitTimeout, kPhaseDispatchRecv, g, r);
+            break;
+          }
         }
         #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -486,9 +500,9 @@ __device__ void dispatch_recv_records_ll(const A2AConfig& cfg, const A2ARankStat
 
 template <typename Y>
 __device__ void combine_send_rows_ll(const A2AConfig& cfg, const A2ARankState& st,
-                                     const CombineSendArgs& a, uint32_t tag, const int TEAM,
-                                     uint32_t (*s_rows)[kMaxTopK], uint32_t (*s_wbits)[kMaxTopK],
-                                     uint32_t* s_n) {
+                                     const CombineSendArgs& a, uint32_t tag, uint32_t rows,
+                                     uint32_t recs, const int TEAM, uint32_t (*s_rows)[kMaxTopK],
+                                     uint32_t (*s_wbits)[kMaxTopK], uint32_t* s_n) {
   const A2ALocal& ws = st.local;
   const Team team(TEAM);
   const int K = cfg.topk;
@@ -498,7 +512,6 @@ __device__ void combine_send_rows_ll(const A2AConfig& cfg, const A2ARankState& s
   const Vec16 flag = {tag, tag, tag, tag};
 
   if (cfg.combine_mode == kCombinePerRoute) {
-    const uint32_t rows = ws.expert_meta[0];
     #pragma unroll 1
     for (uint32_t row = team.id; row < rows; row += team.count) {
       const uint8_t* src = a.expert_y + static_cast<uint64_t>(row) * a.expert_y_stride;
@@ -537,7 +550,6 @@ __device__ void combine_send_rows_ll(const A2AConfig& cfg, const A2ARankState& s
   } else {
     constexpr int N = VecElems<Y>::N;
     constexpr int UP = 4;  // accumulators per lane: UP x 8 floats
-    const uint32_t recs = ws.expert_meta[1];
     #pragma unroll 1
     for (uint32_t r = team.id; r < recs; r += team.count) {
       const uint32_t t = ws.rec_token[2 * r];
