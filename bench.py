@@ -254,6 +254,19 @@ def main() -> None:
         raise SystemExit("launch with torch.distributed.run for --gpus > 1")
     device = torch.device("cuda", local_rank)
     torch.cuda.set_device(device)
+    # Run this process (and first-touch its pinned staging buffers) on cores of the GPU's own
+    # NUMA node, as the reference does for its worker threads
+    # (python/pplx_garden/kernels/p2p_all_to_all.py:120-134).
+    affinity = "unchanged"
+    try:
+        from pplx_garden.fabric_lib import TransferEngine
+
+        for group in TransferEngine.detect_topology():
+            if group.cuda_device == device.index and group.cpus:
+                os.sched_setaffinity(0, set(group.cpus))
+                affinity = f"{len(group.cpus)} cores of NUMA node {group.numa}"
+    except Exception as exc:  # topology is best effort: a container may hide sysfs
+        affinity = f"unchanged ({type(exc).__name__})"
     process_group = global_group = None
     if world > 1:
         process_group = ProcessGroup.from_env(device)
@@ -521,6 +534,7 @@ def main() -> None:
                 "parallelism": f"ep{world}",
                 "combine_mode": args.combine_mode,
                 "l2": "flushed between timed steps (256 MiB device write, then read, before each start event)",
+                "cpu_affinity": affinity,
                 "line_up": "before each start event: NCCL all-reduce, then the library's device barrier (untimed)",
                 "baseline_note": "vs_baseline divides by the reference's published EP8 dispatch+combine "
                                  "(113.9 us decode / 2449.1 us prefill), whatever n_gpus is",

@@ -29,7 +29,7 @@ import torch
 from pplx_garden.distributed import ParallelGroup, ParallelLaunch
 from pplx_garden.kernels.p2p_all_to_all import P2PAllToAll
 from pplx_garden.utils.math import Statistics, ceil_div, round_up
-from pplx_garden.utils.torch import str_to_dtype
+from pplx_garden.utils.torch import profile_range, str_to_dtype
 
 
 @dataclass
@@ -148,7 +148,13 @@ def _worker(device: torch.device, dp_group: Optional[ParallelGroup], global_grou
         nccl_d_out, nccl_c_out = torch.empty_like(nccl_d), torch.empty_like(nccl_c)
 
         names = ("dispatch", "combine", "dispatch_send", "dispatch_recv", "combine_send", "combine_recv",
+                 "overlap_dispatch_send", "overlap_work", "overlap_dispatch_recv",
+                 "overlap_combine_send", "overlap_combine_recv", "overlap_step",
                  "nccl_dispatch", "nccl_combine")
+        # "other work" that a micro-batched model runs between the send and the receive half of a
+        # phase (the reference's overlap section: benchmarks/bench_all_to_all.py:406-425)
+        fake_n = 1024 if cfg.max_num_tokens <= 128 else 4096
+        fake = torch.empty((fake_n, fake_n), dtype=torch.bfloat16, device=device).normal_()
         times: dict[str, list[float]] = {k: [] for k in names}
 
         def timed(fn) -> torch.cuda.Event:
@@ -159,6 +165,9 @@ def _worker(device: torch.device, dp_group: Optional[ParallelGroup], global_grou
             return s, e
 
         for it in range(num_warmup + num_repeats):
+            if it == max(num_warmup - 1, 0):
+                # capture range for `nsys --capture-range=cudaProfilerApi` (reference :359-361)
+                torch.cuda.profiler.start()
             ev = {}
             wait()
             ev["dispatch"] = timed(lambda: dispatch(True, True))
@@ -172,6 +181,20 @@ def _worker(device: torch.device, dp_group: Optional[ParallelGroup], global_grou
             ev["combine_send"] = timed(lambda: combine(True, False))
             wait()
             ev["combine_recv"] = timed(lambda: combine(False, True))
+            # overlap section: send half, other work, receive half, all on one stream
+            wait()
+            ov_start = torch.cuda.Event(enable_timing=True)
+            ov_end = torch.cuda.Event(enable_timing=True)
+            ov_start.record()
+            with profile_range("overlap"):
+                ev["overlap_dispatch_send"] = timed(lambda: dispatch(True, False))
+                ev["overlap_work"] = timed(lambda: torch.matmul(fake, fake))
+                ev["overlap_dispatch_recv"] = timed(lambda: dispatch(False, True))
+                ev["overlap_combine_send"] = timed(lambda: combine(True, False))
+                _ = fake @ fake
+                ev["overlap_combine_recv"] = timed(lambda: combine(False, True))
+            ov_end.record()
+            ev["overlap_step"] = (ov_start, ov_end)
             if global_group is not None:
                 wait()
                 ev["nccl_dispatch"] = timed(lambda: torch.distributed.all_to_all_single(nccl_d_out, nccl_d))
@@ -182,6 +205,7 @@ def _worker(device: torch.device, dp_group: Optional[ParallelGroup], global_grou
                 for k, (s, e) in ev.items():
                     times[k].append(s.elapsed_time(e) * 1000.0)
 
+        torch.cuda.profiler.stop()
         if global_group is not None:
             for k in names:
                 times[k] = sum(global_group.all_gather_object(times[k]), [])

@@ -44,15 +44,6 @@ def _pybind_include() -> str:
     return pybind11.get_include()
 
 
-def _cutlass_include() -> str | None:
-    """CUTLASS/CuTe headers vendored inside an installed wheel (header-only use)."""
-    for site in sys.path:
-        cand = Path(site) / "flashinfer" / "data" / "cutlass" / "include"
-        if (cand / "cute" / "tensor.hpp").exists():
-            return str(cand)
-    return None
-
-
 def _sources() -> dict[str, list[Path]]:
     groups: dict[str, list[Path]] = {"ext": [], "noalloc": [], "fabric_debug": [], "unigram_cli": [], "core_tests": []}
     for path in sorted(CSRC.rglob("*")):
@@ -92,15 +83,13 @@ def write_ninja(verbose: bool) -> Path:
     nvflags = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC",
                "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
                "-Xptxas", "-v" if verbose else "-warn-spills"] + NVCC_ARCH + defines
-    cutlass = _cutlass_include()
-    cutlass_inc = [f"-I{cutlass}"] if cutlass else []
     lines = [
         "ninja_required_version = 1.3",
         f"cxx = {os.environ.get('CXX', 'g++')}",
         f"nvcc = {CUDA_HOME}/bin/nvcc",
         f"cxxflags = {' '.join(cxxflags + common_inc)}",
         f"pyflags = -I{py_inc} -I{_pybind_include()}",
-        f"nvflags = {' '.join(nvflags + common_inc + cutlass_inc)}",
+        f"nvflags = {' '.join(nvflags + common_inc)}",
         f"ldflags = -L{CUDA_HOME}/lib64 -lcudart_static -ldl -lrt -lpthread",
         "rule cxx",
         "  command = $cxx -MMD -MF $out.d $cxxflags $extra -c $in -o $out",

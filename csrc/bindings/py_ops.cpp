@@ -89,7 +89,11 @@ void bind_ops(py::module_& m) {
           sc.done_counter = reinterpret_cast<uint32_t*>(t[7].cast<uint64_t>());
           sc.status = reinterpret_cast<const uint32_t*>(t[8].cast<uint64_t>());
         }
-        grouped_fp8_gemm(p, reinterpret_cast<cudaStream_t>(stream));
+        if (p.wait_cycles != nullptr || p.trace != nullptr || p.debug_skip != 0) {
+          grouped_fp8_gemm_profiled(p, reinterpret_cast<cudaStream_t>(stream));
+        } else {
+          grouped_fp8_gemm(p, reinterpret_cast<cudaStream_t>(stream));
+        }
       },
       py::arg("a"), py::arg("a_stride"), py::arg("a_scale"), py::arg("a_scale_stride_row"),
       py::arg("a_scale_stride_k"), py::arg("b"), py::arg("b_scale"), py::arg("expert_num_tokens"), py::arg("out"),

@@ -10,18 +10,26 @@
 //                 to e4m3 with 1x128 scales -> the input of the down projection
 //   kBf16         out = D as bf16 -> the rows handed to combine
 //
-// Structure (one persistent CTA per SM, three warpgroups):
-//   warp 0      TMA producer: 128x128-byte A tile + four 64-row B boxes per K block into a
-//               4-stage shared-memory ring (SWIZZLE_128B), completion on mbarriers
-//   warps 1, 2  one thread each issues tcgen05.mma (M 128, N 256, K 32 x 4 per K block) into its
-//               own 256-column TMEM accumulator (even / odd K blocks) and commits to mbarriers
-//   (warp 3 idle; the first warpgroup gives most of its registers away with setmaxnreg)
+// Structure: one persistent CTA per SM, twelve warps, launched as clusters of two CTAs. The
+// body is a template on the CTAs per tile:
+//   pairs (256-row tiles)  the two CTAs of a cluster compute one 256 x 256 tile with
+//               tcgen05.mma.cta_group::2 (M 256, N 256, K 32 x 4 per K block). Each CTA loads its
+//               own 128 rows of A and its own half of B's rows (TMA with cta_group::2, bytes
+//               counted on the leader's mbarrier, 128-byte swizzle) and keeps its 128 rows of the
+//               accumulator in its own tensor memory; the leader's commit (two-CTA mask) releases
+//               the stage and publishes the accumulator in both CTAs.
+//   lone CTA (128-row tiles)  cta_group::1, all four B boxes per stage; chosen when an expert's
+//               capacity is 192 rows or less, where the second CTA of a pair would idle.
+//   warp 0      TMA producer into a four-stage shared-memory ring (the count must be even, see
+//               kStages) and, before the loop, the tile schedule from the experts' row counts
+//   warps 1, 2  (leader CTA) one MMA issuer per 256-column TMEM accumulator, even / odd K blocks
+//   warp 3      idle; the first warpgroup gives most of its registers away with setmaxnreg
 //   warps 4-11  epilogue: tcgen05.ld the K block's partial sums, scale them by
 //               a_scale[row, kb] * b_scale[nb, kb] and add into fp32 registers (the per-block
-//               scales differ along K, so the running sum cannot stay in TMEM), then apply the
-//               epilogue and store
+//               scales differ along K, so the running sum cannot stay in TMEM), then SwiGLU +
+//               re-quantise or bf16, staged through shared memory into full-line stores
 // The two TMEM accumulators let the tensor cores work on K block i+1 while block i is being
-// folded. No TMA multicast, no clusters: every CTA loads its own tiles.
+// folded. No TMA multicast anywhere: B is shared inside a pair by each CTA loading half of it.
 //
 // The reference has no GEMM of any kind (its "expert" is x * 2 in tests and benchmarks:
 // tests/p2p_all_to_all/test_p2p_all_to_all.py:44-50); this kernel is the expert-side half of
@@ -37,6 +45,17 @@
 #include "../core/cu_driver.h"
 #include "../core/error.h"
 #include "tcgen05.cuh"
+
+// The profiling aids (per-role wait totals, SM-clock stamps, stage removal) exist only in the
+// translation unit built with PPLX_GEMM_PROFILE (grouped_gemm_profile.cu, entry point
+// grouped_fp8_gemm_profiled); here they compile to nothing.
+#ifdef PPLX_GEMM_PROFILE
+#define PPLX_GEMM_ENTRY grouped_fp8_gemm_profiled
+constexpr bool kProfile = true;
+#else
+#define PPLX_GEMM_ENTRY grouped_fp8_gemm
+constexpr bool kProfile = false;
+#endif
 
 namespace pplx::ops {
 namespace {
@@ -239,7 +258,7 @@ __device__ __forceinline__ void grouped_fp8_gemm_body(const KernelArgs& a) {
   const int num_pairs = gridDim.x / kCtas;
 
   if (threadIdx.x == 0) {
-    if (a.trace != nullptr && blockIdx.x == 0) {   // last row: kernel start / end, SM clock and ns
+    if (kProfile && a.trace != nullptr && blockIdx.x == 0) {   // last row: kernel start / end, SM clock and ns
       a.trace[(kTraceTiles - 1) * 8 + 0] = clock64();
       a.trace[(kTraceTiles - 1) * 8 + 1] = static_cast<long long>(globaltimer_ns());
     }
@@ -363,7 +382,7 @@ __device__ __forceinline__ void grouped_fp8_gemm_body(const KernelArgs& a) {
             for (int i = 0; i < kBBoxes; ++i) brow[i] = e * a.N + n_tile * kBN + 64 * i;
           }
         }
-        const int trace_row = (a.trace != nullptr && blockIdx.x == 0 && t / num_pairs < 32) ? t / num_pairs : -1;
+        const int trace_row = (kProfile && a.trace != nullptr && blockIdx.x == 0 && t / num_pairs < 32) ? t / num_pairs : -1;
         if (trace_row >= 0) a.trace[trace_row * 8 + 6] = clock64();
         for (int kb = 0; kb < nkb; ++kb, ++it) {
           const int s = it % kStages;
@@ -377,7 +396,7 @@ __device__ __forceinline__ void grouped_fp8_gemm_body(const KernelArgs& a) {
             break;
           }
           uint8_t* stage = tiles + static_cast<size_t>(s) * kStageBytes;
-          if (a.debug_skip & 4) {   // profiling aid: hand over the stage without loading it
+          if (kProfile && (a.debug_skip & 4)) {   // profiling aid: hand over the stage without loading it
             if (rank == 0) mbar_arrive(&full_bar[s]);
             continue;
           }
@@ -399,7 +418,7 @@ __device__ __forceinline__ void grouped_fp8_gemm_body(const KernelArgs& a) {
         }
         if (trace_row >= 0) a.trace[trace_row * 8 + 7] = clock64();
       }
-      if (a.wait_cycles != nullptr) a.wait_cycles[blockIdx.x * 4 + 0] = static_cast<unsigned long long>(waited);
+      if (kProfile && a.wait_cycles != nullptr) a.wait_cycles[blockIdx.x * 4 + 0] = static_cast<unsigned long long>(waited);
     }
   } else if ((warp == 1 || warp == 2) && rank == 0) {
     // ------------------------------------------------------------------ MMA issuers
@@ -415,9 +434,9 @@ __device__ __forceinline__ void grouped_fp8_gemm_body(const KernelArgs& a) {
       const uint32_t w = warp - 1;
       const uint32_t my_tiles = pair < total_tiles ? (total_tiles - pair + num_pairs - 1) / num_pairs : 0;
       const uint32_t total_blocks = my_tiles * static_cast<uint32_t>(nkb);
-      const bool timing = a.wait_cycles != nullptr;
-      const bool stamps = a.trace != nullptr && blockIdx.x == 0 && w == 0 && lane == 0;
-      const int reps = (a.debug_skip & 2) ? 0 : ((a.debug_skip & 8) ? 2 : 1);   // profiling aid
+      const bool timing = kProfile && a.wait_cycles != nullptr;
+      const bool stamps = kProfile && a.trace != nullptr && blockIdx.x == 0 && w == 0 && lane == 0;
+      const int reps = (kProfile && (a.debug_skip & 2)) ? 0 : ((kProfile && (a.debug_skip & 8)) ? 2 : 1);   // profiling aid
       const uint32_t d_tmem = tmem_base + w * kBN;
       long long waited_tmem = 0, waited_full = 0;
       for (uint32_t it = w; it < total_blocks; it += 2) {
@@ -525,7 +544,7 @@ __device__ __forceinline__ void grouped_fp8_gemm_body(const KernelArgs& a) {
     }
     for (int t = pair; t < total_tiles; t += num_pairs, tile_parity ^= 1u) {
       int m_pair, n_tile;
-      const int trace_row = (a.trace != nullptr && blockIdx.x == 0 && warp == kFirstEpilogueWarp && lane == 0 &&
+      const int trace_row = (kProfile && a.trace != nullptr && blockIdx.x == 0 && warp == kFirstEpilogueWarp && lane == 0 &&
                              t / num_pairs < 32) ? t / num_pairs : -1;
       if (trace_row >= 0) a.trace[trace_row * 8 + 0] = clock64();
       decode_tile(sched, a.num_experts, n_tiles, t, &e, &m_pair, &n_tile);
@@ -573,7 +592,7 @@ __device__ __forceinline__ void grouped_fp8_gemm_body(const KernelArgs& a) {
         if (kb == 0 && trace_row >= 0) a.trace[trace_row * 8 + 1] = clock64();
         const bool trace_block = trace_row >= 0 && acc_it < kTraceBlocks;
         if (trace_block) a.trace[kTraceBlockBase + acc_it * 8 + 1] = clock64();
-        if (a.debug_skip & 1) {   // profiling aid: leave the partial sums unread
+        if (kProfile && (a.debug_skip & 1)) {   // profiling aid: leave the partial sums unread
           fence_before_thread_sync();
           __syncwarp();
           if (lane == 0) {
@@ -748,7 +767,7 @@ __device__ __forceinline__ void grouped_fp8_gemm_body(const KernelArgs& a) {
       if (trace_row >= 0) a.trace[trace_row * 8 + 3] = clock64();
       if (failed) break;
     }
-    if (a.wait_cycles != nullptr && warp == kFirstEpilogueWarp && lane == 0) {
+    if (kProfile && a.wait_cycles != nullptr && warp == kFirstEpilogueWarp && lane == 0) {
       a.wait_cycles[blockIdx.x * 4 + 3] = static_cast<unsigned long long>(waited_acc);
     }
     // bulk copies this thread handed over must have been performed before the arrival signal
@@ -778,7 +797,7 @@ __device__ __forceinline__ void grouped_fp8_gemm_body(const KernelArgs& a) {
       }
     }
   }
-  if (a.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+  if (kProfile && a.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
     a.trace[(kTraceTiles - 1) * 8 + 2] = clock64();
     a.trace[(kTraceTiles - 1) * 8 + 3] = static_cast<long long>(globaltimer_ns());
   }
@@ -820,7 +839,7 @@ CUtensorMap make_map(const void* base, uint64_t rows, uint64_t cols_bytes, uint6
 
 }  // namespace
 
-void grouped_fp8_gemm(const GroupedGemmParams& p, cudaStream_t stream) {
+void PPLX_GEMM_ENTRY(const GroupedGemmParams& p, cudaStream_t stream) {
   PPLX_REQUIRE(p.K % kBK == 0 && p.K >= kBK, "K must be a multiple of 128");
   PPLX_REQUIRE(p.num_experts >= 1 && p.num_experts <= kMaxExperts, "between 1 and 128 local experts");
   PPLX_REQUIRE(p.expert_padding >= 1, "expert_padding must be positive");

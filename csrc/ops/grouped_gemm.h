@@ -75,4 +75,8 @@ struct GroupedGemmParams {
 
 void grouped_fp8_gemm(const GroupedGemmParams& params, cudaStream_t stream);
 
+// The same kernel built with its profiling aids (wait_cycles, trace, debug_skip); the regular
+// entry point ignores those three fields.
+void grouped_fp8_gemm_profiled(const GroupedGemmParams& params, cudaStream_t stream);
+
 }  // namespace pplx::ops
