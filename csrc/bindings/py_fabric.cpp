@@ -100,7 +100,23 @@ void bind_fabric(py::module_& m) {
       .def_property_readonly("cuda_device", [](const TopologyGroup& g) { return g.cuda_device; })
       .def_property_readonly("numa", [](const TopologyGroup& g) { return g.numa; })
       .def_property_readonly("domains", [](const TopologyGroup& g) { return g.domains; })
-      .def_property_readonly("cpus", [](const TopologyGroup& g) { return g.cpus; });
+      .def_property_readonly("cpus", [](const TopologyGroup& g) { return g.cpus; })
+      .def_property_readonly("pci_address", [](const TopologyGroup& g) { return g.pci_address; })
+      .def_property_readonly("pci_switch", [](const TopologyGroup& g) { return g.pci_switch; })
+      .def_property_readonly("nics", [](const TopologyGroup& g) { return g.nics; });
+  m.def(
+      "_place_gpus_from_sysfs",
+      [](const std::string& sysfs_root, const std::vector<std::string>& gpu_addresses) {
+        py::list out;
+        for (const PciGpuPlacement& p : place_gpus(scan_pci(sysfs_root), gpu_addresses)) {
+          py::list nics;
+          for (const PciNic& n : p.nics) nics.append(py::make_tuple(n.address, n.name));
+          out.append(py::make_tuple(p.gpu_address, p.pci_switch, p.numa, nics));
+        }
+        return out;
+      },
+      py::arg("sysfs_root"), py::arg("gpu_addresses"),
+      "PCI placement of GPUs (switch, NUMA node, share of the switch's RDMA NICs) from a sysfs tree.");
 
   py::class_<MemoryRegionHandle>(m, "MemoryRegionHandle")
       .def_property_readonly("ptr", [](const MemoryRegionHandle& h) { return h.ptr; })

@@ -2,6 +2,7 @@
 
 #include <cuda_runtime.h>
 #include <dirent.h>
+#include <dlfcn.h>
 
 #include <algorithm>
 #include <fstream>
@@ -86,6 +87,7 @@ std::vector<TopologyGroup> detect() {
   struct Raw {
     int device, numa;
     std::vector<int> local_cpus;
+    std::string pci_address;
   };
   std::vector<Raw> raws;
   std::map<int, std::vector<int>> devices_of_numa;
@@ -95,6 +97,7 @@ std::vector<TopologyGroup> detect() {
     if (cudaDeviceGetPCIBusId(bus, sizeof(bus), dev) == cudaSuccess) {
       std::string id(bus);
       std::transform(id.begin(), id.end(), id.begin(), ::tolower);
+      raw.pci_address = id;
       const std::string base = "/sys/bus/pci/devices/" + id;
       const std::string numa = read_file(base + "/numa_node");
       try {
@@ -117,21 +120,77 @@ std::vector<TopologyGroup> detect() {
     devices_of_numa[raw.numa].push_back(dev);
     raws.push_back(std::move(raw));
   }
-  for (const Raw& raw : raws) {
+  std::vector<std::string> gpu_addresses;
+  for (const Raw& raw : raws) gpu_addresses.push_back(raw.pci_address);
+  const std::vector<PciGpuPlacement> placement = place_gpus(scan_pci("/sys"), gpu_addresses);
+  for (size_t ri = 0; ri < raws.size(); ++ri) {
+    const Raw& raw = raws[ri];
     TopologyGroup g;
     g.cuda_device = raw.device;
     g.numa = raw.numa;
+    g.pci_address = raw.pci_address;
+    g.pci_switch = placement[ri].pci_switch;
+    for (const PciNic& nic : placement[ri].nics) {
+      const std::string rate = read_file("/sys/class/infiniband/" + nic.name + "/ports/1/rate");  // "400 Gb/sec (4X NDR)"
+      uint64_t bits = 0;
+      try {
+        bits = static_cast<uint64_t>(std::stod(rate) * 1e9);
+      } catch (...) {
+        bits = 0;
+      }
+      g.nics.push_back(DomainInfo{nic.name, bits, "unavailable"});
+    }
     const std::vector<int>& siblings = devices_of_numa[raw.numa];
     const size_t index = static_cast<size_t>(std::find(siblings.begin(), siblings.end(), raw.device) - siblings.begin());
     g.cpus = split_evenly(raw.local_cpus, siblings.size(), index);
     if (g.cpus.size() < 3) g.cpus = raw.local_cpus;  // never starve a GPU of worker cores
-    g.domains.push_back(DomainInfo{"nvl0:cuda" + std::to_string(raw.device), 7200ull * 1000 * 1000 * 1000, "local"});
+    uint64_t nvlink = nvlink_bits_per_second(raw.device);
+    if (nvlink == 0) nvlink = 7200ull * 1000 * 1000 * 1000;  // NVLink 5: 18 links x 50 GB/s per direction
+    g.domains.push_back(DomainInfo{"nvl0:cuda" + std::to_string(raw.device), nvlink, "local"});
     groups.push_back(std::move(g));
   }
   return groups;
 }
 
 }  // namespace
+
+uint64_t nvlink_bits_per_second(int cuda_device) {
+  // NVML is asked through dlopen so that nothing links against the driver's libraries.
+  struct FieldValue {  // nvmlFieldValue_t
+    uint32_t field_id, scope_id;
+    int64_t timestamp, latency_usec;
+    uint32_t value_type, nvml_return;
+    union {
+      double d;
+      uint32_t ui;
+      unsigned long ul;
+      unsigned long long ull;
+      long long sll;
+    } value;
+  };
+  using InitFn = int (*)();
+  using HandleFn = int (*)(const char*, void**);
+  using FieldsFn = int (*)(void*, int, FieldValue*);
+  static void* lib = dlopen("libnvidia-ml.so.1", RTLD_NOW | RTLD_LOCAL);
+  if (lib == nullptr) return 0;
+  static const auto init = reinterpret_cast<InitFn>(dlsym(lib, "nvmlInit_v2"));
+  static const auto by_bus = reinterpret_cast<HandleFn>(dlsym(lib, "nvmlDeviceGetHandleByPciBusId_v2"));
+  static const auto fields = reinterpret_cast<FieldsFn>(dlsym(lib, "nvmlDeviceGetFieldValues"));
+  if (init == nullptr || by_bus == nullptr || fields == nullptr || init() != 0) return 0;
+  char bus[32] = {0};
+  if (cudaDeviceGetPCIBusId(bus, sizeof(bus), cuda_device) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  void* handle = nullptr;
+  if (by_bus(bus, &handle) != 0) return 0;
+  FieldValue v[2] = {};
+  v[0].field_id = 90;  // NVML_FI_DEV_NVLINK_SPEED_MBPS_COMMON: MB/s per link and direction
+  v[1].field_id = 91;  // NVML_FI_DEV_NVLINK_LINK_COUNT
+  if (fields(handle, 2, v) != 0 || v[0].nvml_return != 0 || v[1].nvml_return != 0) return 0;
+  const uint64_t mbps = v[0].value.ui, links = v[1].value.ui;
+  return mbps * links * 8ull * 1000ull * 1000ull;
+}
 
 const std::vector<TopologyGroup>& detect_topology() {
   static std::vector<TopologyGroup> cached;

@@ -8,6 +8,7 @@
 #include <string>
 #include <vector>
 
+#include "pci_topo.h"
 #include "provider.h"
 
 namespace pplx::fabric {
@@ -17,7 +18,15 @@ struct TopologyGroup {
   int numa = 0;
   std::vector<DomainInfo> domains;
   std::vector<int> cpus;         // physical cores near the device, in preference order
+  std::string pci_address;       // of the GPU, lower case as in sysfs; empty when unknown
+  std::string pci_switch;        // PCIe switch (branching ancestor) the GPU hangs off
+  std::vector<DomainInfo> nics;  // RDMA NICs under the same switch, this GPU's share; they are
+                                 // listed for placement only: no provider drives them here
 };
+
+// NVLink bandwidth of a GPU in bits per second and direction: active links x per-link speed as
+// NVML reports them, or 0 when NVML cannot be asked.
+uint64_t nvlink_bits_per_second(int cuda_device);
 
 // Cached after the first call. Never throws: missing sysfs entries degrade to "NUMA 0,
 // all CPUs of the process".

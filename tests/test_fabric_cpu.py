@@ -389,3 +389,65 @@ def test_writes_and_messages_between_processes() -> None:
         proc.join(20)
         if proc.is_alive():
             proc.terminate()
+
+
+def _fake_pci(root, path, vendor, device, pci_class, numa, rdma=None):
+    """One PCI function in a fake sysfs: `path` is the chain of addresses below the root complex."""
+    import os
+
+    real = os.path.join(root, "devices", "pci0000:00", *path)
+    os.makedirs(real, exist_ok=True)
+    for name, value in (("vendor", f"0x{vendor:04x}"), ("device", f"0x{device:04x}"),
+                        ("class", f"0x{pci_class:06x}"), ("numa_node", str(numa))):
+        with open(os.path.join(real, name), "w") as f:
+            f.write(value + "\n")
+    if rdma:
+        os.makedirs(os.path.join(real, "infiniband", rdma))
+    link_dir = os.path.join(root, "bus", "pci", "devices")
+    os.makedirs(link_dir, exist_ok=True)
+    link = os.path.join(link_dir, path[-1])
+    if not os.path.lexists(link):
+        os.symlink(real, link)
+
+
+def test_pci_placement_groups_gpus_and_nics_by_switch(tmp_path) -> None:
+    """Two PCIe switches, each with two GPUs and two NICs behind single-child bridges, plus a NIC
+    of another make next to the root: every GPU gets the NIC share of its own switch
+    (reference fabric-lib/src/topo.rs:285-458)."""
+    from pplx_garden import _native
+
+    root = str(tmp_path)
+    bridge, gpu, nic = 0x060400, 0x030200, 0x020700
+    for sw, bus in ((0, 0x10), (1, 0x40)):
+        up = f"0000:{bus:02x}:00.0"                       # root port
+        switch = f"0000:{bus + 1:02x}:00.0"               # switch upstream port
+        _fake_pci(root, [up], 0x8086, 0x1, bridge, sw)
+        _fake_pci(root, [up, switch], 0x1000, 0x2, bridge, sw)
+        for i in range(4):                                # four downstream ports
+            down = f"0000:{bus + 2:02x}:{i:02x}.0"
+            _fake_pci(root, [up, switch, down], 0x1000, 0x3, bridge, sw)
+            leaf = f"0000:{bus + 3 + i:02x}:00.0"
+            if i < 2:
+                _fake_pci(root, [up, switch, down, leaf], 0x10de, 0x2901, gpu, sw)
+            else:
+                _fake_pci(root, [up, switch, down, leaf], 0x15b3, 0x1021, nic, sw, rdma=f"mlx5_{2 * sw + i - 2}")
+    _fake_pci(root, ["0000:00:1f.0"], 0x8086, 0x9, bridge, 0)
+    _fake_pci(root, ["0000:00:1f.0", "0000:05:00.0"], 0x14e4, 0x1750, 0x020000, 0, rdma="bnxt_re0")
+
+    gpus = ["0000:13:00.0", "0000:14:00.0", "0000:43:00.0", "0000:44:00.0"]
+    placed = _native._place_gpus_from_sysfs(root, gpus + ["0000:99:00.0"])
+    assert [p[0] for p in placed] == gpus + ["0000:99:00.0"]
+    assert placed[0][1] == placed[1][1] == "0000:11:00.0"      # the switch, not the single-child port above it
+    assert placed[2][1] == placed[3][1] == "0000:41:00.0"
+    assert [p[2] for p in placed[:4]] == [0, 0, 1, 1]
+    assert [[n[1] for n in p[3]] for p in placed[:4]] == [["mlx5_0"], ["mlx5_1"], ["mlx5_2"], ["mlx5_3"]]
+    assert placed[4][1] == "" and placed[4][3] == []             # unknown GPU: no switch, no NICs
+
+
+def test_topology_reports_pci_fields() -> None:
+    from pplx_garden.fabric_lib import TransferEngine
+
+    for group in TransferEngine.detect_topology():
+        assert isinstance(group.pci_address, str) and isinstance(group.pci_switch, str)
+        assert isinstance(group.nics, list)
+        assert group.domains and group.domains[0].link_speed > 0
