@@ -40,6 +40,19 @@ PYBIND11_MODULE(_native, m) {
 
   m.def("cuda_driver_available", [] { return pplx::CuDriver::available(); },
         "True when libcuda.so.1 can be loaded in this process.");
+  m.def(
+      "_profiler_guard_probe",
+      [](const std::string& name) {
+        bool enabled = false;
+        try {
+          enabled = py::module_::import("torch.autograd.profiler").attr("_is_profiler_enabled").cast<bool>();
+        } catch (const py::error_already_set&) {
+          enabled = false;
+        }
+        pplx_py::TorchProfilerGuard guard(name.c_str());
+        return enabled;
+      },
+      py::arg("name"), "Opens and closes one native profiler range; returns whether a profiler was running.");
   m.def("pin_cpu", &pplx::pin_cpu, py::arg("cpu"), "Pin the calling thread to one logical CPU.");
   m.def("current_affinity", &pplx::current_affinity);
   m.def("log_set_level", [](const std::string& level) {

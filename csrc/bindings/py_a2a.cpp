@@ -263,6 +263,7 @@ void bind_a2a(py::module_& m) {
               uint64_t indices_ptr, uint64_t indices_stride, uint64_t weights_ptr,
               uint64_t weights_stride, const py::object& bound_m_ptr, uint64_t stream,
               bool quantize) {
+             pplx_py::TorchProfilerGuard profiler_range("a2a_dispatch_send");
              const DispatchSendArgs a =
                  send_args(num_tokens, x_ptr, x_stride, x_scale_ptr, sse, sst, indices_ptr,
                            indices_stride, weights_ptr, weights_stride, bound_m_ptr, quantize);
@@ -277,6 +278,7 @@ void bind_a2a(py::module_& m) {
            [](PyA2A& s, uint64_t out_num_tokens_ptr, uint64_t out_x_ptr, uint64_t out_x_stride,
               const py::object& out_x_scale_ptr, const py::object& sse, const py::object& sst,
               uint64_t stream, uint32_t out_rows) {
+             pplx_py::TorchProfilerGuard profiler_range("a2a_dispatch_recv");
              const DispatchRecvArgs a = recv_args(out_num_tokens_ptr, out_x_ptr, out_x_stride,
                                                   out_x_scale_ptr, sse, sst, out_rows);
              s.ctx->dispatch(nullptr, &a, false, true, as_stream(stream));
@@ -293,6 +295,7 @@ void bind_a2a(py::module_& m) {
               uint64_t out_x_ptr, uint64_t out_x_stride, const py::object& out_x_scale_ptr,
               const py::object& osse, const py::object& osst, uint64_t stream, uint32_t out_rows,
               bool quantize) {
+             pplx_py::TorchProfilerGuard profiler_range("a2a_dispatch");
              const DispatchSendArgs a =
                  send_args(num_tokens, x_ptr, x_stride, x_scale_ptr, sse, sst, indices_ptr,
                            indices_stride, weights_ptr, weights_stride, bound_m_ptr, quantize);
@@ -311,6 +314,7 @@ void bind_a2a(py::module_& m) {
       .def("combine_send",
            [](PyA2A& s, uint64_t expert_x_ptr, uint64_t expert_x_stride, uint64_t stream,
               const py::object& expert_y_dtype) {
+             pplx_py::TorchProfilerGuard profiler_range("a2a_combine_send");
              const CombineSendArgs a = csend_args(expert_x_ptr, expert_x_stride);
              const int y = expert_y_dtype.is_none() ? s.out_dtype : dtype_code(expert_y_dtype);
              s.ctx->combine(&a, nullptr, true, false, y, s.out_dtype, as_stream(stream));
@@ -342,6 +346,7 @@ void bind_a2a(py::module_& m) {
               uint64_t out_tokens_stride, uint64_t indices_ptr, uint64_t indices_stride,
               uint64_t weights_ptr, uint64_t weights_stride, const py::object& bound_m_ptr,
               bool accumulate, uint64_t stream) {
+             pplx_py::TorchProfilerGuard profiler_range("a2a_combine_recv");
              const CombineRecvArgs a =
                  crecv_args(num_tokens, out_tokens_ptr, out_tokens_stride, indices_ptr,
                             indices_stride, weights_ptr, weights_stride, bound_m_ptr, accumulate);
@@ -359,6 +364,7 @@ void bind_a2a(py::module_& m) {
               uint64_t out_tokens_stride, uint64_t indices_ptr, uint64_t indices_stride,
               uint64_t weights_ptr, uint64_t weights_stride, const py::object& bound_m_ptr,
               bool accumulate, uint64_t stream) {
+             pplx_py::TorchProfilerGuard profiler_range("a2a_combine");
              const CombineSendArgs a = csend_args(expert_x_ptr, expert_x_stride);
              const CombineRecvArgs r =
                  crecv_args(num_tokens, out_tokens_ptr, out_tokens_stride, indices_ptr,
@@ -375,6 +381,7 @@ void bind_a2a(py::module_& m) {
       // ---- several ranks in one launch (one tuple per local rank, same order as above) ----
       .def("dispatch_multi",
            [](PyA2A& s, const py::object& send, const py::object& recv, uint64_t stream) {
+             pplx_py::TorchProfilerGuard profiler_range("a2a_dispatch");
              std::vector<DispatchSendArgs> sa;
              std::vector<DispatchRecvArgs> ra;
              if (!send.is_none()) {
@@ -409,6 +416,7 @@ void bind_a2a(py::module_& m) {
       .def("combine_multi",
            [](PyA2A& s, const py::object& send, const py::object& recv,
               const py::object& expert_y_dtype, uint64_t stream) {
+             pplx_py::TorchProfilerGuard profiler_range("a2a_combine");
              std::vector<CombineSendArgs> sa;
              std::vector<CombineRecvArgs> ra;
              if (!send.is_none()) {

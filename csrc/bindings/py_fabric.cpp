@@ -11,6 +11,7 @@
 #include <pybind11/stl.h>
 
 #include "../core/error.h"
+#include "../fabric/faulty_domain.h"
 #include "../fabric/local_domain.h"
 #include "../fabric/shard.h"
 #include "../fabric/transfer_engine.h"
@@ -360,11 +361,26 @@ void bind_fabric(py::module_& m) {
            py::arg("dst_offset"), py::arg("counter"))
       .def("_inject_write_failure",
            [](PyEngine& e, int device, uint64_t nth) {
-             auto* d = dynamic_cast<LocalDomain*>(e.get().debug_domain(device));
-             PPLX_REQUIRE(d != nullptr, "fault injection needs the intra-box provider");
-             d->inject_write_failure(nth);
+             auto* d = dynamic_cast<FaultyDomain*>(e.get().debug_domain(device));
+             PPLX_REQUIRE(d != nullptr, "this engine's domains are not behind the fault-injection decorator");
+             d->inject(FaultKind::kFailWrite, nth);
            },
-           py::arg("device"), py::arg("nth"), "Test hook: fail the n-th write submitted from now on.");
+           py::arg("device"), py::arg("nth"), "Test hook: fail the n-th write submitted from now on.")
+      .def("_inject_fault",
+           [](PyEngine& e, int device, const std::string& kind, uint64_t value, size_t domain) {
+             auto* d = dynamic_cast<FaultyDomain*>(e.get().debug_domain(device, domain));
+             PPLX_REQUIRE(d != nullptr, "this engine's domains are not behind the fault-injection decorator");
+             FaultKind k = FaultKind::kNone;
+             if (kind == "fail") k = FaultKind::kFailWrite;
+             else if (kind == "drop") k = FaultKind::kDropWrite;
+             else if (kind == "delay") k = FaultKind::kDelayWrites;
+             else if (kind == "reorder") k = FaultKind::kReorderWrites;
+             else PPLX_REQUIRE(kind == "none", "fault kind must be fail, drop, delay, reorder or none");
+             d->inject(k, value);
+           },
+           py::arg("device"), py::arg("kind"), py::arg("value") = 0, py::arg("domain") = 0,
+           "Test hook on one domain of one device: 'fail' / 'drop' the value-th write from now, 'delay' write "
+           "completions by value ms, 'reorder' them in batches of value (newest first), 'none' clears.");
 
   m.def("_shard_single_transfer", &shard_single_transfer, py::arg("total"), py::arg("num_shards"));
   m.def("_shard_pages", &shard_pages, py::arg("num_pages"), py::arg("num_shards"));

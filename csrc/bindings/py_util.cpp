@@ -127,4 +127,51 @@ py::object device_bytes_tensor(uint64_t ptr, uint64_t nbytes, int device, py::ob
   return torch.attr("from_dlpack")(capsule);
 }
 
+namespace {
+struct ProfilerHooks {
+  py::object module;  // torch.autograd.profiler
+  py::object enter;   // torch.ops.profiler._record_function_enter_new
+  py::object exit;    // torch.ops.profiler._record_function_exit._RecordFunction
+  bool ok = false;
+};
+
+ProfilerHooks& profiler_hooks() {
+  // leaked on purpose: destroying Python objects after the interpreter is gone would crash
+  static ProfilerHooks* hooks = [] {
+    auto* h = new ProfilerHooks();
+    try {
+      h->module = py::module_::import("torch.autograd.profiler");
+      py::object ops = py::module_::import("torch").attr("ops").attr("profiler");
+      h->enter = ops.attr("_record_function_enter_new");
+      h->exit = ops.attr("_record_function_exit").attr("_RecordFunction");
+      h->ok = true;
+    } catch (const py::error_already_set&) {
+      h->ok = false;   // torch is not importable: ranges are simply not recorded
+    }
+    return h;
+  }();
+  return *hooks;
+}
+}  // namespace
+
+TorchProfilerGuard::TorchProfilerGuard(const char* name) {
+  ProfilerHooks& h = profiler_hooks();
+  if (!h.ok) return;
+  try {
+    if (!h.module.attr("_is_profiler_enabled").cast<bool>()) return;
+    handle_ = h.enter(py::str(name), py::none());
+  } catch (const py::error_already_set&) {
+    handle_ = py::object();
+  }
+}
+
+TorchProfilerGuard::~TorchProfilerGuard() {
+  if (!handle_) return;
+  try {
+    profiler_hooks().exit(handle_);
+  } catch (const py::error_already_set&) {
+    // a profiler that stopped in between: nothing to close
+  }
+}
+
 }  // namespace pplx_py

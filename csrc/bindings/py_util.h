@@ -29,4 +29,20 @@ py::object device_bytes_capsule(uint64_t ptr, uint64_t nbytes, int device, py::o
 // torch tensor (uint8, 1-D) viewing [ptr, ptr+nbytes) on cuda:`device`.
 py::object device_bytes_tensor(uint64_t ptr, uint64_t nbytes, int device, py::object owner);
 
+// Scope that shows up in a torch profiler trace as a named range, opened from native code. The
+// reference does the same with at::RecordFunction (rust/torch-lib/src/torch_lib.cc:121-130); this
+// extension does not link libtorch, so it goes through torch's own operator pair
+// profiler::_record_function_enter_new / _record_function_exit, and only while a profiler is
+// running (one attribute read otherwise). Needs the GIL, which binding entry points hold.
+class TorchProfilerGuard {
+ public:
+  explicit TorchProfilerGuard(const char* name);
+  ~TorchProfilerGuard();
+  TorchProfilerGuard(const TorchProfilerGuard&) = delete;
+  TorchProfilerGuard& operator=(const TorchProfilerGuard&) = delete;
+
+ private:
+  py::object handle_;
+};
+
 }  // namespace pplx_py

@@ -12,6 +12,7 @@
 #define PPLX_LOG_TARGET "pplx_garden::fabric"
 #include "../core/log.h"
 #include "../core/thread_util.h"
+#include "faulty_domain.h"
 #include "local_domain.h"
 
 namespace pplx::fabric {
@@ -51,7 +52,8 @@ TransferEngine::TransferEngine(std::vector<GpuDomainSpec> gpus, DomainFactory fa
     w->pin_cpu = spec.pin_worker_cpu;
     std::vector<std::unique_ptr<Domain>> domains;
     for (size_t i = 0; i < spec.domains.size(); ++i) {
-      domains.push_back(factory(spec.cuda_device, static_cast<int>(i), spec.domains[i]));
+      // every provider sits behind the fault-injection decorator (inert until armed)
+      domains.push_back(std::make_unique<FaultyDomain>(factory(spec.cuda_device, static_cast<int>(i), spec.domains[i])));
     }
     w->group = std::make_unique<DomainGroup>(std::move(domains));
     num_domains_ += spec.domains.size();

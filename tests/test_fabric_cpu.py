@@ -451,3 +451,60 @@ def test_topology_reports_pci_fields() -> None:
         assert isinstance(group.pci_address, str) and isinstance(group.pci_switch, str)
         assert isinstance(group.nics, list)
         assert group.domains and group.domains[0].link_speed > 0
+
+
+def test_fault_decorator_drop_delay_reorder(pair) -> None:
+    """Host-side fault injection on the provider seam: a dropped write never completes, a delayed
+    one completes late with its bytes in place, reordered completions arrive newest first, and the
+    engine is back to normal once the faults are cleared."""
+    import time
+
+    a, b = pair
+    src = torch.arange(4096, dtype=torch.int32).view(torch.uint8).clone()
+    dst = torch.zeros_like(src)
+    hs, _ = a.register_tensor(src)
+    _, dd = b.register_tensor(dst)
+
+    # drop: neither callback fires; a later write is unaffected
+    a._inject_fault(-1, "drop", 1)
+    lost = Waiter()
+    a.submit_write(hs, 0, 64, None, dd, 0, lost.done, lost.error, 1)
+    ok = Waiter()
+    a.submit_write(hs, 64, 64, None, dd, 64, ok.done, ok.error, 1)
+    ok.wait()
+    assert not lost.event.wait(0.3) and not lost.errors
+    assert dst[:64].sum() == 0 and torch.equal(dst[64:128], src[64:128])
+
+    # delay: completion is held back, data is already there
+    a._inject_fault(-1, "delay", 300)
+    late = Waiter()
+    t0 = time.monotonic()
+    a.submit_write(hs, 128, 64, None, dd, 128, late.done, late.error, 1)
+    late.wait()
+    assert time.monotonic() - t0 >= 0.25
+    assert torch.equal(dst[128:192], src[128:192])
+    a._inject_fault(-1, "none")
+
+    # reorder: writes alternate between the engine's two domains; on each, a batch of two
+    # completes newest first
+    for domain in range(a.nets_per_gpu):
+        a._inject_fault(-1, "reorder", 2, domain)
+    order: list[int] = []
+    waiters = []
+    for i in range(2 * a.nets_per_gpu):
+        w = Waiter()
+        waiters.append(w)
+        a.submit_write(hs, 256 + 64 * i, 64, None, dd, 256 + 64 * i,
+                       (lambda i=i, w=w: (order.append(i), w.done())), w.error, 1)
+    for w in waiters:
+        w.wait()
+    n = a.nets_per_gpu
+    for first in range(n):
+        assert order.index(first + n) < order.index(first), order
+    for domain in range(a.nets_per_gpu):
+        a._inject_fault(-1, "none", 0, domain)
+    a._inject_fault(-1, "none")
+    last = Waiter()
+    a.submit_write(hs, 1024, 64, None, dd, 1024, last.done, last.error, 1)
+    last.wait()
+    assert torch.equal(dst[1024:1088], src[1024:1088])

@@ -166,3 +166,17 @@ def test_native_unit_tests_pass():
     res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
     assert res.returncode == 0, res.stdout + res.stderr
     assert "0 failed" in res.stdout
+
+
+def test_native_profiler_guard_records_a_range():
+    """Native entry points open a torch profiler range around their work
+    (reference rust/torch-lib/src/torch_lib.cc:121-130)."""
+    import torch
+
+    from pplx_garden import _native
+
+    assert _native._profiler_guard_probe("pplx_probe_outside") is False     # no profiler running
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU]) as prof:
+        assert _native._profiler_guard_probe("pplx_probe_inside") is True
+    names = {e.key for e in prof.key_averages()}
+    assert "pplx_probe_inside" in names and "pplx_probe_outside" not in names
