@@ -121,6 +121,8 @@ void bind_cumem(py::module_& m) {
       .def("bind_mem", [](CUMulticastHandle& self, const CUMemAllocHandle& alloc) {
         self.bind_mem(alloc);
       })
+      .def("unbind", [](CUMulticastHandle& self) { self.unbind(); },
+           "Take this process's memory out of the multicast object (before freeing it or exiting).")
       .def_static("supported", [](const py::object& device) {
         return CUMulticastHandle::supported(pplx_py::device_index(device, 0));
       });

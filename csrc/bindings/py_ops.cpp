@@ -5,6 +5,7 @@
 
 #include "../core/error.h"
 #include "../ops/grouped_gemm.h"
+#include "../ops/multimem.h"
 #include "../ops/router.h"
 
 namespace py = pybind11;
@@ -12,6 +13,13 @@ using namespace pplx;
 using namespace pplx::ops;
 
 void bind_ops(py::module_& m) {
+  m.def(
+      "multimem_red_add_u32",
+      [](uint64_t mc_ptr, uint32_t value, uint64_t stream) {
+        multimem_red_add_u32(reinterpret_cast<uint32_t*>(mc_ptr), value, reinterpret_cast<cudaStream_t>(stream));
+      },
+      py::arg("mc_ptr"), py::arg("value"), py::arg("stream"),
+      "Adds value to the 32-bit word at a multicast-mapped address on every bound GPU (one multimem.red).");
   m.def(
       "topk_route",
       [](uint64_t logits, int64_t logits_stride, bool logits_bf16, uint64_t bias, uint64_t indices,

@@ -581,7 +581,23 @@ CUMulticastHandle::CUMulticastHandle(const CUMemExportData& data, int device)
   handle_ = import_generic(data);
 }
 
+void CUMulticastHandle::unbind() {
+  if (bound_bytes_ == 0) return;
+  const CuDriver& cu = CuDriver::get();
+  CUdevice dev;
+  PPLX_CU_CHECK(cu.cuDeviceGet(&dev, bound_device_));
+  PPLX_CU_CHECK(cu.cuMulticastUnbind(handle_, dev, 0, bound_bytes_));
+  bound_bytes_ = 0;
+}
+
 CUMulticastHandle::~CUMulticastHandle() {
+  if (bound_bytes_ != 0) {
+    try {
+      unbind();
+    } catch (const std::exception&) {
+      // nothing more can be done in a destructor
+    }
+  }
   if (exported_fd_ >= 0) {
     fd_server_unregister(exported_fd_);
     close(exported_fd_);
@@ -599,7 +615,10 @@ void CUMulticastHandle::add_device(int device) {
 void CUMulticastHandle::bind_mem(const CUAllocHandleBase& alloc) {
   const CuDriver& cu = CuDriver::get();
   PPLX_REQUIRE(alloc.size() <= size_, "bind_mem: the allocation is larger than the multicast object");
+  PPLX_REQUIRE(bound_bytes_ == 0, "bind_mem: this process has already bound memory to the object");
   PPLX_CU_CHECK(cu.cuMulticastBindMem(handle_, 0, alloc.raw(), 0, alloc.size(), 0));
+  bound_bytes_ = alloc.size();
+  bound_device_ = alloc.device() >= 0 ? alloc.device() : device_;
 }
 
 CUMemExportData CUMulticastHandle::export_handle() {

@@ -111,6 +111,9 @@ class CUMulticastHandle : public CUAllocHandleBase {
   ~CUMulticastHandle() override;
   void add_device(int device);
   void bind_mem(const CUAllocHandleBase& alloc);
+  // Takes this process's device memory out of the multicast object again. Every process unbinds
+  // before it frees the bound allocation or exits; the destructor does it if the caller forgot.
+  void unbind();
   CUMemExportData export_handle();
   int num_devices() const { return num_devices_; }
   // True when the driver and device expose multicast objects.
@@ -120,6 +123,8 @@ class CUMulticastHandle : public CUAllocHandleBase {
   CUMemHandleKind kind_;
   int num_devices_;
   int exported_fd_ = -1;
+  size_t bound_bytes_ = 0;   // bytes of this process's memory bound at offset 0
+  int bound_device_ = -1;
 };
 
 // Rounds `size` up to the minimum allocation granularity of `device`.
