@@ -70,6 +70,10 @@ A2AConfig a2a_make_config(const A2AParams& p, int num_sms, int virtual_ranks) {
   }
   PPLX_REQUIRE(wire == kWirePlain || wire == kWireLL, "wire must be 'plain' or 'll'");
   c.wire = wire;
+  const uint32_t all_ranks = p.world >= 32 ? 0xffffffffu : ((1u << p.world) - 1u);
+  c.node_mask = p.node_mask == 0 ? all_ranks : (p.node_mask & all_ranks);
+  PPLX_REQUIRE(c.node_mask == all_ranks || wire == kWirePlain,
+               "ranks outside the NVLink domain need the plain wire format (wire='plain')");
 
   c.d_header_bytes = round_up_u32(4u * (2 + 2 * p.topk), 16);
   c.d_payload_bytes = static_cast<uint32_t>(p.hidden_dim) * p.in_elemsize;
@@ -162,6 +166,7 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
                  "virtual ranks x blocks must fit the GPU at one block per SM");
   }
 
+  PPLX_CUDA_CHECK(a2a_preload_kernels(cfg_));
   const char* trace_env = std::getenv("PPLX_A2A_TRACE");
   cfg_.trace = (trace_env != nullptr && std::atoi(trace_env) != 0) ? 1 : 0;
   const char* team_env = std::getenv("PPLX_A2A_TEAM");
@@ -246,7 +251,102 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
             cfg_.wire == kWireLL ? "ll" : "plain");
 }
 
+void A2AContext::enable_proxy(int i, fabric::TransferEngine* engine, std::vector<A2AProxyPeer> peers,
+                              int pin_cpu) {
+  PPLX_REQUIRE(i >= 0 && i < num_local_ranks(), "enable_proxy: no such local rank");
+  PPLX_REQUIRE(engine != nullptr, "enable_proxy: a transfer engine is required");
+  PPLX_REQUIRE(cfg_.wire == kWirePlain, "enable_proxy: the plain wire format is required");
+  if (proxies_.size() < ranks_.size()) proxies_.resize(ranks_.size());
+  PPLX_REQUIRE(!proxies_[i].proxy, "enable_proxy: this local rank already has a proxy");
+  PPLX_CUDA_CHECK(cudaSetDevice(device_));
+  A2ARankState& st = states_.r[i];
+  ProxyState& ps = proxies_[i];
+  ps.engine = engine;
+  const int my_group = st.rank / cfg_.dp_size;
+
+  auto device_alloc = [&](size_t bytes) {
+    void* p = nullptr;
+    PPLX_CUDA_CHECK(cudaMalloc(&p, bytes));
+    PPLX_CUDA_CHECK(cudaMemset(p, 0, bytes));
+    ps.device_buffers.push_back(p);
+    return reinterpret_cast<uint64_t>(p);
+  };
+  auto host_alloc = [&](size_t bytes, uint32_t** device_view) {
+    uint32_t* p = nullptr;
+    PPLX_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&p), bytes, cudaHostAllocMapped));
+    std::memset(p, 0, bytes);
+    ps.host_buffers.push_back(p);
+    if (device_view != nullptr) {
+      PPLX_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(device_view), p, 0));
+    }
+    return p;
+  };
+  auto reg = [&](uint64_t ptr, uint64_t len, int device) {
+    engine->register_memory(ptr, len, device);
+    ps.registered.push_back(ptr);
+  };
+
+  A2AProxyBuffers buf;
+  // device-local words of this rank that only exist with a proxy
+  const uint64_t extra = device_alloc(256 + 256);
+  st.local.send_done = reinterpret_cast<uint32_t*>(extra);
+  st.local.stage_cursor = reinterpret_cast<uint32_t*>(extra + 256);
+  uint32_t* proxy_dev = nullptr;
+  uint32_t* proxy_host = host_alloc(sizeof(uint32_t) * kProxyWords, &proxy_dev);
+  st.local.proxy = proxy_dev;
+  buf.proxy_words = proxy_host;
+  uint32_t* slot_dev = nullptr;
+  uint32_t* slot_host = host_alloc(sizeof(uint32_t) * std::max<size_t>(cfg_.max_recv_rows, 1), &slot_dev);
+  st.local.stage_slot = slot_dev;
+  buf.stage_slot = slot_host;
+  const size_t stage_bytes = round_up_u64(static_cast<uint64_t>(cfg_.max_recv_rows) * cfg_.c_stride, 4096);
+  buf.stage = device_alloc(stage_bytes);
+  st.local.stage = reinterpret_cast<uint8_t*>(buf.stage);
+  reg(buf.stage, stage_bytes, device_);
+  uint32_t* flag_host = host_alloc(4096, nullptr);
+  buf.flag_source = reinterpret_cast<uint64_t>(flag_host);
+  buf.flag_source_host = flag_host;
+  reg(buf.flag_source, 4096, -1);
+
+  const uint64_t slice_bytes = round_up_u64(cfg_.drecv_group_stride, 4096);
+  for (const A2AProxyPeer& p : peers) {
+    PPLX_REQUIRE(p.rank >= 0 && p.rank < cfg_.world && ((cfg_.node_mask >> p.rank) & 1u) == 0,
+                 "enable_proxy: a peer is inside the NVLink domain");
+    buf.shadow_sync[p.rank] = device_alloc(cfg_.sync_bytes);
+    reg(buf.shadow_sync[p.rank], cfg_.sync_bytes, device_);
+    buf.shadow_recv[p.rank] = device_alloc(slice_bytes);
+    reg(buf.shadow_recv[p.rank], slice_bytes, device_);
+    // The kernels address "rank p's regions" exactly as they would a mapped peer; only this
+    // rank's group slice of the dispatch records is ever touched there, so only that is backed.
+    st.sync[p.rank] = reinterpret_cast<uint8_t*>(buf.shadow_sync[p.rank]);
+    st.recv[p.rank] = reinterpret_cast<uint8_t*>(buf.shadow_recv[p.rank]) -
+                      (cfg_.off_drecv + static_cast<uint64_t>(my_group) * cfg_.drecv_group_stride);
+  }
+  for (int r = 0; r < cfg_.world; ++r) {
+    if (((cfg_.node_mask >> r) & 1u) == 0) {
+      PPLX_REQUIRE(buf.shadow_sync[r] != 0, "enable_proxy: a rank outside the NVLink domain has no peer entry");
+    }
+  }
+  PPLX_CUDA_CHECK(cudaDeviceSynchronize());
+  ps.proxy = std::make_unique<A2AProxy>(cfg_, st.rank, engine, std::move(peers), buf, pin_cpu);
+  PPLX_INFO("a2a proxy for rank %d: %zu remote rank(s), staging %.1f MiB", st.rank,
+            static_cast<size_t>(__builtin_popcount(~cfg_.node_mask & ((1u << cfg_.world) - 1u))),
+            stage_bytes / 1048576.0);
+}
+
 A2AContext::~A2AContext() {
+  for (ProxyState& ps : proxies_) {
+    ps.proxy.reset();   // joins the thread before its buffers go away
+    for (uint64_t ptr : ps.registered) {
+      try {
+        ps.engine->unregister_memory(ptr);
+      } catch (const std::exception&) {
+        // the engine may already have been stopped
+      }
+    }
+    for (void* p : ps.device_buffers) cudaFree(p);
+    for (void* p : ps.host_buffers) cudaFreeHost(p);
+  }
   for (void* p : allocations_) cudaFree(p);
   for (uint32_t* p : host_flags_) cudaFreeHost(p);
 }
@@ -254,6 +354,9 @@ A2AContext::~A2AContext() {
 bool A2AContext::failed() const {
   for (const uint32_t* p : host_flags_) {
     if (*reinterpret_cast<const volatile uint32_t*>(p) != 0) return true;
+  }
+  for (const ProxyState& p : proxies_) {
+    if (p.proxy && p.proxy->failed()) return true;
   }
   return false;
 }
@@ -270,6 +373,15 @@ void A2AContext::require_phase(int first) const {
   }
 }
 
+void A2AContext::require_proxies() const {
+  const uint32_t all_ranks = cfg_.world >= 32 ? 0xffffffffu : ((1u << cfg_.world) - 1u);
+  if (cfg_.node_mask == all_ranks) return;
+  for (size_t i = 0; i < ranks_.size(); ++i) {
+    PPLX_REQUIRE(i < proxies_.size() && proxies_[i].proxy != nullptr,
+                 "ranks outside the NVLink domain need enable_proxy() before the first dispatch");
+  }
+}
+
 void A2AContext::commit_phase(int last) { next_phase_ = (last + 1) % kNumPhases; }
 
 int A2AContext::pick(int64_t items, int64_t vectors_per_item) const {
@@ -280,6 +392,7 @@ int A2AContext::pick(int64_t items, int64_t vectors_per_item) const {
 void A2AContext::dispatch(const DispatchSendArgs* send, const DispatchRecvArgs* recv, bool do_send,
                           bool do_recv, cudaStream_t stream) {
   PPLX_REQUIRE(do_send || do_recv, "dispatch: nothing to do");
+  require_proxies();
   // Nothing is committed before the launch went through: a rejected call leaves the context
   // where it was, so a corrected call may follow.
   require_phase(do_send ? kPhaseDispatchSend : kPhaseDispatchRecv);
@@ -412,6 +525,13 @@ A2AStatusInfo A2AContext::status(int i) const {
 }
 
 void A2AContext::check() const {
+  for (size_t i = 0; i < proxies_.size(); ++i) {
+    if (proxies_[i].proxy && proxies_[i].proxy->failed()) {
+      // the reference's wording for a failed RDMA completion (p2p-all-to-all/src/a2a_context.rs:332-334)
+      throw Error(ErrorKind::kCustom, "rank " + std::to_string(ranks_[i]) + ": fabric-lib transfer error (" +
+                                          proxies_[i].proxy->error() + ")");
+    }
+  }
   for (int i = 0; i < num_local_ranks(); ++i) {
     const A2AStatusInfo s = status(i);
     if (s.code != kStatusOk) {

@@ -14,6 +14,7 @@
 #include <string>
 #include <vector>
 
+#include "a2a_proxy.h"
 #include "a2a_types.h"
 
 namespace pplx {
@@ -33,6 +34,10 @@ struct A2AParams {
   int combine_mode = kCombinePerRoute;
   int wire = kWireAuto;        // auto: flagged lines up to 512 tokens per call, plain above;
                                // PPLX_A2A_WIRE=ll|plain overrides an automatic choice
+  // Ranks whose memory is mapped into this process (bit r = rank r, own rank included); 0 means
+  // all of them. The others are reached through a transfer engine by a host proxy
+  // (A2AContext::enable_proxy), which needs the plain wire format.
+  uint32_t node_mask = 0;
   int num_blocks = 0;          // 0: one block per SM (divided among virtual ranks)
   int64_t wait_limit_ms = 0;   // 0: PPLX_A2A_TIMEOUT_MS or 10 s
 };
@@ -79,6 +84,19 @@ class A2AContext {
   void combine(const CombineSendArgs* send, const CombineRecvArgs* recv, bool do_send,
                bool do_recv, int y_dtype, int out_dtype, cudaStream_t stream);
 
+  // Serves the ranks outside the NVLink domain of local rank `i` (those missing from
+  // A2AParams::node_mask): allocates the stand-in buffers the kernels write into instead of the
+  // unreachable peers, registers them with `engine` and starts the proxy thread that forwards
+  // them. `peers` names every such rank with the descriptors of its sync and receive regions.
+  // Call once per local rank, before the first dispatch. The engine must outlive the context.
+  void enable_proxy(int i, fabric::TransferEngine* engine, std::vector<A2AProxyPeer> peers, int pin_cpu);
+
+  // (dispatches, combines) the proxy of local rank `i` has forwarded; zeros without a proxy.
+  std::array<uint32_t, 2> proxy_counters(int i = 0) const {
+    if (i < 0 || static_cast<size_t>(i) >= proxies_.size() || !proxies_[i].proxy) return {0, 0};
+    return {proxies_[i].proxy->dispatches(), proxies_[i].proxy->combines()};
+  }
+
   // All ranks of the context meet on the device: returns (in stream order) once every rank has
   // entered. Bounded like every other wait. Collective; may be called between any two phases.
   void barrier(cudaStream_t stream);
@@ -111,6 +129,7 @@ class A2AContext {
   int pick(int64_t items, int64_t vectors_per_item) const;
   void require_phase(int first) const;
   void commit_phase(int last);
+  void require_proxies() const;
 
   A2AConfig cfg_{};
   int device_;
@@ -127,6 +146,14 @@ class A2AContext {
   int64_t last_tokens_ = 0;
   int team_override_ = 0;
   bool external_send_ = false;  // the pending combine's send phase was played by another kernel
+  struct ProxyState {
+    std::unique_ptr<A2AProxy> proxy;
+    fabric::TransferEngine* engine = nullptr;
+    std::vector<uint64_t> registered;   // regions registered with the engine
+    std::vector<void*> device_buffers;  // cudaMalloc
+    std::vector<void*> host_buffers;    // cudaHostAlloc
+  };
+  std::vector<ProxyState> proxies_;
 };
 
 }  // namespace pplx

@@ -300,6 +300,64 @@ __device__ __forceinline__ uint32_t* tok_arrive_ptr(const A2AConfig& cfg, uint8_
 }
 
 
+// ---- ranks outside the NVLink domain (served by the host proxy) ----
+
+__device__ __forceinline__ bool has_remote(const A2AConfig& cfg) {
+  return cfg.node_mask != ((cfg.world >= 32) ? 0xffffffffu : ((1u << cfg.world) - 1u));
+}
+
+__device__ __forceinline__ bool in_node(const A2AConfig& cfg, uint32_t rank) {
+  return ((cfg.node_mask >> rank) & 1u) != 0;
+}
+
+// End of a send phase (which = 0 dispatch, 1 combine): the last block to get here tells the host
+// proxy, after everything this rank staged has been made visible to the host and to copy
+// engines. Called by all threads of every block.
+__device__ __forceinline__ void proxy_phase_done(const A2AConfig& cfg, const A2ALocal& ws, int which,
+                                                 uint32_t tag) {
+  if (!has_remote(cfg)) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const uint32_t old = atom_acq_rel_gpu_add(&ws.send_done[which], 1u);
+    if (old == gridDim.x - 1) {
+      ws.send_done[which] = 0;
+      volatile uint32_t* words = ws.proxy;
+      if (which == 1) {
+        for (int g = 0; g < cfg.num_groups; ++g) {
+          words[kProxyRows + g] = *reinterpret_cast<volatile uint32_t*>(&ws.stage_cursor[g]);
+        }
+      }
+      __threadfence_system();
+      words[which == 0 ? kProxyDispatchSent : kProxyCombineSent] = tag;
+    }
+  }
+}
+
+// How many of token t's combine sources live on ranks inside the NVLink domain (the others are
+// announced per rank by the proxy, not per token). First warp of a team, all 32 lanes.
+__device__ __forceinline__ uint32_t combine_local_sources(const A2AConfig& cfg, const CombineRecvArgs& a,
+                                                          int t) {
+  const int K = cfg.topk;
+  const int L = cfg.experts_per_rank;
+  const int k = threadIdx.x & 31;
+  bool counts = false;
+  if (k < K) {
+    const uint32_t e = a.indices[t * a.indices_stride + k];
+    if (e < static_cast<uint32_t>(cfg.num_experts)) {
+      const uint32_t d = e / L;
+      counts = in_node(cfg, d);
+      if (cfg.combine_mode != kCombinePerRoute) {
+        for (int q = 0; q < k; ++q) {
+          const uint32_t eq = a.indices[t * a.indices_stride + q];
+          counts &= !(eq < static_cast<uint32_t>(cfg.num_experts) && eq / L == d);
+        }
+      }
+    }
+  }
+  return __popc(__ballot_sync(0xffffffffu, counts));
+}
+
 // Source slots (and weights) of token t, compacted into shared memory by the first warp
 // of the team. *out_n is also the number of arrivals the token waits for.
 __device__ __forceinline__ void combine_sources(const A2AConfig& cfg, const CombineRecvArgs& a,

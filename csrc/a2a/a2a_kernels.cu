@@ -107,6 +107,10 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
       }
     }
     __syncthreads();
+    if (has_remote(cfg) && threadIdx.x < world) {
+      const bool served = static_cast<int>(threadIdx.x % cfg.dp_size) == my_tp;
+      reinterpret_cast<volatile uint32_t*>(ws.proxy)[kProxyRecords + threadIdx.x] = served ? nrec[threadIdx.x] : 0u;
+    }
     if constexpr (WIRE == kWireLL) {
       // Flagged lines, to every rank (zeros where this rank serves no records): no fence, and
       // the lines themselves tell the receiver that this rank has started the dispatch.
@@ -332,6 +336,7 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
     if (t == 0) trace_mark(cfg, ws, kTraceSendPublished);
   }
   }  // plain wire
+  proxy_phase_done(cfg, ws, 0, tag);
   trace_mark(cfg, ws, kTraceSendLoopDone);
   trace_max(cfg, ws, kTraceSendLoopLast);
   if (threadIdx.x == 0 && blockIdx.x == 0) atomicAdd(&ws.stats[0], static_cast<unsigned long long>(T));
@@ -500,6 +505,18 @@ __device__ void dispatch_recv_phase(const A2AConfig& cfg, const A2ARankState& st
           ws.row_src[r] = kNoSlot;
         }
       }
+      if (has_remote(cfg) && threadIdx.x == 32) {
+        // where the combine will stage the rows of each origin group that has members outside
+        // the NVLink domain: one dense segment per group, in group order
+        uint32_t first = 0;
+        for (int g = 0; g < G; ++g) {
+          uint32_t rows_g = 0;
+          for (int le = 0; le < L; ++le) rows_g += cnt[g * L + le];
+          reinterpret_cast<volatile uint32_t*>(ws.proxy)[kProxyRowBase + g] = first;
+          ws.stage_cursor[g] = 0;
+          first += rows_g;
+        }
+      }
       if (threadIdx.x == 0) {
         ws.expert_meta[0] = min(padded_rows, row_cap);
         ws.expert_meta[1] = s_rec_prefix[G];
@@ -663,14 +680,38 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
     if (team.lane < 32) {
       const uint32_t npend = s_npend[team.in_block];
       __syncwarp();
-      if (team.lane < cfg.dp_size) {
-        s_pend[team.in_block][npend + team.lane] =
+      // members of the origin group outside the NVLink domain are told by the proxy instead
+      const bool member = team.lane < cfg.dp_size && in_node(cfg, g * cfg.dp_size + team.lane);
+      const uint32_t members = __ballot_sync(0xffffffffu, member);
+      if (member) {
+        s_pend[team.in_block][npend + __popc(members & ((1u << team.lane) - 1u))] =
             tok_arrive_ptr(cfg, st.sync[g * cfg.dp_size + team.lane], t);
       }
-      if (team.lane == 0) s_npend[team.in_block] = npend + cfg.dp_size;
+      if (team.lane == 0) s_npend[team.in_block] = npend + __popc(members);
       __syncwarp();
       if (npend + 2 * cfg.dp_size > kMaxPending || npend + cfg.dp_size >= 8u * cfg.dp_size) flush();
     }
+  };
+
+  // A row whose origin group has members outside the NVLink domain is also copied into the
+  // staging buffer, densely inside the group's segment, and its combine slot is written where
+  // the proxy reads it. Called by the whole team; returns nullptr when no copy is needed.
+  __shared__ uint32_t s_stage_pos[kMaxTeams];
+  const bool remote = has_remote(cfg);
+  auto stage_row = [&](uint32_t g, uint32_t slot) -> uint8_t* {
+    if (!remote) return nullptr;
+    bool any = false;
+    for (int m = 0; m < cfg.dp_size; ++m) any |= !in_node(cfg, g * cfg.dp_size + m);
+    if (!any) return nullptr;   // uniform across the team
+    if (team.lane == 0) {
+      const uint32_t first = reinterpret_cast<volatile uint32_t*>(ws.proxy)[kProxyRowBase + g];
+      const uint32_t pos = first + atom_relaxed_gpu_add(&ws.stage_cursor[g], 1u);
+      s_stage_pos[team.in_block] = pos;
+      if (pos < cfg.max_recv_rows) reinterpret_cast<volatile uint32_t*>(ws.stage_slot)[pos] = slot;
+    }
+    team.sync();
+    const uint32_t pos = s_stage_pos[team.in_block];
+    return pos < cfg.max_recv_rows ? ws.stage + static_cast<uint64_t>(pos) * cfg.c_stride : nullptr;
   };
 
   if constexpr (WIRE == kWireLL) {
@@ -693,13 +734,14 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
       const uint32_t g = ws.row_src[row];
       const uint32_t tk = ws.row_tk[row];
       if (g == kNoSlot) continue;  // padding row; uniform across the team
-      uint8_t* dst[kMaxRanks];
+      uint8_t* dst[kMaxRanks + 1];
       #pragma unroll
       for (int m = 0; m < kMaxRanks; ++m) {
-        dst[m] = m < cfg.dp_size ? st.recv[g * cfg.dp_size + m] + cfg.off_crecv +
-                                       static_cast<uint64_t>(tk) * cfg.c_stride
-                                 : nullptr;
+        dst[m] = (m < cfg.dp_size && in_node(cfg, g * cfg.dp_size + m))
+                     ? st.recv[g * cfg.dp_size + m] + cfg.off_crecv + static_cast<uint64_t>(tk) * cfg.c_stride
+                     : nullptr;
       }
+      dst[kMaxRanks] = stage_row(g, tk);
       for (uint32_t i0 = team.lane; i0 < nvec; i0 += TEAM * U) {
         if (i0 != static_cast<uint32_t>(team.lane)) {
           #pragma unroll
@@ -713,7 +755,7 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
           const uint32_t i = i0 + u * TEAM;
           if (i < nvec) {
             #pragma unroll
-            for (int m = 0; m < kMaxRanks; ++m) {
+            for (int m = 0; m <= kMaxRanks; ++m) {
               if (dst[m] != nullptr) st_stream_v4(dst[m] + 16ull * i, v[u]);
             }
           }
@@ -746,6 +788,7 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
       // A record always yields a partial (zeros if none of its rows fitted): the origin counts
       // one arrival per rank it sent the token to.
       const uint64_t slot = static_cast<uint64_t>(t) * cfg.world + st.rank;
+      uint8_t* staged = stage_row(g, static_cast<uint32_t>(slot));
       constexpr int GB = 4;  // granules a thread carries at once: GB independent loads per row
       for (uint32_t i0 = team.lane; i0 < ngran; i0 += TEAM * GB) {
         float acc[GB][8];
@@ -776,11 +819,15 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
         for (int u = 0; u < GB; ++u) {
           const uint32_t i = i0 + u * TEAM;
           if (i < ngran) {
-            for (int m = 0; m < cfg.dp_size; ++m) {
-              Elem8<Y>::store(st.recv[g * cfg.dp_size + m] + cfg.off_crecv + slot * cfg.c_stride +
-                                  static_cast<uint64_t>(i) * Elem8<Y>::kBytes,
-                              acc[u]);
-            }
+              for (int m = 0; m < cfg.dp_size; ++m) {
+                if (!in_node(cfg, g * cfg.dp_size + m)) continue;
+                Elem8<Y>::store(st.recv[g * cfg.dp_size + m] + cfg.off_crecv + slot * cfg.c_stride +
+                                    static_cast<uint64_t>(i) * Elem8<Y>::kBytes,
+                                acc[u]);
+              }
+              if (staged != nullptr) {
+                Elem8<Y>::store(staged + static_cast<uint64_t>(i) * Elem8<Y>::kBytes, acc[u]);
+              }
           }
         }
       }
@@ -789,6 +836,7 @@ __device__ void combine_send_phase(const A2AConfig& cfg, const A2ARankState& st,
     }
     flush();
   }
+  proxy_phase_done(cfg, ws, 1, tag_c);
   trace_mark(cfg, ws, kTraceCSendLoopDone);
   trace_max(cfg, ws, kTraceCSendLoopLast);
 }
@@ -816,6 +864,20 @@ __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
 
   if (threadIdx.x == 0) s_abort = ws.status[0] != 0 ? 1u : 0u;
   __syncthreads();
+  if (has_remote(cfg)) {
+    // rows from ranks outside the NVLink domain come through the transfer engine; their proxy
+    // announces them all at once, after the last one has landed
+    if (threadIdx.x < cfg.world && !in_node(cfg, threadIdx.x)) {
+      uint64_t waited;
+      const bool ok = wait_flag(flag_ptr(st.sync[st.rank], kFlagRemoteCombine, threadIdx.x), epoch + 1,
+                                cfg.wait_limit_ns, &waited);
+      if (!ok) {
+        report(ws, kStatusWaitTimeout, kPhaseCombineRecv, threadIdx.x, epoch + 1);
+        s_abort = 1;
+      }
+    }
+    __syncthreads();
+  }
   if (a.external) {
     // the sending kernels announce a whole rank's rows at once
     const uint32_t expected = read_epoch(ws, 2) + 1;
@@ -843,8 +905,9 @@ __device__ void combine_recv_phase(const A2AConfig& cfg, const A2ARankState& st,
         combine_sources(cfg, a, t, s_slot[team.in_block], s_wbits[team.in_block],
                         &s_n[team.in_block]);
         __syncwarp();
+        const uint32_t n_local = has_remote(cfg) ? combine_local_sources(cfg, a, t) : s_n[team.in_block];
         if (team.lane == 0 && !a.external) {
-          const uint32_t n = s_n[team.in_block];
+          const uint32_t n = n_local;
           uint32_t* counter = tok_arrive_ptr(cfg, st.sync[st.rank], static_cast<uint32_t>(t));
           if (n != 0) {
             if (wait_word(counter, n, false, cfg.wait_limit_ns, ws.status)) {
@@ -933,7 +996,7 @@ barrier_kernel(const __grid_constant__ A2AConfig cfg, const __grid_constant__ A2
   const A2ALocal& ws = st.local;
   const uint32_t expected = read_epoch(ws, 3) + 1;
   __syncwarp();
-  if (threadIdx.x < cfg.world) {
+  if (threadIdx.x < cfg.world && in_node(cfg, threadIdx.x)) {   // the NVLink domain only
     red_release_sys_add(flag_ptr(st.sync[threadIdx.x], kFlagBarrier, st.rank), 1u);
     uint64_t waited;
     if (!wait_flag(flag_ptr(st.sync[st.rank], kFlagBarrier, threadIdx.x), expected,
@@ -1023,6 +1086,38 @@ cudaError_t a2a_launch_dispatch(const A2AConfig& cfg, const A2ARankStates& state
   }
   return launch(dispatch_kernel<kWirePlain>, grid, smem, stream, cooperative, cfg, states, send, recv,
                 send_team, recv_team);
+}
+
+namespace {
+template <int WIRE>
+cudaError_t preload_wire() {
+  cudaFuncAttributes attr;
+  cudaError_t e = cudaFuncGetAttributes(&attr, dispatch_kernel<WIRE>);
+  if (e != cudaSuccess) return e;
+  const int dtypes[] = {kDtypeBF16, kDtypeF16, kDtypeF32};
+  for (int y : dtypes) {
+    e = with_dtype(y, [&](auto* yp) {
+      using Y = std::remove_pointer_t<decltype(yp)>;
+      cudaError_t r = cudaFuncGetAttributes(&attr, combine_send_kernel<WIRE, Y>);
+      for (int o : dtypes) {
+        if (r != cudaSuccess) break;
+        r = with_dtype(o, [&](auto* op) {
+          using O = std::remove_pointer_t<decltype(op)>;
+          cudaError_t q = cudaFuncGetAttributes(&attr, combine_kernel<WIRE, Y, O>);
+          if (q == cudaSuccess) q = cudaFuncGetAttributes(&attr, combine_recv_kernel<WIRE, Y, O>);
+          return q;
+        });
+      }
+      return r;
+    });
+    if (e != cudaSuccess) return e;
+  }
+  return cudaFuncGetAttributes(&attr, barrier_kernel);
+}
+}  // namespace
+
+cudaError_t a2a_preload_kernels(const A2AConfig& cfg) {
+  return cfg.wire == kWireLL ? preload_wire<kWireLL>() : preload_wire<kWirePlain>();
 }
 
 cudaError_t a2a_launch_barrier(const A2AConfig& cfg, const A2ARankStates& states, int nranks,

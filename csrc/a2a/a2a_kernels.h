@@ -20,6 +20,12 @@ cudaError_t a2a_launch_dispatch(const A2AConfig& cfg, const A2ARankStates& state
                                 const PerRank<DispatchRecvArgs>& recv, int send_team, int recv_team,
                                 cudaStream_t stream);
 
+// Loads every kernel a context with this configuration can launch, on the current device. With
+// lazy module loading the first launch of a kernel may have to wait for the kernels that are
+// running; a dispatch that is running may in turn be waiting for a peer whose next kernel is
+// that first launch. Loading at set-up time takes the first launches out of the steady state.
+cudaError_t a2a_preload_kernels(const A2AConfig& cfg);
+
 // All ranks of the context meet on the device (bounded wait, reported through the status word).
 cudaError_t a2a_launch_barrier(const A2AConfig& cfg, const A2ARankStates& states, int nranks,
                                cudaStream_t stream);

@@ -78,7 +78,20 @@ enum A2AFlagRow : int {
   kFlagDispatchStarted = 0,  // tag of the newest dispatch whose counts message rank s sent here
   kFlagExternalCombine = 1,  // combines whose send phase another kernel of rank s played
   kFlagBarrier = 2,          // barriers rank s has entered
-  kNumFlagRows = 3,
+  kFlagRemoteCombine = 3,    // tag of the newest combine whose rows rank s (a rank outside this
+                             // NVLink domain) has delivered here through the transfer engine
+  kNumFlagRows = 4,
+};
+
+// Words of the pinned host block through which the kernels talk to the host proxy that serves
+// ranks outside the NVLink domain (A2ALocal::proxy).
+enum A2AProxyWord : int {
+  kProxyDispatchSent = 0,   // tag of the newest dispatch whose send phase has finished on this rank
+  kProxyCombineSent = 1,    // same for the combine
+  kProxyRecords = 8,        // [kMaxRanks] records staged for each destination rank by that dispatch
+  kProxyRows = 16,          // [kMaxRanks] rows staged for each origin dp group by that combine
+  kProxyRowBase = 24,       // [kMaxRanks] first staged row of each origin dp group
+  kProxyWords = 32,
 };
 
 // Values of status[0]. status[1] = phase, status[2] = peer/group, status[3] = detail.
@@ -120,6 +133,8 @@ struct A2AConfig {
   int num_blocks;        // grid.x of every a2a kernel (arrival counters depend on it)
   int trace;             // 1: kernels record a coarse timeline into A2ALocal::trace
   int wire;              // A2AWire, never kWireAuto here
+  uint32_t node_mask;    // bit r: rank r is in this rank's NVLink domain (its memory is mapped
+                         // here); the other ranks are served by the host proxy
 
   // wire format
   uint32_t d_header_bytes;
@@ -163,6 +178,12 @@ struct A2ALocal {
   uint32_t* status;        // [4]
   uint32_t* host_flag;     // pinned host word (device-mapped): failure code, readable by the
                            // host without synchronising the stream
+  // ---- only used when some rank is outside the NVLink domain ----
+  uint32_t* proxy;         // pinned host words (device-mapped), see A2AProxyWord
+  uint32_t* send_done;     // [2] blocks that finished the current dispatch / combine send phase
+  uint8_t* stage;          // [max_recv_rows] combine rows bound for ranks outside the domain
+  uint32_t* stage_slot;    // pinned host (device-mapped): [max_recv_rows] combine slot of each staged row
+  uint32_t* stage_cursor;  // [kMaxRanks] rows staged so far for each origin dp group
   unsigned long long* stats;  // [8] counters: tokens sent, -, max dispatch/combine wait ns
   unsigned long long* trace;  // [kTraceSlots] see A2ATrace
 };

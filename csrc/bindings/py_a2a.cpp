@@ -8,6 +8,7 @@
 
 #include "../a2a/a2a_context.h"
 #include "../core/error.h"
+#include "py_fabric.h"
 #include "py_util.h"
 
 namespace py = pybind11;
@@ -41,7 +42,7 @@ A2AParams make_params(int hidden_dim, const py::object& hidden_dim_scale, int in
                       int out_elemsize, const py::object& scale_elemsize, int max_num_tokens,
                       int num_experts, int expert_padding, int num_experts_per_token, int dp_size,
                       int world_size, const py::object& combine_mode, int num_blocks,
-                      int64_t wait_limit_ms, const py::object& wire = py::none()) {
+                      int64_t wait_limit_ms, const py::object& wire = py::none(), uint32_t node_mask = 0) {
   A2AParams p;
   p.world = world_size;
   p.dp_size = dp_size;
@@ -58,6 +59,7 @@ A2AParams make_params(int hidden_dim, const py::object& hidden_dim_scale, int in
   p.num_blocks = num_blocks;
   p.wait_limit_ms = wait_limit_ms;
   p.wire = wire_from(wire);
+  p.node_mask = node_mask;
   return p;
 }
 
@@ -73,6 +75,7 @@ py::dict config_dict(const A2AConfig& c) {
   d["num_blocks"] = c.num_blocks;
   d["combine_mode"] = c.combine_mode;
   d["wire"] = c.wire == kWireLL ? "ll" : "plain";
+  d["node_mask"] = c.node_mask;
   d["dispatch_header_bytes"] = c.d_header_bytes;
   d["dispatch_payload_bytes"] = c.d_payload_bytes;
   d["dispatch_scale_bytes"] = c.d_scale_bytes;
@@ -185,7 +188,65 @@ std::vector<std::vector<uint64_t>> ptr_tables(const py::object& ptrs, size_t nlo
 
 }  // namespace
 
+// The host proxy on its own, over buffers the caller owns and has registered with the engine
+// (host memory in CPU tests, where Python plays the kernels' part).
+struct PyProxyProbe {
+  std::unique_ptr<A2AProxy> proxy;
+};
+
 void bind_a2a(py::module_& m) {
+  py::class_<PyProxyProbe>(m, "_A2AProxyProbe")
+      .def(py::init([](const py::dict& layout_args, int rank, PyEngine& engine, const py::list& peers,
+                       const py::dict& shadow_sync, const py::dict& shadow_recv, uint64_t stage,
+                       uint64_t flag_source, uint64_t proxy_words, uint64_t stage_slot) {
+             auto get = [&](const char* key, py::object fallback) -> py::object {
+               return layout_args.contains(key) ? py::reinterpret_borrow<py::object>(layout_args[key]) : fallback;
+             };
+             const A2AParams p = make_params(
+                 get("hidden_dim", py::int_(0)).cast<int>(), get("hidden_dim_scale", py::none()),
+                 get("in_elemsize", py::int_(2)).cast<int>(), get("out_elemsize", py::int_(2)).cast<int>(),
+                 get("scale_elemsize", py::none()), get("max_num_tokens", py::int_(0)).cast<int>(),
+                 get("num_experts", py::int_(0)).cast<int>(), get("expert_padding", py::int_(1)).cast<int>(),
+                 get("num_experts_per_token", py::int_(0)).cast<int>(), get("dp_size", py::int_(1)).cast<int>(),
+                 get("world_size", py::int_(1)).cast<int>(), get("combine_mode", py::none()), 0,
+                 get("wait_limit_ms", py::int_(0)).cast<int64_t>(), py::str("plain"),
+                 get("node_mask", py::int_(0)).cast<uint32_t>());
+             const A2AConfig cfg = a2a_make_config(p, 148, 1);
+             std::vector<A2AProxyPeer> list;
+             for (const auto& item : peers) {
+               const py::tuple t = item.cast<py::tuple>();
+               A2AProxyPeer peer;
+               peer.rank = t[0].cast<int>();
+               peer.sync_desc = t[1].cast<fabric::MemoryRegionDescriptor>();
+               peer.recv_desc = t[2].cast<fabric::MemoryRegionDescriptor>();
+               list.push_back(std::move(peer));
+             }
+             A2AProxyBuffers buf;
+             for (const auto& kv : shadow_sync) buf.shadow_sync[kv.first.cast<int>()] = kv.second.cast<uint64_t>();
+             for (const auto& kv : shadow_recv) buf.shadow_recv[kv.first.cast<int>()] = kv.second.cast<uint64_t>();
+             buf.stage = stage;
+             buf.flag_source = flag_source;
+             buf.flag_source_host = reinterpret_cast<volatile uint32_t*>(flag_source);
+             buf.proxy_words = reinterpret_cast<volatile uint32_t*>(proxy_words);
+             buf.stage_slot = reinterpret_cast<const volatile uint32_t*>(stage_slot);
+             auto self = std::make_unique<PyProxyProbe>();
+             fabric::TransferEngine* eng = &engine.get();
+             py::gil_scoped_release release;
+             self->proxy = std::make_unique<A2AProxy>(cfg, rank, eng, std::move(list), buf, -1);
+             return self;
+           }),
+           py::arg("layout_args"), py::arg("rank"), py::arg("transfer_engine"), py::arg("peers"),
+           py::arg("shadow_sync"), py::arg("shadow_recv"), py::arg("stage"), py::arg("flag_source"),
+           py::arg("proxy_words"), py::arg("stage_slot"))
+      .def("failed", [](const PyProxyProbe& s) { return s.proxy && s.proxy->failed(); })
+      .def("error", [](const PyProxyProbe& s) { return s.proxy ? s.proxy->error() : std::string(); })
+      .def("counters",
+           [](const PyProxyProbe& s) { return py::make_tuple(s.proxy->dispatches(), s.proxy->combines()); })
+      .def("close", [](PyProxyProbe& s) {
+        py::gil_scoped_release release;
+        s.proxy.reset();
+      });
+
   py::class_<PyA2A>(m, "AllToAllContext")
       .def_static(
           "layout",
@@ -193,11 +254,11 @@ void bind_a2a(py::module_& m) {
              const py::object& scale_elemsize, int max_num_tokens, int num_experts,
              int expert_padding, int num_experts_per_token, int dp_size, int world_size,
              const py::object& combine_mode, int num_blocks, int num_sms, int virtual_ranks,
-             const py::object& wire) {
+             const py::object& wire, uint32_t node_mask) {
             const A2AParams p = make_params(hidden_dim, hidden_dim_scale, in_elemsize, out_elemsize,
                                             scale_elemsize, max_num_tokens, num_experts,
                                             expert_padding, num_experts_per_token, dp_size,
-                                            world_size, combine_mode, num_blocks, 0, wire);
+                                            world_size, combine_mode, num_blocks, 0, wire, node_mask);
             return config_dict(a2a_make_config(p, num_sms, virtual_ranks));
           },
           py::kw_only(), py::arg("hidden_dim"), py::arg("hidden_dim_scale") = py::none(),
@@ -205,7 +266,7 @@ void bind_a2a(py::module_& m) {
           py::arg("max_num_tokens"), py::arg("num_experts"), py::arg("expert_padding") = 1,
           py::arg("num_experts_per_token"), py::arg("dp_size") = 1, py::arg("world_size"),
           py::arg("combine_mode") = py::none(), py::arg("num_blocks") = 0,
-          py::arg("num_sms") = 148, py::arg("virtual_ranks") = 1, py::arg("wire") = py::none(),
+          py::arg("num_sms") = 148, py::arg("virtual_ranks") = 1, py::arg("wire") = py::none(), py::arg("node_mask") = 0,
           "Wire format and symmetric-buffer layout for a configuration (no GPU needed).")
       .def_static(
           "create",
@@ -221,7 +282,7 @@ void bind_a2a(py::module_& m) {
              const py::object& recv_ptrs, int device, const py::object& /*imm_base*/,
              const py::object& /*ranks*/, const py::object& /*transfer_engine*/,
              const py::object& /*worker_cpu*/, const py::object& combine_mode, int num_blocks,
-             int64_t wait_limit_ms, const py::object& wire) {
+             int64_t wait_limit_ms, const py::object& wire, uint32_t node_mask) {
             std::vector<int> local_ranks;
             if (py::isinstance<py::int_>(rank)) {
               local_ranks.push_back(rank.cast<int>());
@@ -231,7 +292,7 @@ void bind_a2a(py::module_& m) {
             const A2AParams p = make_params(hidden_dim, hidden_dim_scale, in_elemsize, out_elemsize,
                                             scale_elemsize, max_num_tokens, num_experts,
                                             expert_padding, num_experts_per_token, dp_size,
-                                            world_size, combine_mode, num_blocks, wait_limit_ms, wire);
+                                            world_size, combine_mode, num_blocks, wait_limit_ms, wire, node_mask);
             auto self = std::make_unique<PyA2A>();
             self->out_dtype = dtype_code(out_dtype);
             self->ctx = std::make_unique<A2AContext>(p, device, local_ranks,
@@ -253,7 +314,7 @@ void bind_a2a(py::module_& m) {
           py::arg("imm_base") = py::none(), py::arg("ranks") = py::none(),
           py::arg("transfer_engine") = py::none(), py::arg("worker_cpu") = py::none(),
           py::arg("combine_mode") = py::none(), py::arg("num_blocks") = 0,
-          py::arg("wait_limit_ms") = 0, py::arg("wire") = py::none(),
+          py::arg("wait_limit_ms") = 0, py::arg("wire") = py::none(), py::arg("node_mask") = 0,
           "Create a context. `rank` may be a list: the context then plays several ranks on one "
           "GPU and sync_ptrs / recv_ptrs hold one pointer table per local rank.")
       .def("config", [](const PyA2A& s) { return config_dict(s.ctx->config()); })
@@ -446,6 +507,28 @@ void bind_a2a(py::module_& m) {
              s.after_launch();
            },
            py::arg("send"), py::arg("recv"), py::arg("expert_y_dtype"), py::arg("stream"))
+      .def("enable_proxy",
+           [](PyA2A& s, PyEngine& engine, const py::list& peers, int local_rank, int worker_cpu) {
+             std::vector<A2AProxyPeer> list;
+             for (const auto& item : peers) {
+               const py::tuple t = item.cast<py::tuple>();
+               PPLX_REQUIRE(t.size() == 3, "a proxy peer is (rank, sync descriptor, receive descriptor)");
+               A2AProxyPeer p;
+               p.rank = t[0].cast<int>();
+               p.sync_desc = t[1].cast<fabric::MemoryRegionDescriptor>();
+               p.recv_desc = t[2].cast<fabric::MemoryRegionDescriptor>();
+               list.push_back(std::move(p));
+             }
+             fabric::TransferEngine* eng = &engine.get();
+             py::gil_scoped_release release;
+             s.ctx->enable_proxy(local_rank, eng, std::move(list), worker_cpu);
+           },
+           py::arg("transfer_engine"), py::arg("peers"), py::arg("local_rank") = 0, py::arg("worker_cpu") = -1,
+           "Serve the ranks outside this rank's NVLink domain through a transfer engine: peers is a list of "
+           "(rank, MemoryRegionDescriptor of its sync region, MemoryRegionDescriptor of its receive region).")
+      .def("proxy_counters",
+           [](const PyA2A& s, int local_rank) { return s.ctx->proxy_counters(local_rank); },
+           py::arg("local_rank") = 0, "(dispatches, combines) the host proxy has served.")
       .def("barrier",
            [](PyA2A& s, uint64_t stream) {
              s.ctx->barrier(as_stream(stream));

@@ -15,6 +15,7 @@
 #include "../fabric/local_domain.h"
 #include "../fabric/shard.h"
 #include "../fabric/transfer_engine.h"
+#include "py_fabric.h"
 #include "py_util.h"
 
 namespace py = pybind11;
@@ -25,14 +26,6 @@ namespace {
 
 struct PyPageIndices {
   std::shared_ptr<const std::vector<uint32_t>> pages;
-};
-
-struct PyEngine {
-  std::unique_ptr<TransferEngine> engine;
-  TransferEngine& get() {
-    if (!engine) throw Error(ErrorKind::kWorkerDown, "the transfer engine was stopped");
-    return *engine;
-  }
 };
 
 struct PyBuilder {

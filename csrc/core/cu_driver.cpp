@@ -53,6 +53,7 @@ Loaded& loaded() {
     bind(t.cuMemExportToShareableHandle, "cuMemExportToShareableHandle", true);
     bind(t.cuMemImportFromShareableHandle, "cuMemImportFromShareableHandle", true);
     bind(t.cuMemGetAddressRange, "cuMemGetAddressRange_v2", true);
+    bind(t.cuMemRetainAllocationHandle, "cuMemRetainAllocationHandle", false);
     bind(t.cuMemGetHandleForAddressRange, "cuMemGetHandleForAddressRange", false);
     bind(t.cuTensorMapEncodeTiled, "cuTensorMapEncodeTiled", false);
     bind(t.cuMulticastCreate, "cuMulticastCreate", false);

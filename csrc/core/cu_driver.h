@@ -35,6 +35,7 @@ struct CuDriver {
   CUresult (*cuMemImportFromShareableHandle)(CUmemGenericAllocationHandle*, void*,
                                              CUmemAllocationHandleType);
   CUresult (*cuMemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr);
+  CUresult (*cuMemRetainAllocationHandle)(CUmemGenericAllocationHandle*, void*);
   CUresult (*cuMemGetHandleForAddressRange)(void*, CUdeviceptr, size_t,
                                             CUmemRangeHandleType, unsigned long long);
   CUresult (*cuTensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

@@ -13,6 +13,7 @@
 #include "../core/error.h"
 #define PPLX_LOG_TARGET "pplx_garden::fabric::local"
 #include "../core/log.h"
+#include "../cumem/cumem.h"
 #include "peer_copy.h"
 
 namespace pplx::fabric {
@@ -46,6 +47,10 @@ struct MrInfoWire {
   uint32_t pad;
   uint64_t ipc_offset;
   cudaIpcMemHandle_t ipc;
+  int32_t has_vmm;
+  int32_t vmm_fd;
+  uint64_t vmm_size;
+  char vmm_socket[96];   // descriptor server of the owner, NUL terminated
 };
 
 std::mutex g_registry_mu;
@@ -131,6 +136,11 @@ LocalDomain::~LocalDomain() {
     }
     for (auto& kv : remotes_) {
       if (kv.second.ipc_base != nullptr) cudaIpcCloseMemHandle(kv.second.ipc_base);
+      if (kv.second.vmm_va != 0 && CuDriver::available()) {
+        const CuDriver& cu = CuDriver::get();
+        cu.cuMemUnmap(static_cast<CUdeviceptr>(kv.second.vmm_va), kv.second.vmm_size);
+        cu.cuMemAddressFree(static_cast<CUdeviceptr>(kv.second.vmm_va), kv.second.vmm_size);
+      }
     }
     if (scratch_) cudaFree(scratch_);
     if (error_flag_host_) cudaFreeHost(error_flag_host_);
@@ -152,6 +162,11 @@ void LocalDomain::ensure_stream() {
   PPLX_CUDA_CHECK(cudaHostAlloc(reinterpret_cast<void**>(&error_flag_host_), 64, cudaHostAllocMapped));
   std::memset(error_flag_host_, 0, 64);
   PPLX_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&error_flag_dev_), error_flag_host_, 0));
+  // Everything a later write could otherwise allocate or load lazily is set up here, at
+  // registration time: a write may be submitted while a kernel that waits for it fills the GPU,
+  // and cudaMalloc or a first kernel launch can then block behind that very kernel.
+  device_scratch(1u << 17);
+  PPLX_CUDA_CHECK(warm_up_paged_copy(stream_));
 }
 
 uint32_t* LocalDomain::device_scratch(size_t words) {
@@ -181,6 +196,7 @@ MemoryRegionRemoteKey LocalDomain::register_mr(uint64_t ptr, uint64_t len, int d
   r.len = len;
   r.device = device;
   r.rkey = next_rkey_++;
+  if (device >= 0 && device_ >= 0) ensure_stream();
   if (device >= 0) {
     // A CUDA IPC handle names a whole allocation: find its base so that peers in other
     // processes can map it and add the offset of this region.
@@ -195,7 +211,21 @@ MemoryRegionRemoteKey LocalDomain::register_mr(uint64_t ptr, uint64_t len, int d
         r.ipc = h;
         r.ipc_offset = ptr - static_cast<uint64_t>(base);
       } else {
-        cudaGetLastError();  // VMM or managed memory: reachable inside this process only
+        cudaGetLastError();
+        // not cudaMalloc memory; a virtual-memory allocation can be shared as a file descriptor
+        CUmemGenericAllocationHandle handle;
+        if (cu.cuMemRetainAllocationHandle != nullptr &&
+            cu.cuMemRetainAllocationHandle(&handle, reinterpret_cast<void*>(ptr)) == CUDA_SUCCESS) {
+          int fd = -1;
+          if (cu.cuMemExportToShareableHandle(&fd, handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0) ==
+              CUDA_SUCCESS) {
+            r.vmm_fd = fd;
+            r.vmm_size = size;
+            r.ipc_offset = ptr - static_cast<uint64_t>(base);
+            fd_server_register(fd);
+          }
+          cu.cuMemRelease(handle);   // the retain above took a reference
+        }
       }
     }
   }
@@ -208,6 +238,10 @@ void LocalDomain::unregister_mr(uint64_t ptr) {
   std::lock_guard<std::mutex> lock(regions_mu_);
   auto it = regions_.find(ptr);
   if (it == regions_.end()) return;
+  if (it->second.vmm_fd >= 0) {
+    fd_server_unregister(it->second.vmm_fd);
+    close(it->second.vmm_fd);
+  }
   by_rkey_.erase(it->second.rkey);
   regions_.erase(it);
 }
@@ -221,6 +255,13 @@ std::string LocalDomain::region_info(const Region& r) const {
   w.has_ipc = r.has_ipc ? 1 : 0;
   w.ipc_offset = r.ipc_offset;
   w.ipc = r.ipc;
+  if (r.vmm_fd >= 0) {
+    w.has_vmm = 1;
+    w.vmm_fd = r.vmm_fd;
+    w.vmm_size = r.vmm_size;
+    const std::string name = fd_server_name();
+    std::strncpy(w.vmm_socket, name.c_str(), sizeof(w.vmm_socket) - 1);
+  }
   return std::string(reinterpret_cast<const char*>(&w), sizeof(w));
 }
 
@@ -338,10 +379,45 @@ void LocalDomain::handle(Message& msg, std::vector<DomainCompletion>* out) {
         rr.owner_ptr = w.ptr;
         rr.len = w.len;
         if (w.device >= 0) {
-          if (!w.has_ipc) {
-            failure = "the destination region cannot be shared between processes (no CUDA IPC handle)";
-          } else if (device_ < 0) {
+          if (device_ < 0) {
             failure = "a host-only domain cannot write into another process's GPU memory";
+          } else if (!w.has_ipc && w.has_vmm) {
+            // a CUDA virtual-memory allocation: fetch its descriptor, import and map it here
+            try {
+              const CuDriver& cu = CuDriver::get();
+              cudaSetDevice(device_);
+              cu_ensure_context(device_);
+              w.vmm_socket[sizeof(w.vmm_socket) - 1] = 0;
+              const int fd = fd_fetch(w.pid, w.vmm_fd, w.vmm_socket);
+              CUmemGenericAllocationHandle handle;
+              const CUresult imported = cu.cuMemImportFromShareableHandle(
+                  &handle, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)), CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+              close(fd);
+              PPLX_CU_CHECK(imported);
+              CUdeviceptr va = 0;
+              PPLX_CU_CHECK(cu.cuMemAddressReserve(&va, w.vmm_size, 0, 0, 0));
+              CUresult mapped = cu.cuMemMap(va, w.vmm_size, 0, handle, 0);
+              cu.cuMemRelease(handle);   // the mapping keeps the memory alive
+              if (mapped == CUDA_SUCCESS) {
+                CUmemAccessDesc access{};
+                access.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+                access.location.id = device_;
+                access.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+                mapped = cu.cuMemSetAccess(va, w.vmm_size, &access, 1);
+                if (mapped != CUDA_SUCCESS) cu.cuMemUnmap(va, w.vmm_size);
+              }
+              if (mapped != CUDA_SUCCESS) {
+                cu.cuMemAddressFree(va, w.vmm_size);
+                PPLX_CU_CHECK(mapped);
+              }
+              rr.vmm_va = static_cast<uint64_t>(va);
+              rr.vmm_size = w.vmm_size;
+              rr.mapped = reinterpret_cast<uint8_t*>(va) + w.ipc_offset;
+            } catch (const std::exception& e) {
+              failure = std::string("importing the destination's virtual-memory allocation: ") + e.what();
+            }
+          } else if (!w.has_ipc) {
+            failure = "the destination region cannot be shared between processes (no CUDA IPC handle)";
           } else {
             cudaSetDevice(device_);
             void* base = nullptr;
@@ -692,7 +768,12 @@ void LocalDomain::run_write(const PendingWrite& w, RemoteRegion& rr, std::vector
   ensure_stream();
   PPLX_CUDA_CHECK(cudaSetDevice(device_));
 
-  if (dst_dev && src_dev) {
+  if (dst_dev && src_dev && num_pages == 1 && src_pages == nullptr) {
+    // One contiguous range: the copy engines move it, no SM is needed. That matters to callers
+    // whose own kernels fill the GPU while they wait for this very copy (the all-to-all proxy).
+    PPLX_CUDA_CHECK(cudaMemcpyAsync(rr.mapped + dst_offset, reinterpret_cast<const void*>(src_base + src_offset),
+                                    length, cudaMemcpyDeviceToDevice, stream_));
+  } else if (dst_dev && src_dev) {
     PagedCopyArgs a{};
     a.src_base = reinterpret_cast<const uint8_t*>(src_base);
     a.dst_base = rr.mapped;
@@ -763,8 +844,14 @@ void LocalDomain::poll_progress(std::vector<DomainCompletion>* out) {
     const cudaError_t e = cudaEventQuery(f.event);
     if (e == cudaErrorNotReady) {
       cudaGetLastError();
+      if (++stuck_polls_ == 2000000) {
+        PPLX_WARN("a copy of transfer %llu on %s has not completed after %llu polls (%zu in flight)",
+                  static_cast<unsigned long long>(f.id), info_.name.c_str(),
+                  static_cast<unsigned long long>(stuck_polls_), in_flight_.size());
+      }
       break;
     }
+    stuck_polls_ = 0;
     DomainCompletion c;
     c.transfer_id = f.id;
     if (e != cudaSuccess) {

@@ -56,6 +56,10 @@ class LocalDomain : public Domain {
     bool has_ipc = false;
     cudaIpcMemHandle_t ipc{};
     uint64_t ipc_offset = 0;  // ptr - allocation base
+    // CUDA virtual-memory allocations (cuMemCreate) have no IPC handle: they travel as a POSIX
+    // file descriptor that the importer fetches from this process's descriptor server
+    int vmm_fd = -1;
+    uint64_t vmm_size = 0;    // bytes of the whole allocation; ipc_offset is the offset into it
   };
   struct RemoteRegion {
     bool resolved = false;
@@ -64,6 +68,7 @@ class LocalDomain : public Domain {
     uint64_t owner_ptr = 0, len = 0;
     uint8_t* mapped = nullptr;  // usable base pointer here (device regions), else nullptr
     void* ipc_base = nullptr;   // to close
+    uint64_t vmm_va = 0, vmm_size = 0;   // to unmap (imported virtual-memory allocation)
   };
   struct Message {
     uint32_t type = 0;
@@ -131,6 +136,7 @@ class LocalDomain : public Domain {
   std::unordered_map<TransferId, size_t> host_write_acks_;  // outstanding cross-process host writes
   uint64_t writes_submitted_ = 0;
   uint64_t fail_write_at_ = 0;
+  uint64_t stuck_polls_ = 0;   // polls since the oldest copy in flight last made progress
 };
 
 }  // namespace pplx::fabric

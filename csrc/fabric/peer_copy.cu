@@ -136,4 +136,20 @@ cudaError_t launch_paged_copy(const PagedCopyArgs& args, int max_ctas, cudaStrea
   return cudaGetLastError();
 }
 
+cudaError_t warm_up_paged_copy(cudaStream_t stream) {
+  // Empty launches: the kernels return at once, but their code is loaded and their attributes
+  // are set. With lazy module loading the first launch of a kernel may otherwise have to wait
+  // for kernels that are running, and one of those may be waiting for this copy.
+  PagedCopyArgs args{};
+  const size_t smem = static_cast<size_t>(kStages) * kChunkBytes;
+  cudaError_t e = cudaFuncSetAttribute(paged_copy_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  paged_copy_bulk_kernel<<<1, kBulkThreads, smem, stream>>>(args);
+  paged_copy_simt_kernel<<<1, 256, 0, stream>>>(args);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  return cudaStreamSynchronize(stream);
+}
+
 }  // namespace pplx::fabric

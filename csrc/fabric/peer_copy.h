@@ -28,4 +28,8 @@ struct PagedCopyArgs {
 // `max_ctas` <= 0 picks a default that saturates NVLink with a fraction of the SMs.
 cudaError_t launch_paged_copy(const PagedCopyArgs& args, int max_ctas, cudaStream_t stream);
 
+// Loads the copy kernels on the current device (empty launches) and waits for them. Call once
+// per device at set-up time, never while a kernel that depends on a later copy is running.
+cudaError_t warm_up_paged_copy(cudaStream_t stream);
+
 }  // namespace pplx::fabric

@@ -12,8 +12,10 @@ serving code written against it runs unchanged. What happens underneath differs:
 * receive regions are sized for the worst case (each source token reaches a rank at most
   once), so ``max_private_tokens`` has nothing left to tune and is accepted for
   compatibility only; ``nets_per_gpu`` likewise;
-* a world larger than one NVSwitch domain (8 GPUs) needs an RDMA transport and is
-  rejected here.
+* ranks outside ``node_group`` (another node, or the other half of this box when a test
+  slices it into "nodes") are served by a host proxy thread that forwards what the kernels
+  staged for them through a ``TransferEngine`` and writes their arrival flags after the data
+  (csrc/a2a/a2a_proxy.h); on this build the engine's provider is the intra-box one.
 
 Extensions (keyword-only, all optional): ``combine_mode="pre_reduce"`` makes the expert
 ranks apply the routing weights given at dispatch time and send one partial sum per
@@ -109,15 +111,28 @@ class P2PAllToAll(AllToAllKernel):
 
         rank = global_group.rank if global_group is not None else 0
         world_size = global_group.size if global_group is not None else 1
-        if world_size > _NVLINK_DOMAIN:
-            raise NotImplementedError(
-                f"world size {world_size} exceeds one NVLink domain ({_NVLINK_DOMAIN} GPUs); "
-                "the inter-node path needs an RDMA NIC, which this build does not drive"
-            )
+        # Ranks of `node_group` share an NVLink domain: their memory is mapped here and the kernels
+        # write into it. Ranks outside it are served by a host proxy through a transfer engine, as
+        # every inter-node rank is in the reference (p2p-all-to-all/src/a2a_worker.rs:340-455).
+        # Unlike there, node_group=None means "all ranks are in one NVLink domain".
+        node_ranks = list(range(world_size))
         if node_group is not None and node_group.size != world_size:
-            logger.info(
-                "node_group of %d ranks inside a world of %d: all ranks share one NVSwitch "
-                "domain here, so all traffic uses NVLink", node_group.size, world_size)
+            node_ranks = sorted(node_group.all_gather_object(rank))
+        if len(node_ranks) > _NVLINK_DOMAIN:
+            raise NotImplementedError(
+                f"an NVLink domain of {len(node_ranks)} ranks: at most {_NVLINK_DOMAIN} GPUs share a switch; "
+                "pass node_group to name the ranks of this node")
+        if world_size > 32:
+            raise NotImplementedError("the rank masks of the kernels hold 32 ranks")
+        self._node_ranks = node_ranks
+        self._multi_node = len(node_ranks) != world_size
+        node_mask = 0
+        for r in node_ranks:
+            node_mask |= 1 << r
+        if self._multi_node:
+            if wire not in (None, "plain"):
+                raise ValueError("ranks outside the NVLink domain need wire='plain'")
+            wire = "plain"
         self._rank = rank
         self._world_size = world_size
         self._num_local_experts = ceil_div(num_experts, world_size)
@@ -125,6 +140,10 @@ class P2PAllToAll(AllToAllKernel):
         self._all_to_all: Optional[AllToAllContext] = None
 
         props = torch.cuda.get_device_properties(device)
+        if self._multi_node and num_blocks == 0:
+            # The engine's paged copies are kernels of their own: while a dispatch or combine
+            # waits for rows that such a copy is to deliver, the copy must find a free SM.
+            num_blocks = max(1, props.multi_processor_count - 16)
         layout = AllToAllContext.layout(
             hidden_dim=hidden_dim,
             hidden_dim_scale=hidden_dim_scale,
@@ -141,6 +160,7 @@ class P2PAllToAll(AllToAllKernel):
             num_blocks=num_blocks,
             num_sms=props.multi_processor_count,
             wire=wire,
+            node_mask=node_mask,
         )
         self._layout = layout
         self.max_recv_rows: int = layout["max_recv_rows"]
@@ -156,26 +176,41 @@ class P2PAllToAll(AllToAllKernel):
         recv_mapping.to_tensor((recv_mapping.size,), torch.uint8).zero_()
         torch.cuda.synchronize(device)
 
-        self._mappings: list[_PeerMappings] = []
-        if world_size > 1:
-            assert global_group is not None
-            mine = _RankRegions(self._sync_handle.export(), self._recv_handle.export())
-            everyone = global_group.all_gather_object(mine)
-            for peer, regions in enumerate(everyone):
-                if peer == rank:
-                    self._mappings.append(_PeerMappings(sync_mapping, recv_mapping))
-                else:
-                    self._mappings.append(
-                        _PeerMappings(
-                            regions.sync_handle.bind(device).map(device),
-                            regions.recv_handle.bind(device).map(device),
-                        )
+        self._mappings: list[Optional[_PeerMappings]] = [None] * world_size
+        self._mappings[rank] = _PeerMappings(sync_mapping, recv_mapping)
+        sharing_group = node_group if self._multi_node else global_group
+        if len(node_ranks) > 1:
+            assert sharing_group is not None
+            mine = (rank, _RankRegions(self._sync_handle.export(), self._recv_handle.export()))
+            for peer, regions in sharing_group.all_gather_object(mine):
+                if peer != rank:
+                    self._mappings[peer] = _PeerMappings(
+                        regions.sync_handle.bind(device).map(device),
+                        regions.recv_handle.bind(device).map(device),
                     )
             # Every peer has imported our descriptors: the exporter may now close them.
-            global_group.barrier()
-            del mine, everyone
-        else:
-            self._mappings.append(_PeerMappings(sync_mapping, recv_mapping))
+            sharing_group.barrier()
+            del mine
+
+        # The transfer engine for the ranks outside the domain, and everybody's descriptors.
+        self._engine = None
+        proxy_peers = []
+        if self._multi_node:
+            from pplx_garden.fabric_lib import TransferEngine
+
+            assert global_group is not None
+            if os.environ.get("CUDA_MODULE_LOADING", "").upper() != "EAGER":
+                logger.warning(
+                    "ranks outside the NVLink domain are served by copies that this GPU executes itself "
+                    "(intra-box provider): set CUDA_MODULE_LOADING=EAGER, or make sure no kernel is launched "
+                    "for the first time while a dispatch or combine is in flight; lazy module loading holds "
+                    "copies back until running kernels finish, and those kernels wait for the copies")
+            self._engine = TransferEngine(max(nets_per_gpu, 1), [device.index])
+            _, sync_desc = self._engine.register_memory(sync_mapping.data_ptr(), sync_mapping.size, device)
+            _, recv_desc = self._engine.register_memory(recv_mapping.data_ptr(), recv_mapping.size, device)
+            for peer, sd, rd in global_group.all_gather_object((rank, sync_desc, recv_desc)):
+                if peer not in node_ranks:
+                    proxy_peers.append((peer, sd, rd))
 
         self._all_to_all = AllToAllContext.create(
             hidden_dim=hidden_dim,
@@ -193,14 +228,24 @@ class P2PAllToAll(AllToAllKernel):
             dp_size=self._dp_size,
             node_size=world_size,
             world_size=world_size,
-            sync_ptrs=[m.sync.data_ptr() for m in self._mappings],
-            recv_ptrs=[m.recv.data_ptr() for m in self._mappings],
+            sync_ptrs=[0 if m is None else m.sync.data_ptr() for m in self._mappings],
+            recv_ptrs=[0 if m is None else m.recv.data_ptr() for m in self._mappings],
             device=device.index,
             combine_mode=combine_mode,
             num_blocks=num_blocks,
             wait_limit_ms=wait_limit_ms,
             wire=layout["wire"],
+            node_mask=node_mask,
         )
+        if self._multi_node:
+            cpus = []
+            try:
+                for group in type(self._engine).detect_topology():
+                    if group.cuda_device == device.index:
+                        cpus = group.cpus
+            except Exception:
+                cpus = []
+            self._all_to_all.enable_proxy(self._engine, proxy_peers, 0, cpus[-1] if cpus else -1)
         self._check_every = int(os.environ.get("PPLX_A2A_CHECK_EVERY", "0"))
         self._calls = 0
 
@@ -390,11 +435,17 @@ class P2PAllToAll(AllToAllKernel):
         # No peer may still be writing into our regions when they are unmapped.
         if self._global_group is not None:
             self._global_group.barrier()
-        self._all_to_all.destroy()
+        self._all_to_all.destroy()      # joins the proxy thread, if any
         self._all_to_all = None
+        if self._engine is not None:
+            self._engine.stop()
+            self._engine = None
+            if self._global_group is not None:
+                self._global_group.barrier()   # no engine still has our regions mapped
         for m in self._mappings:
-            m.sync.unmap()
-            m.recv.unmap()
+            if m is not None:
+                m.sync.unmap()
+                m.recv.unmap()
         self._mappings.clear()
         del self._sync_handle, self._recv_handle
         if self._global_group is not None:
