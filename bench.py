@@ -322,6 +322,9 @@ def main() -> None:
             a2a.dispatch(num, ox, osc, xq, sc, idx, w)
             a2a.combine(out, idx, w, expert_y)
 
+        def all_counts_idx(i32: torch.Tensor) -> torch.Tensor:
+            return i32.view(torch.int32).to(torch.int64).flatten()
+
         def line_up() -> None:
             # cold L2 without a cache full of dirty lines: write 256 MiB, then read it back
             flush.zero_()
@@ -454,21 +457,75 @@ def main() -> None:
             res_out = torch.empty((tokens, H), dtype=torch.bfloat16).pin_memory()
             h2d = offs[-1]
             d2h = res_num.numel() * 4 + res_out.numel() * 2
-            e2e_us = []
             xq, sc, idx, w = views(d_in)
-            for i in range(warmup + steps):
-                line_up()
-                torch.cuda.synchronize()
-                t0 = time.perf_counter()
+
+            def eager_step(i: int) -> None:
                 packed_dev.copy_(packed_host[i % pool], non_blocking=True)
                 a2a.dispatch(num, ox, osc, xq, sc, idx, w)
                 a2a.combine(out, idx, w, expert_y)
                 res_num.copy_(num, non_blocking=True)
                 res_out.copy_(out, non_blocking=True)
-                torch.cuda.current_stream().synchronize()
-                if i >= warmup:
-                    e2e_us.append((time.perf_counter() - t0) * 1e6)
-            e2e = {"mean_us": statistics.fmean(e2e_us), "h2d": h2d, "d2h": d2h}
+
+            def measure(run_step) -> tuple[float, float]:
+                """(device-timed, host-clock) mean microseconds of one step. Device: CUDA events
+                around [copy in ... copy out] on the launching stream, the ranks lined up by the
+                untimed barrier just before, the host enqueuing ahead of the GPU as a serving loop
+                does. Host clock: from an idle GPU to the result being readable on the host."""
+                dev_us, host_us = [], []
+                for i in range(warmup + steps):
+                    ev0 = torch.cuda.Event(enable_timing=True)
+                    ev1 = torch.cuda.Event(enable_timing=True)
+                    line_up()
+                    ev0.record()
+                    run_step(i)
+                    ev1.record()
+                    torch.cuda.current_stream().synchronize()    # the result is on the host now
+                    if i >= warmup:
+                        dev_us.append(ev0.elapsed_time(ev1) * 1000)
+                for i in range(warmup + steps):
+                    line_up()
+                    torch.cuda.synchronize()
+                    t0 = time.perf_counter()
+                    run_step(i)
+                    torch.cuda.current_stream().synchronize()
+                    if i >= warmup:
+                        host_us.append((time.perf_counter() - t0) * 1e6)
+                return statistics.fmean(dev_us), statistics.fmean(host_us)
+
+            eager_dev, eager_host = measure(eager_step)
+            e2e = {"mean_us": eager_dev, "host_clock_us": eager_host, "h2d": h2d, "d2h": d2h,
+                   "mode": "eager calls"}
+            # The same step as a serving loop launches it: captured once per staging buffer in a
+            # CUDA graph (copy in, dispatch, combine, copy out) and replayed. Epochs and cursors
+            # live on the device, so a replay is a step like any other.
+            if args.impl == "ours":
+                try:
+                    side = torch.cuda.Stream(device)
+                    graphs = []
+                    torch.cuda.synchronize()
+                    for buf in packed_host:
+                        g = torch.cuda.CUDAGraph()
+                        with torch.cuda.stream(side):
+                            with torch.cuda.graph(g, stream=side):
+                                packed_dev.copy_(buf, non_blocking=True)
+                                a2a.dispatch(num, ox, osc, xq, sc, idx, w)
+                                a2a.combine(out, idx, w, expert_y)
+                                res_num.copy_(num, non_blocking=True)
+                                res_out.copy_(out, non_blocking=True)
+                        graphs.append(g)
+                    torch.cuda.synchronize()
+                    graph_dev, graph_host = measure(lambda i: graphs[i % pool].replay())
+                    a2a.check()
+                    if world == 1:   # the replay really ran the step: its counts match the routing it was given
+                        assert torch.equal(res_num.to(torch.int64),
+                                           torch.bincount(all_counts_idx(idx), minlength=E)[:L].cpu())
+                    e2e.update(eager_mean_us=eager_dev, eager_host_clock_us=eager_host,
+                               graph_mean_us=graph_dev, graph_host_clock_us=graph_host)
+                    if graph_dev < eager_dev:
+                        e2e.update(mean_us=graph_dev, host_clock_us=graph_host,
+                                   mode="CUDA graph replay of [copy in, dispatch, combine, copy out]")
+                except Exception as exc:  # capture is an optimisation of the measurement, not a requirement
+                    e2e["graph_error"] = f"{type(exc).__name__}: {exc}"[:200]
 
         if args.impl == "ours":
             a2a.check()
@@ -496,6 +553,7 @@ def main() -> None:
         "back_to_back_us_per_step": reduce_max(main_res["b2b_us"]),
     }
     e2e_val = reduce_max(main_res["e2e"]["mean_us"]) if main_res["e2e"] else None
+    e2e_host = reduce_max(main_res["e2e"]["host_clock_us"]) if main_res["e2e"] else None
     other_tokens = 4096 if args.tokens == 128 else 128
     if not args.no_prefill:
         other_steps = max(10, min(args.steps, 40)) if other_tokens > 128 else args.steps
@@ -550,6 +608,15 @@ def main() -> None:
                 "h2d_bytes_per_step": main_res["e2e"]["h2d"],
                 "d2h_bytes_per_step": main_res["e2e"]["d2h"],
                 "readback": "the whole combined tensor [tokens, hidden] bf16 + per-expert token counts, to pinned host memory",
+                "mode": main_res["e2e"].get("mode"),
+                "timing": "CUDA events around [copy in ... copy out], max over ranks of the mean; "
+                          "host_clock_value is the same step by the host clock from an idle GPU",
+                "host_clock_value": e2e_host,
+                "eager_value": main_res["e2e"].get("eager_mean_us"),
+                "eager_host_clock_value": main_res["e2e"].get("eager_host_clock_us"),
+                "graph_value": main_res["e2e"].get("graph_mean_us"),
+                "graph_host_clock_value": main_res["e2e"].get("graph_host_clock_us"),
+                "graph_error": main_res["e2e"].get("graph_error"),
             }
         print(json.dumps(line))
 

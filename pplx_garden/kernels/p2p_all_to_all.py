@@ -65,6 +65,13 @@ class _PeerMappings:
     recv: CUMemMapping
 
 
+def _sig(t: Optional[torch.Tensor]):
+    """What the argument checks of dispatch / combine depend on."""
+    if t is None:
+        return None
+    return (t.data_ptr(), t.shape, t.stride(), t.dtype)
+
+
 class P2PAllToAll(AllToAllKernel):
     def __init__(
         self,
@@ -246,6 +253,8 @@ class P2PAllToAll(AllToAllKernel):
             except Exception:
                 cpus = []
             self._all_to_all.enable_proxy(self._engine, proxy_peers, 0, cpus[-1] if cpus else -1)
+        self._dispatch_args: dict = {}
+        self._combine_args: dict = {}
         self._check_every = int(os.environ.get("PPLX_A2A_CHECK_EVERY", "0"))
         self._calls = 0
 
@@ -287,6 +296,21 @@ class P2PAllToAll(AllToAllKernel):
         a2a = self._all_to_all
         assert a2a is not None
         assert do_send or do_recv
+        # A serving loop calls with the same tensors step after step: the checks below run once
+        # per distinct set of (address, shape, strides, dtype) and the packed arguments are kept.
+        key = (_sig(out_expert_num_tokens), _sig(out_expert_x), _sig(out_expert_x_scale), _sig(dp_x),
+               _sig(dp_x_scale), _sig(indices), _sig(weights), _sig(bound_m))
+        cached = self._dispatch_args.get(key)
+        if cached is not None:
+            send, recv, out_rows, quantize = cached
+            stream = torch.cuda.current_stream().cuda_stream
+            if do_send and do_recv:
+                a2a.dispatch(*send, *recv, stream, out_rows, quantize)
+            elif do_send:
+                a2a.dispatch_send(*send, stream, quantize)
+            else:
+                a2a.dispatch_recv(*recv, stream, out_rows)
+            return
         num_tokens = dp_x.shape[0]
         K = self._num_experts_per_token
         H = self._hidden_dim
@@ -338,6 +362,9 @@ class P2PAllToAll(AllToAllKernel):
                 indices.data_ptr(), indices.stride(0), weights.data_ptr(), weights.stride(0),
                 bound_m_ptr)
         recv = (out_expert_num_tokens.data_ptr(), out_expert_x.data_ptr(), out_x_stride, *out_scale)
+        if len(self._dispatch_args) > 64:
+            self._dispatch_args.clear()
+        self._dispatch_args[key] = (send, recv, out_rows, quantize)
         if do_send and do_recv:
             a2a.dispatch(*send, *recv, stream, out_rows, quantize)
         elif do_send:
@@ -361,6 +388,18 @@ class P2PAllToAll(AllToAllKernel):
         assert a2a is not None
         assert do_send or do_recv
         assert not accumulate or self._dp_size == 1, "accumulate is not supported with dp_size > 1"
+        key = (_sig(out_tokens), _sig(indices), _sig(weights), _sig(expert_y), _sig(bound_m), accumulate)
+        cached = self._combine_args.get(key)
+        if cached is not None and expert_y is not None:
+            y_ptr, y_stride, num_tokens, y_dtype, y_rows, recv = cached
+            stream = torch.cuda.current_stream().cuda_stream
+            if do_send and do_recv:
+                a2a.combine(y_ptr, y_stride, num_tokens, y_dtype, *recv, stream)
+            elif do_send:
+                a2a.combine_send(y_ptr, y_stride, stream, y_dtype)
+            else:
+                a2a.combine_recv(num_tokens, y_rows, y_dtype, *recv, stream)
+            return
         K = self._num_experts_per_token
         H = self._hidden_dim
         num_tokens = indices.shape[0]
@@ -392,13 +431,16 @@ class P2PAllToAll(AllToAllKernel):
         y_ptr = expert_y.data_ptr()
         y_stride = expert_y.stride(0) * expert_y.element_size()
         recv = (out_tokens.data_ptr(), out_tokens.stride(0), indices.data_ptr(), indices.stride(0),
-                weights.data_ptr(), weights.stride(0), bound_m_ptr, accumulate, stream)
+                weights.data_ptr(), weights.stride(0), bound_m_ptr, accumulate)
+        if len(self._combine_args) > 64:
+            self._combine_args.clear()
+        self._combine_args[key] = (y_ptr, y_stride, num_tokens, expert_y.dtype, expert_y.shape[0], recv)
         if do_send and do_recv:
-            a2a.combine(y_ptr, y_stride, num_tokens, expert_y.dtype, *recv)
+            a2a.combine(y_ptr, y_stride, num_tokens, expert_y.dtype, *recv, stream)
         elif do_send:
             a2a.combine_send(y_ptr, y_stride, stream, expert_y.dtype)
         else:
-            a2a.combine_recv(num_tokens, expert_y.shape[0], expert_y.dtype, *recv)
+            a2a.combine_recv(num_tokens, expert_y.shape[0], expert_y.dtype, *recv, stream)
 
     # ------------------------------------------------------------------
     def barrier(self) -> None:

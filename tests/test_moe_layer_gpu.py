@@ -176,7 +176,7 @@ def _worker(device, dp_group, global_group, seed, fused=False):
 
 
 @pytest.mark.parametrize("fused", [False, True])
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_multi_gpu_layer_matches_reference(world: int, fused: bool) -> None:
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
