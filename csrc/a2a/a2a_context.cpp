@@ -212,6 +212,9 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
     const size_t o_stats = take(sizeof(unsigned long long) * 8);
     const size_t o_trace = take(sizeof(unsigned long long) * kTraceSlots);
     const size_t o_scatter_done = take(sizeof(uint32_t));
+    const size_t o_route_hist = take(sizeof(uint32_t) * 2 * cfg_.num_experts);
+    const size_t o_route_nrec = take(sizeof(uint32_t) * 2 * kMaxRanks);
+    const size_t o_route_done = take(sizeof(uint32_t) * 2);
     void* base = nullptr;
     PPLX_CUDA_CHECK(cudaMalloc(&base, off));
     allocations_.push_back(base);
@@ -230,6 +233,9 @@ A2AContext::A2AContext(const A2AParams& params, int device, const std::vector<in
     st.local.status = reinterpret_cast<uint32_t*>(b + o_status);
     st.local.stats = reinterpret_cast<unsigned long long*>(b + o_stats);
     st.local.trace = reinterpret_cast<unsigned long long*>(b + o_trace);
+    st.local.route_hist = reinterpret_cast<uint32_t*>(b + o_route_hist);
+    st.local.route_nrec = reinterpret_cast<uint32_t*>(b + o_route_nrec);
+    st.local.route_done = reinterpret_cast<uint32_t*>(b + o_route_done);
     trace_ptrs_.push_back(st.local.trace);
     scatter_done_ptrs_.push_back(reinterpret_cast<uint32_t*>(b + o_scatter_done));
     uint32_t* host_flag = nullptr;
@@ -413,6 +419,10 @@ void A2AContext::dispatch(const DispatchSendArgs* send, const DispatchRecvArgs* 
                      "fused quantisation needs a 1-byte wire type and one scale per 128 elements");
       } else if (cfg_.hidden_dim_scale > 0) {
         PPLX_REQUIRE(send[i].x_scale != nullptr, "dispatch: dp_x_scale is required");
+      }
+      if (send[i].logits != nullptr) {
+        PPLX_REQUIRE(cfg_.num_experts <= 512, "routing fused into dispatch handles at most 512 experts");
+        PPLX_REQUIRE(send[i].logits_stride >= cfg_.num_experts, "dispatch: logits rows are shorter than num_experts");
       }
       last_tokens_ = std::max<int64_t>(send[i].num_tokens, 1);
     }

@@ -43,6 +43,7 @@
 #include "a2a_types.h"
 #include "ptx.cuh"
 #include "a2a_device.cuh"
+#include "../ops/router.cuh"
 #include "a2a_ll.cuh"
 
 namespace pplx {
@@ -60,53 +61,34 @@ __host__ __device__ inline size_t dispatch_stage_offset(const A2AConfig& cfg) {
   return ((send > recv ? send : recv) + 15) / 16 * 16;
 }
 
+// Top-k routing of token t by the calling warp (see ops/router.cuh); lane r < k gets the r-th
+// expert and its weight.
+__device__ __forceinline__ void route_token(const A2AConfig& cfg, const DispatchSendArgs& a, int t,
+                                            uint32_t* expert, float* weight) {
+  const size_t elem = a.logits_bf16 ? 2 : 4;
+  const void* row = static_cast<const char*>(a.logits) + static_cast<size_t>(t) * a.logits_stride * elem;
+  if (cfg.num_experts <= 128) {
+    ops::route_token_warp<4>(row, a.logits_bf16 != 0, a.logits_bias, cfg.num_experts, cfg.topk, expert, weight);
+  } else if (cfg.num_experts <= 256) {
+    ops::route_token_warp<8>(row, a.logits_bf16 != 0, a.logits_bias, cfg.num_experts, cfg.topk, expert, weight);
+  } else {
+    ops::route_token_warp<16>(row, a.logits_bf16 != 0, a.logits_bias, cfg.num_experts, cfg.topk, expert, weight);
+  }
+}
+
+// The counts message of one dispatch, sent by one whole block from a histogram in shared memory:
+// per destination, how many records it will get from this rank and how many of them each of
+// its experts takes. It also tells every rank that this rank has started the dispatch (and so
+// has left its previous combine): a rank that has heard that from everybody may write the
+// combine buffers again.
 template <int WIRE>
-__device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st,
-                                    const DispatchSendArgs& a, uint32_t* dyn_smem, const int TEAM) {
+__device__ void send_counts(const A2AConfig& cfg, const A2ARankState& st, const uint32_t* hist,
+                            const uint32_t* nrec, uint32_t tag, uint32_t par) {
   const A2ALocal& ws = st.local;
-  const Team team(TEAM);
   const int world = cfg.world;
-  const int K = cfg.topk;
   const int L = cfg.experts_per_rank;
   const int my_group = st.rank / cfg.dp_size;
   const int my_tp = st.rank % cfg.dp_size;
-  const uint32_t epoch = read_epoch(ws, 0);
-  const uint32_t tag = epoch + 1;
-  const uint32_t par = epoch & 1u;
-  trace_mark(cfg, ws, kTraceSendStart);
-
-  int T = a.num_tokens;
-  if (a.bound_m != nullptr) T = min(T, *a.bound_m);
-  T = max(0, min(T, cfg.max_num_tokens));
-
-  // ---- counts message: leaves before any payload, from the block with the fewest tokens ----
-  // Per destination: how many records it will get from this rank and how many of them each
-  // of its experts takes. The "dispatch started" word goes to every rank (also to those this
-  // rank serves no records): a rank that has seen it from everybody knows that all ranks
-  // have left their previous combine, so the combine buffers may be written again.
-  if (blockIdx.x == gridDim.x - 1) {
-    uint32_t* hist = dyn_smem;                // [num_experts]
-    uint32_t* nrec = hist + cfg.num_experts;  // [kMaxRanks]
-    for (int i = threadIdx.x; i < cfg.num_experts + kMaxRanks; i += blockDim.x) hist[i] = 0;
-    // the slot cursors of the next dispatch; nobody touches that bank during this launch
-    if (threadIdx.x < kMaxRanks) ws.send_cursor[(par ^ 1u) * kMaxRanks + threadIdx.x] = 0;
-    __syncthreads();
-    for (int t = threadIdx.x; t < T; t += blockDim.x) {
-      uint32_t mask = 0;
-      for (int k = 0; k < K; ++k) {
-        const uint32_t e = a.indices[t * a.indices_stride + k];
-        if (e < static_cast<uint32_t>(cfg.num_experts)) {
-          atomicAdd(&hist[e], 1u);
-          mask |= 1u << (e / L);
-        } else {
-          report(ws, kStatusBadExpertIndex, kPhaseDispatchSend, t, e);
-        }
-      }
-      for (int d = 0; d < world; ++d) {
-        if ((mask >> d) & 1u) atomicAdd(&nrec[d], 1u);
-      }
-    }
-    __syncthreads();
     if (has_remote(cfg) && threadIdx.x < world) {
       const bool served = static_cast<int>(threadIdx.x % cfg.dp_size) == my_tp;
       reinterpret_cast<volatile uint32_t*>(ws.proxy)[kProxyRecords + threadIdx.x] = served ? nrec[threadIdx.x] : 0u;
@@ -155,13 +137,100 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
       st_release_sys(flag_ptr(st.sync[threadIdx.x], kFlagDispatchStarted, st.rank), tag);
     }
     }  // plain wire
+}
+
+// Routing fused into the dispatch: every team added its token's routes to a histogram in device
+// memory. The block that finishes its tokens last sends the counts message from it and clears
+// it for the dispatch after next. Called by all threads of every block.
+template <int WIRE>
+__device__ void route_finish(const A2AConfig& cfg, const A2ARankState& st, uint32_t* dyn_smem, uint32_t tag,
+                             uint32_t par) {
+  const A2ALocal& ws = st.local;
+  __shared__ uint32_t s_last_router;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last_router = atom_acq_rel_gpu_add(&ws.route_done[par], 1u) == gridDim.x - 1 ? 1u : 0u;
+  }
+  __syncthreads();
+  if (s_last_router == 0) return;
+  uint32_t* hist = dyn_smem;                // [num_experts]
+  uint32_t* nrec = hist + cfg.num_experts;  // [kMaxRanks]
+  for (int i = threadIdx.x; i < cfg.num_experts; i += blockDim.x) {
+    volatile uint32_t* g = &ws.route_hist[par * cfg.num_experts + i];
+    hist[i] = *g;
+    *g = 0;
+  }
+  if (threadIdx.x < kMaxRanks) {
+    volatile uint32_t* g = &ws.route_nrec[par * kMaxRanks + threadIdx.x];
+    nrec[threadIdx.x] = *g;
+    *g = 0;
+  }
+  if (threadIdx.x == 0) ws.route_done[par] = 0;
+  __syncthreads();
+  send_counts<WIRE>(cfg, st, hist, nrec, tag, par);
+}
+
+template <int WIRE>
+__device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st,
+                                    const DispatchSendArgs& a, uint32_t* dyn_smem, const int TEAM) {
+  const A2ALocal& ws = st.local;
+  const Team team(TEAM);
+  const int world = cfg.world;
+  const int K = cfg.topk;
+  const int L = cfg.experts_per_rank;
+  const int my_group = st.rank / cfg.dp_size;
+  const int my_tp = st.rank % cfg.dp_size;
+  const uint32_t epoch = read_epoch(ws, 0);
+  const uint32_t tag = epoch + 1;
+  const uint32_t par = epoch & 1u;
+  trace_mark(cfg, ws, kTraceSendStart);
+
+  int T = a.num_tokens;
+  if (a.bound_m != nullptr) T = min(T, *a.bound_m);
+  T = max(0, min(T, cfg.max_num_tokens));
+
+  // ---- counts message: leaves before any payload, from the block with the fewest tokens ----
+  // Per destination: how many records it will get from this rank and how many of them each
+  // of its experts takes. The "dispatch started" word goes to every rank (also to those this
+  // rank serves no records): a rank that has seen it from everybody knows that all ranks
+  // have left their previous combine, so the combine buffers may be written again.
+  const bool fused_route = a.logits != nullptr;
+  if (fused_route && blockIdx.x == gridDim.x - 1 && threadIdx.x < kMaxRanks) {
+    ws.send_cursor[(par ^ 1u) * kMaxRanks + threadIdx.x] = 0;
+  }
+  if (!fused_route && blockIdx.x == gridDim.x - 1) {
+    uint32_t* hist = dyn_smem;                // [num_experts]
+    uint32_t* nrec = hist + cfg.num_experts;  // [kMaxRanks]
+    for (int i = threadIdx.x; i < cfg.num_experts + kMaxRanks; i += blockDim.x) hist[i] = 0;
+    // the slot cursors of the next dispatch; nobody touches that bank during this launch
+    if (threadIdx.x < kMaxRanks) ws.send_cursor[(par ^ 1u) * kMaxRanks + threadIdx.x] = 0;
+    __syncthreads();
+    for (int t = threadIdx.x; t < T; t += blockDim.x) {
+      uint32_t mask = 0;
+      for (int k = 0; k < K; ++k) {
+        const uint32_t e = a.indices[t * a.indices_stride + k];
+        if (e < static_cast<uint32_t>(cfg.num_experts)) {
+          atomicAdd(&hist[e], 1u);
+          mask |= 1u << (e / L);
+        } else {
+          report(ws, kStatusBadExpertIndex, kPhaseDispatchSend, t, e);
+        }
+      }
+      for (int d = 0; d < world; ++d) {
+        if ((mask >> d) & 1u) atomicAdd(&nrec[d], 1u);
+      }
+    }
+    __syncthreads();
+    send_counts<WIRE>(cfg, st, hist, nrec, tag, par);
     if (cfg.trace && threadIdx.x == 0) ws.trace[kTraceSendSignalled] = globaltimer_ns();
   }
 
   // ---- token loop: one team per token ----
   if constexpr (WIRE == kWireLL) {
     uint8_t* side = reinterpret_cast<uint8_t*>(dyn_smem) + dispatch_stage_offset(cfg);
-    dispatch_send_tokens_ll(cfg, st, a, T, tag, par, TEAM, side);
+    dispatch_send_tokens_ll(cfg, st, a, T, tag, par, TEAM, side,
+                            [&](int t, uint32_t* e, float* w) { route_token(cfg, a, t, e, w); });
   } else {
   __shared__ uint32_t s_idx[kMaxTeams][kMaxTopK];
   __shared__ float s_w[kMaxTeams][kMaxTopK];
@@ -184,7 +253,20 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
         if (i < nvec) v[u] = ld_input_v4(src + 16ull * i);
       }
     }
-    if (team.lane < K) {
+    if (fused_route) {
+      if (team.lane < 32) {
+        uint32_t e;
+        float w;
+        route_token(cfg, a, t, &e, &w);
+        if (team.lane < K) {
+          s_idx[team.in_block][team.lane] = e;
+          s_w[team.in_block][team.lane] = w;
+          const_cast<uint32_t*>(a.indices)[t * a.indices_stride + team.lane] = e;
+          const_cast<float*>(a.weights)[t * a.weights_stride + team.lane] = w;
+          atom_relaxed_gpu_add(&ws.route_hist[par * cfg.num_experts + e], 1u);
+        }
+      }
+    } else if (team.lane < K) {
       s_idx[team.in_block][team.lane] = a.indices[t * a.indices_stride + team.lane];
       s_w[team.in_block][team.lane] = a.weights[t * a.weights_stride + team.lane];
     }
@@ -201,6 +283,7 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
         }
       }
       if (hit) {
+        if (fused_route) atom_relaxed_gpu_add(&ws.route_nrec[par * kMaxRanks + d], 1u);
         my_slot = atom_relaxed_gpu_add(&ws.send_cursor[par * kMaxRanks + d], 1u);
         if (my_slot >= static_cast<uint32_t>(cfg.max_num_tokens)) {
           report(ws, kStatusRecordOverflow, kPhaseDispatchSend, d, my_slot);
@@ -336,6 +419,7 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
     if (t == 0) trace_mark(cfg, ws, kTraceSendPublished);
   }
   }  // plain wire
+  if (fused_route) route_finish<WIRE>(cfg, st, dyn_smem, tag, par);
   proxy_phase_done(cfg, ws, 0, tag);
   trace_mark(cfg, ws, kTraceSendLoopDone);
   trace_max(cfg, ws, kTraceSendLoopLast);

@@ -195,9 +195,11 @@ __device__ __forceinline__ LLSide ll_side(const A2AConfig& cfg, uint8_t* base, i
 
 // Logical layout of a record (16-byte vectors): header | payload | scales, as in the plain
 // format; the tag word of the header is filled in too but nobody waits on it.
+template <typename Route>
 __device__ void dispatch_send_tokens_ll(const A2AConfig& cfg, const A2ARankState& st,
                                         const DispatchSendArgs& a, int T, uint32_t tag, uint32_t par,
-                                        const int TEAM, uint8_t* side_base) {
+                                        const int TEAM, uint8_t* side_base, Route route) {
+  const bool fused_route = a.logits != nullptr;
   const A2ALocal& ws = st.local;
   const Team team(TEAM);
   const int world = cfg.world;
@@ -233,12 +235,28 @@ __device__ void dispatch_send_tokens_ll(const A2AConfig& cfg, const A2ARankState
       }
     }
     // header and scales of the record, as they will appear on the wire
+    if (fused_route && team.lane < 32) {
+      // the routing is made here: top-k on logit + bias, softmax over the chosen logits
+      uint32_t e;
+      float w;
+      route(t, &e, &w);
+      if (team.lane < K) {
+        side.hdr[2 + team.lane] = e;
+        side.hdr[2 + K + team.lane] = __float_as_uint(w);
+        const_cast<uint32_t*>(a.indices)[t * a.indices_stride + team.lane] = e;
+        const_cast<float*>(a.weights)[t * a.weights_stride + team.lane] = w;
+        atom_relaxed_gpu_add(&ws.route_hist[par * cfg.num_experts + e], 1u);
+      }
+    }
     for (uint32_t wi = team.lane; wi < hdr_vecs * 4; wi += TEAM) {
       uint32_t word = 0;
       if (wi == 0) word = tag;
       else if (wi == 1) word = static_cast<uint32_t>(t);
-      else if (wi < 2u + K) word = a.indices[t * a.indices_stride + (wi - 2)];
-      else if (wi < 2u + 2 * K) word = __float_as_uint(a.weights[t * a.weights_stride + (wi - 2 - K)]);
+      else if (wi < 2u + 2 * K) {
+        if (fused_route) continue;
+        word = wi < 2u + K ? a.indices[t * a.indices_stride + (wi - 2)]
+                           : __float_as_uint(a.weights[t * a.weights_stride + (wi - 2 - K)]);
+      }
       side.hdr[wi] = word;
     }
     if (quant) {
@@ -286,6 +304,7 @@ __device__ void dispatch_send_tokens_ll(const A2AConfig& cfg, const A2ARankState
       }
       uint8_t* rec = nullptr;
       if (hit) {
+        if (fused_route) atom_relaxed_gpu_add(&ws.route_nrec[par * kMaxRanks + d], 1u);
         const uint32_t slot = atom_relaxed_gpu_add(&ws.send_cursor[par * kMaxRanks + d], 1u);
         if (slot < static_cast<uint32_t>(cfg.max_num_tokens)) {
           rec = st.recv[d] + cfg.off_drecv + my_group * cfg.drecv_group_stride +

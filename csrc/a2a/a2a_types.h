@@ -178,6 +178,10 @@ struct A2ALocal {
   uint32_t* status;        // [4]
   uint32_t* host_flag;     // pinned host word (device-mapped): failure code, readable by the
                            // host without synchronising the stream
+  // ---- routing fused into the dispatch: counts gathered from all blocks ----
+  uint32_t* route_hist;    // [2][num_experts] routes per expert, by dispatch parity
+  uint32_t* route_nrec;    // [2][kMaxRanks] records per destination rank
+  uint32_t* route_done;    // [2] blocks that have routed all their tokens
   // ---- only used when some rank is outside the NVLink domain ----
   uint32_t* proxy;         // pinned host words (device-mapped), see A2AProxyWord
   uint32_t* send_done;     // [2] blocks that finished the current dispatch / combine send phase
@@ -213,6 +217,14 @@ struct DispatchSendArgs {
   const int32_t* bound_m;
   int32_t num_tokens;
   int32_t quantize;  // 1: x is bf16 and is quantised to e4m3 with 1x128 scales on the fly
+  // Routing fused into the dispatch: when `logits` is set, the team that sends a token first picks
+  // its top-k experts (on logit + bias) and the softmax weights over the chosen logits, writes
+  // them to `indices` / `weights` (outputs then, the combine reads them later) and sends by them.
+  const void* logits;          // [num_tokens, num_experts] fp32 or bf16, nullptr: routing is given
+  int64_t logits_stride;       // elements
+  const float* logits_bias;    // [num_experts] or nullptr
+  int32_t logits_bf16;
+  int32_t pad_;
 };
 
 struct DispatchRecvArgs {

@@ -100,7 +100,9 @@ DispatchSendArgs send_args(int num_tokens, uint64_t x_ptr, uint64_t x_stride,
                            const py::handle& x_scale_ptr, const py::handle& sse,
                            const py::handle& sst, uint64_t indices_ptr, uint64_t indices_stride,
                            uint64_t weights_ptr, uint64_t weights_stride,
-                           const py::handle& bound_m_ptr, bool quantize) {
+                           const py::handle& bound_m_ptr, bool quantize,
+                           const py::handle& logits_ptr = py::none(), int64_t logits_stride = 0,
+                           bool logits_bf16 = false, const py::handle& logits_bias_ptr = py::none()) {
   DispatchSendArgs a{};
   a.num_tokens = num_tokens;
   a.x = reinterpret_cast<const uint8_t*>(x_ptr);
@@ -114,6 +116,10 @@ DispatchSendArgs send_args(int num_tokens, uint64_t x_ptr, uint64_t x_stride,
   a.weights_stride = weights_stride;
   a.bound_m = reinterpret_cast<const int32_t*>(opt_u64(bound_m_ptr));
   a.quantize = quantize ? 1 : 0;
+  a.logits = reinterpret_cast<const void*>(opt_u64(logits_ptr));
+  a.logits_stride = logits_stride;
+  a.logits_bf16 = logits_bf16 ? 1 : 0;
+  a.logits_bias = reinterpret_cast<const float*>(opt_u64(logits_bias_ptr));
   return a;
 }
 
@@ -323,18 +329,22 @@ void bind_a2a(py::module_& m) {
               const py::object& x_scale_ptr, const py::object& sse, const py::object& sst,
               uint64_t indices_ptr, uint64_t indices_stride, uint64_t weights_ptr,
               uint64_t weights_stride, const py::object& bound_m_ptr, uint64_t stream,
-              bool quantize) {
+              bool quantize, const py::object& logits_ptr, int64_t logits_stride, bool logits_bf16,
+              const py::object& logits_bias_ptr) {
              pplx_py::TorchProfilerGuard profiler_range("a2a_dispatch_send");
              const DispatchSendArgs a =
                  send_args(num_tokens, x_ptr, x_stride, x_scale_ptr, sse, sst, indices_ptr,
-                           indices_stride, weights_ptr, weights_stride, bound_m_ptr, quantize);
+                           indices_stride, weights_ptr, weights_stride, bound_m_ptr, quantize, logits_ptr,
+                           logits_stride, logits_bf16, logits_bias_ptr);
              s.ctx->dispatch(&a, nullptr, true, false, as_stream(stream));
              s.after_launch();
            },
            py::arg("num_tokens"), py::arg("x_ptr"), py::arg("x_stride"), py::arg("x_scale_ptr"),
            py::arg("x_scale_stride_elem"), py::arg("x_scale_stride_token"), py::arg("indices_ptr"),
            py::arg("indices_stride"), py::arg("weights_ptr"), py::arg("weights_stride"),
-           py::arg("bound_m_ptr"), py::arg("stream"), py::arg("quantize") = false)
+           py::arg("bound_m_ptr"), py::arg("stream"), py::arg("quantize") = false,
+           py::arg("logits_ptr") = py::none(), py::arg("logits_stride") = 0, py::arg("logits_bf16") = false,
+           py::arg("logits_bias_ptr") = py::none())
       .def("dispatch_recv",
            [](PyA2A& s, uint64_t out_num_tokens_ptr, uint64_t out_x_ptr, uint64_t out_x_stride,
               const py::object& out_x_scale_ptr, const py::object& sse, const py::object& sst,
@@ -355,11 +365,13 @@ void bind_a2a(py::module_& m) {
               uint64_t weights_stride, const py::object& bound_m_ptr, uint64_t out_num_tokens_ptr,
               uint64_t out_x_ptr, uint64_t out_x_stride, const py::object& out_x_scale_ptr,
               const py::object& osse, const py::object& osst, uint64_t stream, uint32_t out_rows,
-              bool quantize) {
+              bool quantize, const py::object& logits_ptr, int64_t logits_stride, bool logits_bf16,
+              const py::object& logits_bias_ptr) {
              pplx_py::TorchProfilerGuard profiler_range("a2a_dispatch");
              const DispatchSendArgs a =
                  send_args(num_tokens, x_ptr, x_stride, x_scale_ptr, sse, sst, indices_ptr,
-                           indices_stride, weights_ptr, weights_stride, bound_m_ptr, quantize);
+                           indices_stride, weights_ptr, weights_stride, bound_m_ptr, quantize, logits_ptr,
+                           logits_stride, logits_bf16, logits_bias_ptr);
              const DispatchRecvArgs r = recv_args(out_num_tokens_ptr, out_x_ptr, out_x_stride,
                                                   out_x_scale_ptr, osse, osst, out_rows);
              s.ctx->dispatch(&a, &r, true, true, as_stream(stream));
@@ -371,7 +383,9 @@ void bind_a2a(py::module_& m) {
            py::arg("bound_m_ptr"), py::arg("out_num_tokens_ptr"), py::arg("out_x_ptr"),
            py::arg("out_x_stride"), py::arg("out_x_scale_ptr"), py::arg("out_x_scale_stride_elem"),
            py::arg("out_x_scale_stride_token"), py::arg("stream"), py::arg("out_rows") = 0,
-           py::arg("quantize") = false, "dispatch_send and dispatch_recv fused into one launch.")
+           py::arg("quantize") = false, py::arg("logits_ptr") = py::none(), py::arg("logits_stride") = 0,
+           py::arg("logits_bf16") = false, py::arg("logits_bias_ptr") = py::none(),
+           "dispatch_send and dispatch_recv fused into one launch.")
       .def("combine_send",
            [](PyA2A& s, uint64_t expert_x_ptr, uint64_t expert_x_stride, uint64_t stream,
               const py::object& expert_y_dtype) {
@@ -448,7 +462,16 @@ void bind_a2a(py::module_& m) {
              if (!send.is_none()) {
                for (const auto& item : send.cast<py::list>()) {
                  const py::tuple t = item.cast<py::tuple>();
-                 PPLX_REQUIRE(t.size() == 12, "send tuple needs 12 entries");
+                 PPLX_REQUIRE(t.size() == 12 || t.size() == 16,
+                              "send tuple needs 12 entries (16 with logits, their stride, bf16 flag and bias)");
+                 if (t.size() == 16) {
+                   sa.push_back(send_args(t[0].cast<int>(), t[1].cast<uint64_t>(), t[2].cast<uint64_t>(), t[3],
+                                          t[4], t[5], t[6].cast<uint64_t>(), t[7].cast<uint64_t>(),
+                                          t[8].cast<uint64_t>(), t[9].cast<uint64_t>(), t[10],
+                                          t[11].cast<bool>(), t[12], t[13].cast<int64_t>(), t[14].cast<bool>(),
+                                          t[15]));
+                   continue;
+                 }
                  sa.push_back(send_args(t[0].cast<int>(), t[1].cast<uint64_t>(),
                                         t[2].cast<uint64_t>(), t[3], t[4], t[5],
                                         t[6].cast<uint64_t>(), t[7].cast<uint64_t>(),

@@ -108,7 +108,11 @@ class LocalAllToAllGroup:
         bound_m: Optional[Sequence[Optional[torch.Tensor]]] = None,
         do_send: bool = True,
         do_recv: bool = True,
+        logits: Optional[Sequence[torch.Tensor]] = None,
+        logits_bias: Optional[Sequence[Optional[torch.Tensor]]] = None,
     ) -> None:
+        """With ``logits`` (one [tokens, experts] tensor per rank) the kernel routes: it fills
+        ``indices`` and ``weights`` instead of reading them."""
         send = recv = None
         if do_send:
             send = []
@@ -124,7 +128,10 @@ class LocalAllToAllGroup:
                     None if xs is None else xs.stride(0),
                     indices[r].data_ptr(), indices[r].stride(0),
                     weights[r].data_ptr(), weights[r].stride(0), bm, quantize,
-                ))
+                ) + (() if logits is None else (
+                    logits[r].data_ptr(), logits[r].stride(0), logits[r].dtype == torch.bfloat16,
+                    None if logits_bias is None or logits_bias[r] is None else logits_bias[r].data_ptr(),
+                )))
         if do_recv:
             recv = []
             for r in range(self.world_size):

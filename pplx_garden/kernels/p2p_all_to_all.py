@@ -253,6 +253,8 @@ class P2PAllToAll(AllToAllKernel):
             except Exception:
                 cpus = []
             self._all_to_all.enable_proxy(self._engine, proxy_peers, 0, cpus[-1] if cpus else -1)
+        self._validate_only = False
+        self._num_experts = num_experts
         self._dispatch_args: dict = {}
         self._combine_args: dict = {}
         self._check_every = int(os.environ.get("PPLX_A2A_CHECK_EVERY", "0"))
@@ -292,10 +294,20 @@ class P2PAllToAll(AllToAllKernel):
         bound_m: Optional[torch.Tensor] = None,
         do_send: bool = True,
         do_recv: bool = True,
+        logits: Optional[torch.Tensor] = None,
+        logits_bias: Optional[torch.Tensor] = None,
     ) -> None:
+        """``logits`` ([tokens, num_experts] fp32 or bf16) fuses the routing into the dispatch: the
+        kernel picks each token's top-k experts on ``logits + logits_bias``, takes the softmax over
+        the chosen logits, WRITES them to ``indices`` / ``weights`` (pass these to ``combine``) and
+        sends by them, all in the team that moves the token."""
         a2a = self._all_to_all
         assert a2a is not None
         assert do_send or do_recv
+        if logits is not None:
+            return self._dispatch_routed(out_expert_num_tokens, out_expert_x, out_expert_x_scale, dp_x,
+                                         dp_x_scale, indices, weights, bound_m, do_send, do_recv, logits,
+                                         logits_bias)
         # A serving loop calls with the same tensors step after step: the checks below run once
         # per distinct set of (address, shape, strides, dtype) and the packed arguments are kept.
         key = (_sig(out_expert_num_tokens), _sig(out_expert_x), _sig(out_expert_x_scale), _sig(dp_x),
@@ -365,10 +377,44 @@ class P2PAllToAll(AllToAllKernel):
         if len(self._dispatch_args) > 64:
             self._dispatch_args.clear()
         self._dispatch_args[key] = (send, recv, out_rows, quantize)
+        if self._validate_only:
+            return
         if do_send and do_recv:
             a2a.dispatch(*send, *recv, stream, out_rows, quantize)
         elif do_send:
             a2a.dispatch_send(*send, stream, quantize)
+        else:
+            a2a.dispatch_recv(*recv, stream, out_rows)
+
+    def _dispatch_routed(self, out_expert_num_tokens, out_expert_x, out_expert_x_scale, dp_x, dp_x_scale,
+                         indices, weights, bound_m, do_send, do_recv, logits, logits_bias) -> None:
+        E = self._num_local_experts * self._world_size
+        T = dp_x.shape[0]
+        assert logits.dim() == 2 and logits.shape[0] == T and logits.shape[1] >= self._num_experts <= E
+        assert logits.stride(1) == 1 and logits.dtype in (torch.float32, torch.bfloat16)
+        if logits_bias is not None:
+            assert logits_bias.dtype == torch.float32 and logits_bias.is_contiguous()
+            assert logits_bias.numel() >= self._num_experts
+        extra = dict(logits_ptr=logits.data_ptr(), logits_stride=logits.stride(0),
+                     logits_bf16=logits.dtype == torch.bfloat16,
+                     logits_bias_ptr=None if logits_bias is None else logits_bias.data_ptr())
+        # the plain path validates everything else and caches the packed arguments
+        key = (_sig(out_expert_num_tokens), _sig(out_expert_x), _sig(out_expert_x_scale), _sig(dp_x),
+               _sig(dp_x_scale), _sig(indices), _sig(weights), _sig(bound_m))
+        if key not in self._dispatch_args:
+            self._validate_only = True
+            try:
+                self.dispatch(out_expert_num_tokens, out_expert_x, out_expert_x_scale, dp_x, dp_x_scale,
+                              indices, weights, bound_m, do_send, do_recv)
+            finally:
+                self._validate_only = False
+        send, recv, out_rows, quantize = self._dispatch_args[key]
+        stream = torch.cuda.current_stream().cuda_stream
+        a2a = self._all_to_all
+        if do_send and do_recv:
+            a2a.dispatch(*send, *recv, stream, out_rows, quantize, **extra)
+        elif do_send:
+            a2a.dispatch_send(*send, stream, quantize, **extra)
         else:
             a2a.dispatch_recv(*recv, stream, out_rows)
 

@@ -98,12 +98,16 @@ class ExpertParallelMoE:
         assert not fused_combine or combine_mode == "per_route"
 
     def forward(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """x bf16 [tokens, hidden]; indices uint32 and weights fp32 [tokens, k]."""
+                out: Optional[torch.Tensor] = None, logits: Optional[torch.Tensor] = None,
+                logits_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x bf16 [tokens, hidden]; indices uint32 and weights fp32 [tokens, k]. With ``logits``
+        ([tokens, experts]) the routing is made inside the dispatch kernel, which fills ``indices``
+        and ``weights``; without, they are inputs."""
         assert x.dtype == torch.bfloat16 and x.shape[1] == self.hidden_dim
         if out is None:
             out = torch.empty_like(x)
-        self.a2a.dispatch(self.expert_num_tokens, self.expert_x, self.expert_x_scale, x, None, indices, weights)
+        self.a2a.dispatch(self.expert_num_tokens, self.expert_x, self.expert_x_scale, x, None, indices, weights,
+                          logits=logits, logits_bias=logits_bias)
         self.gate_up()
         if self.fused_combine:
             self.down_and_send()

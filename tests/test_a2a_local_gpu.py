@@ -372,3 +372,55 @@ def test_barrier_and_rejected_call_leaves_phase_order_intact() -> None:
         group.check()
     finally:
         group.destroy()
+
+
+@pytest.mark.parametrize("wire", ["ll", "plain"])
+@pytest.mark.parametrize("experts,topk,with_bias,bf16_logits", [(64, 4, False, False), (256, 8, True, False),
+                                                                 (288, 6, True, True)])
+def test_routing_fused_into_dispatch(wire: str, experts: int, topk: int, with_bias: bool, bf16_logits: bool) -> None:
+    """dispatch(logits=...) picks the experts itself: the indices and weights it writes equal
+    torch.topk + softmax (choice on logit + bias, weight from the plain logits), and the layer it
+    drives gives the same tokens as routing first and dispatching with the result."""
+    world, tokens, hidden = 4, 40, 256
+    cfg = Cfg(world=world, tokens=tokens, experts=experts, hidden=hidden, topk=topk, in_dtype=torch.bfloat16,
+              out_dtype=torch.bfloat16, wire=wire)
+    device = torch.device("cuda", 0)
+    group = _make_group(cfg, device)
+    try:
+        gen = torch.Generator(device="cpu").manual_seed(5)
+        xs = [torch.randn((tokens, hidden), generator=gen).to(torch.bfloat16).to(device) for _ in range(world)]
+        logits = [torch.randn((tokens, experts), generator=gen) for _ in range(world)]
+        if bf16_logits:
+            logits = [lg.to(torch.bfloat16) for lg in logits]
+        bias = [torch.randn(experts, generator=gen).to(device) if with_bias else None for _ in range(world)]
+        logits = [lg.to(device) for lg in logits]
+        idx = [torch.zeros((tokens, topk), dtype=torch.int32, device=device).view(torch.uint32) for _ in range(world)]
+        wts = [torch.zeros((tokens, topk), dtype=torch.float32, device=device) for _ in range(world)]
+        num, ox, _, out = _outputs(cfg, group, device)
+        group.dispatch(num, ox, None, xs, None, idx, wts, logits=logits, logits_bias=bias if with_bias else None)
+        ys = [act(ox[r], None).to(cfg.out_dtype) for r in range(world)]
+        group.combine(out, idx, wts, ys)
+        torch.cuda.synchronize()
+        group.check()
+        for r in range(world):
+            lg = logits[r].float()
+            key = lg + bias[r] if with_bias else lg
+            want_idx = torch.topk(key, topk, dim=-1).indices
+            want_w = torch.softmax(torch.gather(lg, 1, want_idx), dim=-1)
+            got_idx = idx[r].view(torch.int32).long()
+            assert torch.equal(got_idx.sort(dim=-1).values, want_idx.sort(dim=-1).values), f"rank {r}: experts differ"
+            order_g, order_w = got_idx.argsort(dim=-1), want_idx.argsort(dim=-1)
+            torch.testing.assert_close(torch.gather(wts[r], 1, order_g), torch.gather(want_w, 1, order_w),
+                                       rtol=1e-4, atol=1e-6)
+        # the same layer with the routing given: identical counts and tokens
+        num2, ox2, _, out2 = _outputs(cfg, group, device)
+        group.dispatch(num2, ox2, None, xs, None, idx, wts)
+        ys2 = [act(ox2[r], None).to(cfg.out_dtype) for r in range(world)]
+        group.combine(out2, idx, wts, ys2)
+        torch.cuda.synchronize()
+        group.check()
+        for r in range(world):
+            assert torch.equal(num[r], num2[r])
+            assert torch.equal(out[r], out2[r]), f"rank {r}: fused routing changed the combined tokens"
+    finally:
+        group.destroy()
