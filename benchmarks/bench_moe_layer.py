@@ -126,6 +126,22 @@ def main() -> None:
     layer.check()
     ours_out = out.float().clone()
 
+    # the same layer with the routing made inside the dispatch kernel: one launch instead of two
+    r_idx = torch.zeros((T, K), dtype=torch.int32, device=device).view(torch.uint32)
+    r_w = torch.zeros((T, K), dtype=torch.float32, device=device)
+
+    def r_dispatch() -> None:
+        layer.a2a.dispatch(layer.expert_num_tokens, layer.expert_x, layer.expert_x_scale, x, None, r_idx, r_w,
+                           logits=logits)
+
+    def r_combine() -> None:
+        layer.a2a.combine(out, r_idx, r_w, layer.expert_y)
+
+    routed = timed_phases([("route_and_dispatch", r_dispatch), ("gate_up_swiglu", o_gemm1), ("down", o_gemm2),
+                           ("combine", r_combine)])
+    layer.check()
+    routed["equal_to_unfused"] = bool(torch.equal(out.float(), ours_out))
+
     # the same layer with the down projection writing its rows into the peers' combine buffers
     fused = fused_bulk = None
     if not args.no_fused:
@@ -200,7 +216,7 @@ def main() -> None:
                        "experts": E, "topk": K, "n_gpus": world, "l2": "flushed before each layer",
                        "steps": args.steps, "warmup": args.warmup},
             "unit": "us, max over ranks",
-            "ours": ours, "ours_fused_combine": fused, "ours_fused_combine_bulk": fused_bulk, "library": lib, "max_rel_err_ours_vs_library": max_err,
+            "ours": ours, "ours_route_in_dispatch": routed, "ours_fused_combine": fused, "ours_fused_combine_bulk": fused_bulk, "library": lib, "max_rel_err_ours_vs_library": max_err,
             "speedup_layer": None if lib is None else lib["layer"] / ours["layer"],
             "speedup_layer_fused": None if lib is None or fused is None else lib["layer"] / fused["layer"],
         }))

@@ -793,7 +793,12 @@ void LocalDomain::run_write(const PendingWrite& w, RemoteRegion& rr, std::vector
       a.src_pages = scratch;
       a.dst_pages = scratch + num_pages;
     }
-    PPLX_CUDA_CHECK(launch_paged_copy(a, 0, stream_));
+    // CTAs of the bulk-copy kernel: PPLX_COPY_CTAS overrides the default (a fraction of the SMs)
+    static const int copy_ctas = [] {
+      const char* env = std::getenv("PPLX_COPY_CTAS");
+      return env != nullptr ? std::atoi(env) : 0;
+    }();
+    PPLX_CUDA_CHECK(launch_paged_copy(a, copy_ctas, stream_));
   } else {
     // one side is host memory of this process: let the copy engine move each page
     for (size_t i = 0; i < num_pages; ++i) {

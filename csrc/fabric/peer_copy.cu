@@ -10,6 +10,7 @@ namespace {
 constexpr uint32_t kChunkBytes = 32 * 1024;  // one bulk copy
 constexpr int kStages = 4;                   // chunks in flight per CTA (128 KiB of smem)
 constexpr int kBulkThreads = 32;
+constexpr uint64_t kSmallPageBytes = 16 * 1024;  // at or below: one warp per page (paged_copy_rows_kernel)
 
 __device__ __forceinline__ uint64_t page_offset(const uint32_t* pages, uint32_t i, uint64_t stride,
                                                 uint64_t offset) {
@@ -112,6 +113,34 @@ __global__ void __launch_bounds__(256) paged_copy_simt_kernel(const __grid_const
   }
 }
 
+// Many small pages (rows of a weight shard, short KV pages): one warp per page, 16-byte vectors,
+// four loads in flight per lane, as many CTAs as it takes to have every SM storing. A page this
+// small is not worth a bulk-copy descriptor and a shared-memory round trip per page; what counts
+// is how many independent pages are in flight.
+constexpr int kRowsWarps = 8;
+
+__global__ void __launch_bounds__(kRowsWarps * 32) paged_copy_rows_kernel(const __grid_constant__ PagedCopyArgs a) {
+  const uint32_t lane = threadIdx.x & 31u;
+  const uint64_t warp = static_cast<uint64_t>(blockIdx.x) * kRowsWarps + (threadIdx.x >> 5);
+  const uint64_t warps = static_cast<uint64_t>(gridDim.x) * kRowsWarps;
+  const uint32_t nvec = static_cast<uint32_t>(a.length / 16);
+  for (uint64_t page = warp; page < a.num_pages; page += warps) {
+    const uint8_t* src = a.src_base + page_offset(a.src_pages, static_cast<uint32_t>(page), a.src_stride, a.src_offset);
+    uint8_t* dst = a.dst_base + page_offset(a.dst_pages, static_cast<uint32_t>(page), a.dst_stride, a.dst_offset);
+    for (uint32_t i0 = lane; i0 < nvec; i0 += 128) {
+      Vec16 v[4];
+      #pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (i0 + 32 * u < nvec) v[u] = ld_input_v4(src + 16ull * (i0 + 32 * u));
+      }
+      #pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (i0 + 32 * u < nvec) st_stream_v4(dst + 16ull * (i0 + 32 * u), v[u]);
+      }
+    }
+  }
+}
+
 }  // namespace
 
 cudaError_t launch_paged_copy(const PagedCopyArgs& args, int max_ctas, cudaStream_t stream) {
@@ -122,7 +151,14 @@ cudaError_t launch_paged_copy(const PagedCopyArgs& args, int max_ctas, cudaStrea
   const int grid = static_cast<int>(std::min<uint64_t>(total, static_cast<uint64_t>(max_ctas)));
   const uint64_t all = reinterpret_cast<uintptr_t>(args.src_base) | reinterpret_cast<uintptr_t>(args.dst_base) |
                        args.src_stride | args.dst_stride | args.src_offset | args.dst_offset | args.length;
-  if ((all & 15u) == 0) {
+  if ((all & 15u) == 0 && args.length <= kSmallPageBytes && args.num_pages >= 64) {
+    int sms = 0, device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const uint64_t wanted = (args.num_pages + kRowsWarps - 1) / kRowsWarps;
+    const int rows_grid = static_cast<int>(std::min<uint64_t>(wanted, static_cast<uint64_t>(std::max(sms, 1)) * 4));
+    paged_copy_rows_kernel<<<rows_grid, kRowsWarps * 32, 0, stream>>>(args);
+  } else if ((all & 15u) == 0) {
     const size_t smem = static_cast<size_t>(kStages) * kChunkBytes;
     // per device and cheap: set it on every launch rather than tracking devices
     cudaError_t e = cudaFuncSetAttribute(paged_copy_bulk_kernel,
@@ -147,6 +183,7 @@ cudaError_t warm_up_paged_copy(cudaStream_t stream) {
   if (e != cudaSuccess) return e;
   paged_copy_bulk_kernel<<<1, kBulkThreads, smem, stream>>>(args);
   paged_copy_simt_kernel<<<1, 256, 0, stream>>>(args);
+  paged_copy_rows_kernel<<<1, kRowsWarps * 32, 0, stream>>>(args);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   return cudaStreamSynchronize(stream);

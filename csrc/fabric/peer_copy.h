@@ -23,8 +23,9 @@ struct PagedCopyArgs {
   uint32_t* error_flag;         // device word set to non-zero if a bounded wait ran out
 };
 
-// Launches the copy on `stream`. Uses the bulk-copy (TMA) engine when addresses, strides
-// and the length are multiples of 16 bytes, a vectorised SIMT loop otherwise.
+// Launches the copy on `stream`. With addresses, strides and length all multiples of 16 bytes:
+// pages of up to 16 KiB (64 or more of them) are copied one warp per page on every SM, larger
+// ones through the bulk-copy (TMA) engine with a few CTAs; otherwise a byte-wise SIMT loop.
 // `max_ctas` <= 0 picks a default that saturates NVLink with a fraction of the SMs.
 cudaError_t launch_paged_copy(const PagedCopyArgs& args, int max_ctas, cudaStream_t stream);
 
