@@ -21,6 +21,8 @@ class AllToAllContext:
         num_blocks: int = 0,
         num_sms: int = 148,
         virtual_ranks: int = 1,
+        wire: str | int | None = None,
+        node_mask: int = 0,
     ) -> dict[str, int]: ...
     @staticmethod
     def create(
@@ -58,6 +60,8 @@ class AllToAllContext:
         combine_mode: str | int | None = None,
         num_blocks: int = 0,
         wait_limit_ms: int = 0,
+        wire: str | int | None = None,
+        node_mask: int = 0,
     ) -> AllToAllContext: ...
     def config(self) -> dict[str, int]: ...
     def dispatch_send(
@@ -75,6 +79,10 @@ class AllToAllContext:
         bound_m_ptr: int | None,
         stream: int,
         quantize: bool = False,
+        logits_ptr: int | None = None,
+        logits_stride: int = 0,
+        logits_bf16: bool = False,
+        logits_bias_ptr: int | None = None,
     ) -> None: ...
     def dispatch_recv(
         self,
@@ -95,6 +103,7 @@ class AllToAllContext:
         stream: int,
         expert_y_dtype: torch.dtype | None = None,
     ) -> None: ...
+    def combine_send_external(self) -> list[tuple]: ...
     def combine_recv(
         self,
         num_tokens: int,
@@ -116,6 +125,15 @@ class AllToAllContext:
         self, send: list[tuple] | None, recv: list[tuple] | None, expert_y_dtype: torch.dtype, stream: int
     ) -> None: ...
     def barrier(self, stream: int) -> None: ...
+    def enable_proxy(
+        self,
+        transfer_engine: Any,
+        peers: list[tuple[int, Any, Any]],
+        local_rank: int = 0,
+        worker_cpu: int = -1,
+    ) -> None: ...
+    def proxy_counters(self, local_rank: int = 0) -> tuple[int, int]: ...
+    def trace(self, local_rank: int = 0) -> list[int]: ...
     def failed(self) -> bool: ...
     def check(self) -> None: ...
     def status(self, local_rank: int = 0) -> tuple[int, int, int, int, str]: ...
