@@ -44,8 +44,13 @@ def main() -> None:
     ap.add_argument("--copies", type=int, default=4, help="operand sets rotated to defeat L2")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tile-rows", type=int, default=0, help="256 = CTA pairs, 128 = single CTAs, 0 = automatic")
+    ap.add_argument("--num-ctas", type=int, default=0, help="CTAs to launch (0 = one per SM)")
+    ap.add_argument("--scales", choices=["fp32", "pow2"], default="pow2",
+                    help="pow2: power-of-two scales applied by the tensor cores (block-scaled MMA); "
+                         "fp32: any scales, folded in by the epilogue per K block")
     ap.add_argument("--ablate", action="store_true", help="also time the kernel with one pipeline stage removed")
     args = ap.parse_args()
+    pow2 = args.scales == "pow2"
     dev = torch.device("cuda", 0)
     E, M, H, I = args.experts, args.rows_per_expert, args.hidden, args.intermediate
     rows = E * M
@@ -56,9 +61,9 @@ def main() -> None:
     sets = []
     for c in range(args.copies):
         g = torch.Generator(device="cpu").manual_seed(c)
-        x, xs = quantize_1x128(torch.randn(rows, H, generator=g))
-        w13, w13s = quantize_128x128(torch.randn(E, 2 * I, H, generator=g) * H ** -0.5)
-        w2, w2s = quantize_128x128(torch.randn(E, H, I, generator=g) * I ** -0.5)
+        x, xs = quantize_1x128(torch.randn(rows, H, generator=g), pow2=pow2)
+        w13, w13s = quantize_128x128(torch.randn(E, 2 * I, H, generator=g) * H ** -0.5, pow2=pow2)
+        w2, w2s = quantize_128x128(torch.randn(E, H, I, generator=g) * I ** -0.5, pow2=pow2)
         sets.append([t.to(dev) for t in (x, xs, w13, w13s, w2, w2s)])
     act = torch.zeros(rows, I, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
     act_s = torch.zeros(rows, I // 128, dtype=torch.float32, device=dev)
@@ -70,12 +75,13 @@ def main() -> None:
         x, xs, w13, w13s, _, _ = sets[state["i"] % args.copies]
         state["i"] += 1
         grouped_fp8_gemm(x, xs, w13, w13s, cnt, act, act_s, mode=MODE_SWIGLU_QUANT, error_flag=flag,
-                         tile_rows=args.tile_rows)
+                         tile_rows=args.tile_rows, scale_format=args.scales, num_ctas=args.num_ctas)
 
     def gemm2() -> None:
         _, _, _, _, w2, w2s = sets[state["i"] % args.copies]
         state["i"] += 1
-        grouped_fp8_gemm(act, act_s, w2, w2s, cnt, y, mode=MODE_BF16, error_flag=flag, tile_rows=args.tile_rows)
+        grouped_fp8_gemm(act, act_s, w2, w2s, cnt, y, mode=MODE_BF16, error_flag=flag, tile_rows=args.tile_rows,
+                         scale_format=args.scales, num_ctas=args.num_ctas)
 
     def both() -> None:
         gemm1()
@@ -86,7 +92,7 @@ def main() -> None:
     # where the pipeline waits (one instrumented launch per GEMM)
     waits = {}
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    for name, run in (("gate_up", 0), ("down", 1)):
+    for name, run in (("gate_up", 0), ("down", 1)) if not pow2 else ():
         wc = torch.zeros((sms, 4), dtype=torch.int64, device=dev)
         x, xs, w13, w13s, w2, w2s = sets[0]
         torch.cuda.synchronize()
@@ -104,7 +110,7 @@ def main() -> None:
             "epilogue_for_partial_sums": m[3]}}
     # what the remaining stages sustain with one stage removed (results are garbage, timing only)
     ablation = {}
-    if args.ablate:
+    if args.ablate and not pow2:
         for label, skip in (("no_epilogue_reads", 1), ("no_mma", 2), ("no_tma", 4), ("tma_only", 3), ("mma_only", 5)):
             def g1() -> None:
                 x, xs, w13, w13s, _, _ = sets[state["i"] % args.copies]
@@ -121,6 +127,7 @@ def main() -> None:
     f1, f2 = 2.0 * rows * 2 * I * H, 2.0 * rows * H * I
     out = {
         "shape": {"experts": E, "rows_per_expert": M, "hidden": H, "intermediate": I},
+        "scales": args.scales, "num_ctas": args.num_ctas,
         "gate_up_swiglu_us": t1, "gate_up_tflops": f1 / t1 / 1e6,
         "down_us": t2, "down_tflops": f2 / t2 / 1e6,
         "ffn_us": t12, "ffn_tflops": (f1 + f2) / t12 / 1e6,

@@ -131,8 +131,9 @@ __device__ __forceinline__ void trace_max(const A2AConfig& cfg, const A2ALocal& 
 
 
 // Quantises 16 consecutive bf16 values (two 16-byte vectors) held by one lane to e4m3;
-// eight neighbouring lanes share one 1x128 block and therefore one scale.
-__device__ __forceinline__ Vec16 quantize16(const Vec16& a, const Vec16& b, float* scale_out) {
+// eight neighbouring lanes share one 1x128 block and therefore one scale. With `pow2` the scale is
+// rounded up to a power of two (what the block-scaled MMA of the expert GEMM can apply itself).
+__device__ __forceinline__ Vec16 quantize16(const Vec16& a, const Vec16& b, float* scale_out, bool pow2) {
   const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
   const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
   float2 f[8];
@@ -147,7 +148,8 @@ __device__ __forceinline__ Vec16 quantize16(const Vec16& a, const Vec16& b, floa
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
   amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-  const float scale = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+  float scale = fmaxf(amax, 1e-10f) * (1.0f / 448.0f);
+  if (pow2) scale = __uint_as_float((__float_as_uint(scale) + 0x007fffffu) & 0x7f800000u);
   const float inv = 1.0f / scale;
   *scale_out = scale;
   Vec16 out;

@@ -375,7 +375,7 @@ __device__ void dispatch_send_phase(const A2AConfig& cfg, const A2ARankState& st
           hi = ld_input_v4(src + 32ull * i + 16);
         }
         float scale;
-        const Vec16 q = quantize16(lo, hi, &scale);
+        const Vec16 q = quantize16(lo, hi, &scale, a.quantize == 2);
         if (valid) {
           #pragma unroll
           for (int d = 0; d < kMaxRanks; ++d) {

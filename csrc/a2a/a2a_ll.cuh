@@ -272,7 +272,7 @@ __device__ void dispatch_send_tokens_ll(const A2AConfig& cfg, const A2ARankState
           hi = ld_input_v4(src + 32ull * i + 16);
         }
         float scale;
-        const Vec16 q = quantize16(lo, hi, &scale);
+        const Vec16 q = quantize16(lo, hi, &scale, a.quantize == 2);
         if (valid) {
           *reinterpret_cast<Vec16*>(side.payload + 16ull * i) = q;
           if ((i & 7u) == 0) *reinterpret_cast<float*>(side.scales + 4 * (i >> 3)) = scale;

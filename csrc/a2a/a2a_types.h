@@ -216,7 +216,8 @@ struct DispatchSendArgs {
   uint64_t weights_stride;  // elements
   const int32_t* bound_m;
   int32_t num_tokens;
-  int32_t quantize;  // 1: x is bf16 and is quantised to e4m3 with 1x128 scales on the fly
+  int32_t quantize;  // 1: x is bf16 and is quantised to e4m3 with 1x128 scales on the fly; 2: the same with
+                     // scales rounded up to powers of two
   // Routing fused into the dispatch: when `logits` is set, the team that sends a token first picks
   // its top-k experts (on logit + bias) and the softmax weights over the chosen logits, writes
   // them to `indices` / `weights` (outputs then, the combine reads them later) and sends by them.

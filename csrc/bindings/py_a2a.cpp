@@ -100,7 +100,7 @@ DispatchSendArgs send_args(int num_tokens, uint64_t x_ptr, uint64_t x_stride,
                            const py::handle& x_scale_ptr, const py::handle& sse,
                            const py::handle& sst, uint64_t indices_ptr, uint64_t indices_stride,
                            uint64_t weights_ptr, uint64_t weights_stride,
-                           const py::handle& bound_m_ptr, bool quantize,
+                           const py::handle& bound_m_ptr, int quantize,
                            const py::handle& logits_ptr = py::none(), int64_t logits_stride = 0,
                            bool logits_bf16 = false, const py::handle& logits_bias_ptr = py::none()) {
   DispatchSendArgs a{};
@@ -115,7 +115,8 @@ DispatchSendArgs send_args(int num_tokens, uint64_t x_ptr, uint64_t x_stride,
   a.weights = reinterpret_cast<const float*>(weights_ptr);
   a.weights_stride = weights_stride;
   a.bound_m = reinterpret_cast<const int32_t*>(opt_u64(bound_m_ptr));
-  a.quantize = quantize ? 1 : 0;
+  PPLX_REQUIRE(quantize >= 0 && quantize <= 2, "quantize is 0 (no), 1 (fp32 scales) or 2 (power-of-two scales)");
+  a.quantize = quantize;
   a.logits = reinterpret_cast<const void*>(opt_u64(logits_ptr));
   a.logits_stride = logits_stride;
   a.logits_bf16 = logits_bf16 ? 1 : 0;
@@ -329,7 +330,7 @@ void bind_a2a(py::module_& m) {
               const py::object& x_scale_ptr, const py::object& sse, const py::object& sst,
               uint64_t indices_ptr, uint64_t indices_stride, uint64_t weights_ptr,
               uint64_t weights_stride, const py::object& bound_m_ptr, uint64_t stream,
-              bool quantize, const py::object& logits_ptr, int64_t logits_stride, bool logits_bf16,
+              int quantize, const py::object& logits_ptr, int64_t logits_stride, bool logits_bf16,
               const py::object& logits_bias_ptr) {
              pplx_py::TorchProfilerGuard profiler_range("a2a_dispatch_send");
              const DispatchSendArgs a =
@@ -342,7 +343,7 @@ void bind_a2a(py::module_& m) {
            py::arg("num_tokens"), py::arg("x_ptr"), py::arg("x_stride"), py::arg("x_scale_ptr"),
            py::arg("x_scale_stride_elem"), py::arg("x_scale_stride_token"), py::arg("indices_ptr"),
            py::arg("indices_stride"), py::arg("weights_ptr"), py::arg("weights_stride"),
-           py::arg("bound_m_ptr"), py::arg("stream"), py::arg("quantize") = false,
+           py::arg("bound_m_ptr"), py::arg("stream"), py::arg("quantize") = 0,
            py::arg("logits_ptr") = py::none(), py::arg("logits_stride") = 0, py::arg("logits_bf16") = false,
            py::arg("logits_bias_ptr") = py::none())
       .def("dispatch_recv",
@@ -365,7 +366,7 @@ void bind_a2a(py::module_& m) {
               uint64_t weights_stride, const py::object& bound_m_ptr, uint64_t out_num_tokens_ptr,
               uint64_t out_x_ptr, uint64_t out_x_stride, const py::object& out_x_scale_ptr,
               const py::object& osse, const py::object& osst, uint64_t stream, uint32_t out_rows,
-              bool quantize, const py::object& logits_ptr, int64_t logits_stride, bool logits_bf16,
+              int quantize, const py::object& logits_ptr, int64_t logits_stride, bool logits_bf16,
               const py::object& logits_bias_ptr) {
              pplx_py::TorchProfilerGuard profiler_range("a2a_dispatch");
              const DispatchSendArgs a =
@@ -383,7 +384,7 @@ void bind_a2a(py::module_& m) {
            py::arg("bound_m_ptr"), py::arg("out_num_tokens_ptr"), py::arg("out_x_ptr"),
            py::arg("out_x_stride"), py::arg("out_x_scale_ptr"), py::arg("out_x_scale_stride_elem"),
            py::arg("out_x_scale_stride_token"), py::arg("stream"), py::arg("out_rows") = 0,
-           py::arg("quantize") = false, py::arg("logits_ptr") = py::none(), py::arg("logits_stride") = 0,
+           py::arg("quantize") = 0, py::arg("logits_ptr") = py::none(), py::arg("logits_stride") = 0,
            py::arg("logits_bf16") = false, py::arg("logits_bias_ptr") = py::none(),
            "dispatch_send and dispatch_recv fused into one launch.")
       .def("combine_send",
@@ -468,7 +469,7 @@ void bind_a2a(py::module_& m) {
                    sa.push_back(send_args(t[0].cast<int>(), t[1].cast<uint64_t>(), t[2].cast<uint64_t>(), t[3],
                                           t[4], t[5], t[6].cast<uint64_t>(), t[7].cast<uint64_t>(),
                                           t[8].cast<uint64_t>(), t[9].cast<uint64_t>(), t[10],
-                                          t[11].cast<bool>(), t[12], t[13].cast<int64_t>(), t[14].cast<bool>(),
+                                          t[11].cast<int>(), t[12], t[13].cast<int64_t>(), t[14].cast<bool>(),
                                           t[15]));
                    continue;
                  }
@@ -476,7 +477,7 @@ void bind_a2a(py::module_& m) {
                                         t[2].cast<uint64_t>(), t[3], t[4], t[5],
                                         t[6].cast<uint64_t>(), t[7].cast<uint64_t>(),
                                         t[8].cast<uint64_t>(), t[9].cast<uint64_t>(), t[10],
-                                        t[11].cast<bool>()));
+                                        t[11].cast<int>()));
                }
                PPLX_REQUIRE(static_cast<int>(sa.size()) == s.ctx->num_local_ranks(),
                             "one send tuple per local rank is required");

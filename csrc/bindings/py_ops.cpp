@@ -48,7 +48,7 @@ void bind_ops(py::module_& m) {
          uint64_t b, uint64_t b_scale, uint64_t expert_num_tokens, uint64_t out, int64_t out_stride,
          uint64_t out_scale, int64_t out_scale_stride_row, uint64_t error_flag, int num_experts, int N, int K,
          int expert_padding, int max_rows, int mode, int num_ctas, uint64_t stream, uint64_t wait_cycles,
-         int debug_skip, uint64_t trace, const py::object& scatter, int tile_rows) {
+         int debug_skip, uint64_t trace, const py::object& scatter, int tile_rows, int scale_format) {
         GroupedGemmParams p;
         p.a = reinterpret_cast<const void*>(a);
         p.a_stride = a_stride;
@@ -73,6 +73,7 @@ void bind_ops(py::module_& m) {
         p.wait_cycles = reinterpret_cast<unsigned long long*>(wait_cycles);
         p.debug_skip = debug_skip;
         p.tile_rows = tile_rows;
+        p.scale_format = scale_format;
         p.trace = reinterpret_cast<long long*>(trace);
         if (!scatter.is_none()) {
           // the tuple AllToAllContext.combine_send_external() returns for this rank
@@ -97,7 +98,7 @@ void bind_ops(py::module_& m) {
           sc.done_counter = reinterpret_cast<uint32_t*>(t[7].cast<uint64_t>());
           sc.status = reinterpret_cast<const uint32_t*>(t[8].cast<uint64_t>());
         }
-        if (p.wait_cycles != nullptr || p.trace != nullptr || p.debug_skip != 0) {
+        if (p.scale_format == kScalesFp32 && (p.wait_cycles != nullptr || p.trace != nullptr || p.debug_skip != 0)) {
           grouped_fp8_gemm_profiled(p, reinterpret_cast<cudaStream_t>(stream));
         } else {
           grouped_fp8_gemm(p, reinterpret_cast<cudaStream_t>(stream));
@@ -109,5 +110,5 @@ void bind_ops(py::module_& m) {
       py::arg("num_experts"), py::arg("N"), py::arg("K"), py::arg("expert_padding"), py::arg("max_rows"),
       py::arg("mode"), py::arg("num_ctas"), py::arg("stream"), py::arg("wait_cycles") = 0,
       py::arg("debug_skip") = 0, py::arg("trace") = 0,
-      py::arg("scatter") = py::none(), py::arg("tile_rows") = 0);
+      py::arg("scatter") = py::none(), py::arg("tile_rows") = 0, py::arg("scale_format") = 0);
 }

@@ -17,6 +17,18 @@ enum GroupedGemmMode : int {
   kBf16Scatter = 2,
 };
 
+// How the scales of A and B are applied.
+enum GroupedGemmScales : int {
+  // any fp32 value; the epilogue reads every K block's partial sums out of tensor memory and
+  // folds them with a_scale * b_scale (the tensor cores wait for it)
+  kScalesFp32 = 0,
+  // every scale is a power of two (mantissa bits zero; what a UE8M0 scale can express). The kernel
+  // takes the exponents and the tensor cores apply them (tcgen05.mma kind::mxf8f6f4.block_scale),
+  // so the sum over K stays in tensor memory; the SwiGLU epilogue then writes power-of-two scales
+  // too. A scale with mantissa bits set is truncated to the power of two below it.
+  kScalesPow2 = 1,
+};
+
 // Where the rows of a kBf16Scatter GEMM go. Filled by A2AContext::combine_scatter_begin().
 struct CombineScatter {
   static constexpr int kMaxPeers = 8;
@@ -70,10 +82,14 @@ struct GroupedGemmParams {
   // bit 3: every MMA is issued twice. Timing the kernel with
   // one stage removed shows what the other stages can sustain.
   int debug_skip = 0;
+  int scale_format = kScalesFp32;  // GroupedGemmScales
   CombineScatter scatter;          // kBf16Scatter only
 };
 
 void grouped_fp8_gemm(const GroupedGemmParams& params, cudaStream_t stream);
+
+// The kScalesPow2 kernel (grouped_gemm_mx.cu); grouped_fp8_gemm() forwards to it.
+void grouped_fp8_gemm_mx(const GroupedGemmParams& params, cudaStream_t stream);
 
 // The same kernel built with its profiling aids (wait_cycles, trace, debug_skip); the regular
 // entry point ignores those three fields.

@@ -193,4 +193,104 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" : : "r"(bar_cluster_addr) : "memory");
 }
 
+// ---- block-scaled MMA (kind::mxf8f6f4.block_scale): one UE8M0 scale per operand row and 32
+// elements of K, applied inside the tensor core. The scales live in tensor memory: 32 lanes x one
+// 32-bit column hold the scales of 32 rows (row r of a 128-row block -> lane r % 32, column r / 32),
+// repeated in each of the four lane quarters; the four bytes of a word are four scales along K,
+// and the instruction descriptor's scale-factor id says which byte this MMA uses.
+
+// Instruction descriptor: e4m3 x e4m3 -> f32, both K-major, UE8M0 scales; `sf_id` selects the
+// byte of the scale words for A and for B.
+__host__ __device__ constexpr uint32_t idesc_mx_e4m3_ue8m0(int m, int n, uint32_t sf_id = 0) {
+  return (sf_id << 4)                              // B scale-factor id
+         | (0u << 7) | (0u << 10)                  // A, B format e4m3
+         | (0u << 15) | (0u << 16)                 // A, B K-major
+         | (static_cast<uint32_t>(n >> 3) << 17)   // N / 8
+         | (1u << 23)                              // scale format UE8M0
+         | (static_cast<uint32_t>(m >> 4) << 24)   // M / 16
+         | (sf_id << 29);                          // A scale-factor id
+}
+
+// Shared-memory descriptor of a block of scale words laid out for tcgen05.cp 32x128b: 32 rows of
+// 16 bytes, rows 16 bytes apart (K-major, no swizzle: 8-row groups 128 bytes apart).
+__device__ __forceinline__ uint64_t smem_desc_sf(const void* smem_block) {
+  const uint32_t addr = smem_u32(smem_block);
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);
+  d |= static_cast<uint64_t>(128 >> 4) << 32;         // stride byte offset: 8 rows x 16 B
+  d |= static_cast<uint64_t>(1) << 46;                // descriptor version (Blackwell)
+  return d;
+}
+
+// Copies 32 rows x 16 bytes from shared memory into 4 tensor-memory columns of all four lane
+// quarters (what the block-scaled MMA reads its scales from). Asynchronous, ordered with the
+// tcgen05.mma and tcgen05.commit instructions of the issuing thread. With kCtas == 2 the copy
+// happens in both CTAs of the pair, each from its own shared memory at the same offset.
+template <int kCtas>
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  if constexpr (kCtas == 2) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" : : "r"(taddr), "l"(sdesc) : "memory");
+  } else {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" : : "r"(taddr), "l"(sdesc) : "memory");
+  }
+}
+
+// D[tmem] (+)= (A * 2^sfa) (B * 2^sfb)^T, one thread issues. M 128 (one CTA) or 256 (a pair).
+template <int kCtas>
+__device__ __forceinline__ void mma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  if constexpr (kCtas == 2) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+        "}\n"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+        "}\n"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+  }
+}
+
+// Arrival that publishes this thread's earlier shared-memory writes to the other CTA of the
+// cluster (cluster-scope release), and the matching bounded wait (cluster-scope acquire).
+__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" : : "r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_acquire_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_timed_acquire_cluster(uint64_t* bar, uint32_t parity, uint64_t timeout_ns) {
+  if (mbar_try_wait_acquire_cluster(bar, parity)) return true;
+  const long long start = clock64();
+  const long long limit = static_cast<long long>(timeout_ns) * 2;
+  for (;;) {
+    #pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      if (mbar_try_wait_acquire_cluster(bar, parity)) return true;
+    }
+    if (clock64() - start > limit) return false;
+  }
+}
+
 }  // namespace pplx::tc

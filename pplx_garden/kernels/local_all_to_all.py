@@ -41,11 +41,13 @@ class LocalAllToAllGroup:
         num_blocks: int = 0,
         wait_limit_ms: int = 0,
         wire: Optional[str] = None,
+        pow2_scales: bool = False,
     ) -> None:
         device = torch.device(device)
         if device.index is None:
             device = torch.device("cuda", torch.cuda.current_device())
         self.world_size = world_size
+        self.quantize_mode = 2 if pow2_scales else 1
         self.dp_size = dp_size
         self.device = device
         self.hidden_dim = hidden_dim
@@ -118,7 +120,7 @@ class LocalAllToAllGroup:
             send = []
             for r in range(self.world_size):
                 x = dp_x[r]
-                quantize = x.dtype != self.in_dtype
+                quantize = self.quantize_mode if x.dtype != self.in_dtype else 0
                 xs = None if dp_x_scale is None else dp_x_scale[r]
                 bm = None if bound_m is None or bound_m[r] is None else bound_m[r].data_ptr()
                 send.append((

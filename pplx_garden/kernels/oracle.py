@@ -128,13 +128,16 @@ def expected_combine(
     return out
 
 
-def quantize_1x128(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+def quantize_1x128(x: torch.Tensor, pow2: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """float32 reference of block-scaled e4m3 quantisation: one scale per 128 contiguous
-    elements, ``scale = max(amax, 1e-10) / 448``, values rounded to nearest-even and
-    saturated. Returns (e4m3 tensor, float32 scales [tokens, hidden / 128])."""
+    elements, ``scale = max(amax, 1e-10) / 448`` (rounded up to a power of two with ``pow2``),
+    values rounded to nearest-even and saturated. Returns (e4m3 tensor, float32 scales
+    [tokens, hidden / 128])."""
     t, h = x.shape
     blocks = x.to(torch.float32).reshape(t, h // 128, 128)
     amax = blocks.abs().amax(dim=-1).clamp_min(1e-10)
     scale = amax * (1.0 / 448.0)
+    if pow2:
+        scale = ((scale.contiguous().view(torch.int32) + 0x007FFFFF) & 0x7F800000).view(torch.float32)
     q = (blocks * (1.0 / scale).unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
     return q.reshape(t, h), scale

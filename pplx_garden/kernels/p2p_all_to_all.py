@@ -95,6 +95,7 @@ class P2PAllToAll(AllToAllKernel):
         num_blocks: int = 0,
         wait_limit_ms: int = 0,
         wire: Optional[str] = None,
+        pow2_scales: bool = False,
     ) -> None:
         device = torch.device(device)
         if device.type != "cuda":
@@ -107,6 +108,9 @@ class P2PAllToAll(AllToAllKernel):
             raise ValueError("only float32 scales are supported")
 
         self._hidden_dim = hidden_dim
+        # scales of the quantisation fused into dispatch are rounded up to powers of two
+        # (for grouped_fp8_gemm(..., scale_format="pow2"))
+        self._quantize_mode = 2 if pow2_scales else 1
         self._hidden_dim_scale = hidden_dim_scale
         self._num_experts_per_token = num_experts_per_token
         self._in_dtype = in_dtype
@@ -342,14 +346,14 @@ class P2PAllToAll(AllToAllKernel):
             out_scale = (None, None, None)
 
         assert dp_x.shape == (num_tokens, H) and dp_x.stride(1) == 1
-        quantize = False
+        quantize = 0
         if dp_x.dtype != self._in_dtype:
             # fused quantisation: bf16 in, e4m3 + 1x128 fp32 scales on the wire
             assert dp_x.dtype == torch.bfloat16 and self._in_dtype == torch.float8_e4m3fn, (
                 f"dp_x is {dp_x.dtype}, the context was built for {self._in_dtype}")
             assert dp_x_scale is None and self._hidden_dim_scale == H // 128
             assert out_expert_x_scale is not None
-            quantize = True
+            quantize = self._quantize_mode
         if dp_x_scale is not None:
             assert self._scale_dtype is not None and self._hidden_dim_scale is not None
             assert out_expert_x_scale is not None

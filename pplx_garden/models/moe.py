@@ -54,8 +54,15 @@ class ExpertParallelMoE:
         combine_mode: str = "per_route",
         fused_combine: bool = False,
         fused_bulk: bool = False,
+        scale_format: str = "pow2",
     ) -> None:
         assert hidden_dim % 256 == 0 and intermediate_dim % 128 == 0
+        assert scale_format in ("pow2", "fp32")
+        # "pow2": every scale (weights, dispatch's quantisation, the SwiGLU epilogue's) is a power of two
+        # and the tensor cores apply them (block-scaled MMA); "fp32": any scale, folded in by the
+        # GEMM's epilogue per K block, which is slower
+        self.scale_format = scale_format
+        pow2 = scale_format == "pow2"
         self.hidden_dim = hidden_dim
         self.intermediate_dim = intermediate_dim
         self.topk = num_experts_per_token
@@ -68,8 +75,8 @@ class ExpertParallelMoE:
             gen = torch.Generator(device="cpu").manual_seed(seed + 1000 * rank)
             w13 = torch.randn((L, 2 * intermediate_dim, hidden_dim), generator=gen) * init_std
             w2 = torch.randn((L, hidden_dim, intermediate_dim), generator=gen) * init_std
-        self.w13, self.w13_scale = (t.to(self.device) for t in quantize_128x128(w13))
-        self.w2, self.w2_scale = (t.to(self.device) for t in quantize_128x128(w2))
+        self.w13, self.w13_scale = (t.to(self.device) for t in quantize_128x128(w13, pow2=pow2))
+        self.w2, self.w2_scale = (t.to(self.device) for t in quantize_128x128(w2, pow2=pow2))
         self.a2a = P2PAllToAll(
             max_num_tokens=max_num_tokens, num_experts=num_experts, expert_padding=1,
             hidden_dim=hidden_dim, hidden_dim_scale=hidden_dim // 128, in_dtype=torch.float8_e4m3fn,
@@ -77,7 +84,7 @@ class ExpertParallelMoE:
             num_experts_per_token=num_experts_per_token, device=self.device, dp_group=None,
             node_group=None, global_group=global_group, combine_mode=combine_mode,
             # a down projection that sends its own rows writes them in the plain row format
-            wire="plain" if fused_combine else None)
+            wire="plain" if fused_combine else None, pow2_scales=pow2)
         rows = self.a2a.max_recv_rows
         dev = self.device
         self.expert_num_tokens = torch.zeros(L, dtype=torch.int32, device=dev)
@@ -121,7 +128,7 @@ class ExpertParallelMoE:
         """act = quantise(silu(x W_gate^T) * (x W_up^T)) on the rows dispatch delivered."""
         grouped_fp8_gemm(self.expert_x, self.expert_x_scale, self.w13, self.w13_scale, self.expert_num_tokens,
                          self.act, self.act_scale, mode=MODE_SWIGLU_QUANT, error_flag=self.error_flag,
-                         tile_rows=self.tile_rows)
+                         tile_rows=self.tile_rows, scale_format=self.scale_format)
 
     def down_and_send(self) -> None:
         """The down projection and the combine's send phase in one kernel: every output row is
@@ -129,12 +136,13 @@ class ExpertParallelMoE:
         grouped_fp8_gemm(self.act, self.act_scale, self.w2, self.w2_scale, self.expert_num_tokens, None,
                          mode=MODE_BF16_SCATTER, error_flag=self.error_flag,
                          scatter=self.a2a.combine_send_external(self.fused_bulk),
-                         tile_rows=256 if self.fused_bulk else self.tile_rows)
+                         tile_rows=256 if self.fused_bulk else self.tile_rows, scale_format=self.scale_format)
 
     def down(self) -> None:
         """expert_y = act W_down^T in bf16: the rows combine sends home."""
         grouped_fp8_gemm(self.act, self.act_scale, self.w2, self.w2_scale, self.expert_num_tokens,
-                         self.expert_y, mode=MODE_BF16, error_flag=self.error_flag, tile_rows=self.tile_rows)
+                         self.expert_y, mode=MODE_BF16, error_flag=self.error_flag, tile_rows=self.tile_rows,
+                         scale_format=self.scale_format)
 
     __call__ = forward
 

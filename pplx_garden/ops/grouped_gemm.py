@@ -3,6 +3,11 @@ torch-side quantisation helpers that define its number format.
 
 Format: activations e4m3 with one fp32 scale per row and 128 columns (1x128), weights e4m3
 with one fp32 scale per 128x128 block; ``scale = max(amax, 1e-10) / 448``.
+
+With ``pow2=True`` the scale is rounded up to the next power of two (what a UE8M0 scale can
+express). ``grouped_fp8_gemm(..., scale_format="pow2")`` then lets the tensor cores apply the scales
+(``tcgen05.mma.kind::mxf8f6f4.block_scale``, csrc/ops/grouped_gemm_mx.cu) instead of folding every
+K block's partial sums in the epilogue, which is about twice as fast.
 """
 
 from __future__ import annotations
@@ -17,21 +22,36 @@ MODE_SWIGLU_QUANT = 0
 MODE_BF16 = 1
 MODE_BF16_SCATTER = 2
 
+SCALES_FP32 = 0
+SCALES_POW2 = 1
+_SCALE_FORMATS = {"fp32": SCALES_FP32, "pow2": SCALES_POW2, "ue8m0": SCALES_POW2, SCALES_FP32: SCALES_FP32,
+                  SCALES_POW2: SCALES_POW2}
 
-def quantize_1x128(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+
+def round_scale_pow2(scale: torch.Tensor) -> torch.Tensor:
+    """The smallest power of two that is >= each (positive, normal) fp32 scale."""
+    bits = scale.contiguous().view(torch.int32)
+    return ((bits + 0x007FFFFF) & 0x7F800000).view(torch.float32)
+
+
+def quantize_1x128(x: torch.Tensor, pow2: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """[rows, K] float -> (e4m3 [rows, K], fp32 scales [rows, K // 128])."""
     rows, k = x.shape
     blocks = x.to(torch.float32).reshape(rows, k // 128, 128)
     scale = blocks.abs().amax(dim=-1).clamp_min(1e-10) * (1.0 / 448.0)
+    if pow2:
+        scale = round_scale_pow2(scale)
     q = (blocks / scale.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
     return q.reshape(rows, k), scale
 
 
-def quantize_128x128(w: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+def quantize_128x128(w: torch.Tensor, pow2: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
     """[..., N, K] float -> (e4m3 same shape, fp32 scales [..., N // 128, K // 128])."""
     *lead, n, k = w.shape
     blocks = w.to(torch.float32).reshape(*lead, n // 128, 128, k // 128, 128)
     scale = blocks.abs().amax(dim=(-3, -1)).clamp_min(1e-10) * (1.0 / 448.0)
+    if pow2:
+        scale = round_scale_pow2(scale)
     q = (blocks / scale.unsqueeze(-1).unsqueeze(-3)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
     return q.reshape(*lead, n, k), scale
 
@@ -62,6 +82,7 @@ def grouped_fp8_gemm(
     trace: Optional[torch.Tensor] = None,
     scatter: Optional[tuple] = None,
     tile_rows: int = 0,
+    scale_format: str | int = "fp32",
 ) -> None:
     """``out[rows of expert e] = epilogue(dequant(a rows) @ dequant(b[e]).T)``.
 
@@ -75,6 +96,10 @@ def grouped_fp8_gemm(
     buffer of the GPU its token came from (peer stores), and the kernel signals the receivers.
     ``tile_rows``: 256 = pairs of CTAs per tile (each CTA loads half of B), 128 = one CTA per tile,
     better for experts with few rows; 0 picks by ``rows / experts`` (capacity, not the counts).
+    ``scale_format``: "fp32" takes any scales; "pow2" (or "ue8m0") promises that every scale of
+    ``a_scale`` and ``b_scale`` is a power of two (``quantize_*(..., pow2=True)``; a scale that is not
+    is truncated to the one below) and runs the block-scaled MMA kernel, whose SwiGLU epilogue
+    writes power-of-two scales as well. The profiling arguments below are for "fp32" only.
     ``wait_cycles`` (int64 [num CTAs, 4], optional) receives the cycles each pipeline role spent
     waiting: producer for a free stage, MMA for a free accumulator, MMA for operands, epilogue
     for partial sums. ``debug_skip`` (profiling only, wrong results) removes a stage: 1 the
@@ -107,4 +132,4 @@ def grouped_fp8_gemm(
         0 if out_scale is None else out_scale.stride(0), error_flag.data_ptr(), e, n, k, expert_padding, rows, mode,
         num_ctas, torch.cuda.current_stream().cuda_stream,
         0 if wait_cycles is None else wait_cycles.data_ptr(), debug_skip,
-        0 if trace is None else trace.data_ptr(), scatter, tile_rows)
+        0 if trace is None else trace.data_ptr(), scatter, tile_rows, _SCALE_FORMATS[scale_format])

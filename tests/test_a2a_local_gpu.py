@@ -226,12 +226,14 @@ def test_zero_tokens() -> None:
 
 
 @pytest.mark.parametrize("wire", ["ll", "plain"])
-def test_fused_quantisation_matches_reference_quantiser(wire: str) -> None:
-    """bf16 tokens in, e4m3 + one fp32 scale per 1x128 block at the experts."""
+@pytest.mark.parametrize("pow2", [False, True])
+def test_fused_quantisation_matches_reference_quantiser(wire: str, pow2: bool) -> None:
+    """bf16 tokens in, e4m3 + one fp32 scale per 1x128 block at the experts; with ``pow2_scales``
+    every scale is the next power of two."""
     cfg = Cfg(world=4, tokens=32, experts=32, hidden=1024, hidden_scale=8, topk=4,
               in_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16, wire=wire)
     device = torch.device("cuda", 0)
-    group = _make_group(cfg, device)
+    group = _make_group(cfg, device, pow2_scales=pow2)
     try:
         groups = cfg.world
         raw = [make_rank_data(seed=g, num_experts=cfg.experts, topk=cfg.topk, num_tokens=cfg.tokens,
@@ -242,7 +244,7 @@ def test_fused_quantisation_matches_reference_quantiser(wire: str) -> None:
                        [d.weights for d in raw])
         torch.cuda.synchronize()
         group.check()
-        quant = [oracle.quantize_1x128(d.dp_x.cpu().to(torch.float32)) for d in raw]
+        quant = [oracle.quantize_1x128(d.dp_x.cpu().to(torch.float32), pow2=pow2) for d in raw]
         for r in range(cfg.world):
             exp = oracle.expected_dispatch(
                 r, cfg.world, cfg.experts, cfg.padding,
@@ -254,6 +256,8 @@ def test_fused_quantisation_matches_reference_quantiser(wire: str) -> None:
                 n = want.shape[0]
                 got = ox[r][start:start + n].cpu().to(torch.float32)
                 gs = os_[r][start:start + n].cpu()
+                if pow2:
+                    assert (torch.frexp(gs)[0] == 0.5).all(), "scales must be powers of two"
                 deq_got = got * gs.repeat_interleave(128, dim=1)
                 deq_want = want * ws.repeat_interleave(128, dim=1)
                 key_g = deq_got.sum(dim=1).argsort()

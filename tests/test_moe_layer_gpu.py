@@ -12,9 +12,9 @@ from pplx_garden.ops import dequantize_128x128, dequantize_1x128, quantize_1x128
 pytestmark = pytest.mark.gpu
 
 
-def _reference(x, indices, weights, w13_q, w13_s, w2_q, w2_s, experts_per_rank_offset=0):
+def _reference(x, indices, weights, w13_q, w13_s, w2_q, w2_s, experts_per_rank_offset=0, pow2=True):
     """out[t] = sum_k w[t,k] * FFN_{e(t,k)}(x[t]) with fp8 quantisation at the same places."""
-    xq, xs = quantize_1x128(x.float().cpu())
+    xq, xs = quantize_1x128(x.float().cpu(), pow2=pow2)
     xd = dequantize_1x128(xq, xs)
     w13 = dequantize_128x128(w13_q.cpu(), w13_s.cpu())
     w2 = dequantize_128x128(w2_q.cpu(), w2_s.cpu())
@@ -26,19 +26,21 @@ def _reference(x, indices, weights, w13_q, w13_s, w2_q, w2_s, experts_per_rank_o
             e = int(idx[t, k])
             d = w13[e] @ xd[t]
             act = torch.nn.functional.silu(d[:I]) * d[I:]
-            aq, a_s = quantize_1x128(act.unsqueeze(0))
+            aq, a_s = quantize_1x128(act.unsqueeze(0), pow2=pow2)
             y = (w2[e] @ dequantize_1x128(aq, a_s)[0]).to(torch.bfloat16).float()
             out[t] += weights[t, k].item() * y
     return out
 
 
-def test_single_gpu_layer_matches_reference() -> None:
+@pytest.mark.parametrize("scale_format", ["pow2", "fp32"])
+def test_single_gpu_layer_matches_reference(scale_format: str) -> None:
     from pplx_garden.models import ExpertParallelMoE, route_topk
 
     dev = torch.device("cuda", 0)
     H, I, E, K, T = 512, 256, 8, 2, 48
     layer = ExpertParallelMoE(hidden_dim=H, intermediate_dim=I, num_experts=E, num_experts_per_token=K,
-                              max_num_tokens=T, device=dev, global_group=None, init_std=0.05)
+                              max_num_tokens=T, device=dev, global_group=None, init_std=0.05,
+                              scale_format=scale_format)
     try:
         gen = torch.Generator(device="cpu").manual_seed(3)
         x = torch.randn((T, H), generator=gen).to(torch.bfloat16).to(dev)
@@ -46,7 +48,8 @@ def test_single_gpu_layer_matches_reference() -> None:
         out = layer(x, indices, weights)
         torch.cuda.synchronize()
         layer.check()
-        want = _reference(x, indices.view(torch.int32), weights.cpu(), layer.w13, layer.w13_scale, layer.w2, layer.w2_scale)
+        want = _reference(x, indices.view(torch.int32), weights.cpu(), layer.w13, layer.w13_scale, layer.w2, layer.w2_scale,
+                          pow2=scale_format == "pow2")
         got = out.float().cpu()
         err = (got - want).abs().max().item()
         assert err <= 0.06 * want.abs().max().item() + 1e-3, f"max abs error {err} vs scale {want.abs().max().item()}"
@@ -164,8 +167,8 @@ def _worker(device, dp_group, global_group, seed, fused=False):
         layer.check()
         from pplx_garden.ops import quantize_128x128
 
-        w13_q, w13_s = quantize_128x128(w13_all)
-        w2_q, w2_s = quantize_128x128(w2_all)
+        w13_q, w13_s = quantize_128x128(w13_all, pow2=True)
+        w2_q, w2_s = quantize_128x128(w2_all, pow2=True)
         want = _reference(x, indices.view(torch.int32), weights.cpu(), w13_q, w13_s, w2_q, w2_s)
         got = out.float().cpu()
         err = (got - want).abs().max().item()
