@@ -50,6 +50,8 @@ def main() -> None:
     ap.add_argument("--topk", type=int, default=8)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--scales", choices=["pow2", "fp32"], default="pow2",
+                    help="pow2: power-of-two scales applied by the tensor cores; fp32: any scales, folded in by the epilogue")
     ap.add_argument("--no-library", action="store_true")
     ap.add_argument("--no-fused", action="store_true", help="skip the arm whose down projection sends the rows itself")
     ap.add_argument("--bulk", action="store_true", help="also time the fused arm with bulk copies (cp.async.bulk) as the sender")
@@ -65,7 +67,7 @@ def main() -> None:
     T, H, I, E, K = args.tokens, args.hidden, args.intermediate, args.experts, args.topk
 
     layer = ExpertParallelMoE(hidden_dim=H, intermediate_dim=I, num_experts=E, num_experts_per_token=K,
-                              max_num_tokens=T, device=device, global_group=group, seed=1)
+                              max_num_tokens=T, device=device, global_group=group, seed=1, scale_format=args.scales)
     gen = torch.Generator(device="cpu").manual_seed(100 + rank)
     x = torch.randn((T, H), generator=gen).to(torch.bfloat16).to(device)
     logits = torch.randn((T, E), generator=gen).to(device)
@@ -213,7 +215,7 @@ def main() -> None:
     if rank == 0:
         print(json.dumps({
             "config": {"model": "Qwen3-30B-A3B-like MoE layer", "tokens_per_rank": T, "hidden": H, "intermediate": I,
-                       "experts": E, "topk": K, "n_gpus": world, "l2": "flushed before each layer",
+                       "experts": E, "topk": K, "n_gpus": world, "scales": args.scales, "l2": "flushed before each layer",
                        "steps": args.steps, "warmup": args.warmup},
             "unit": "us, max over ranks",
             "ours": ours, "ours_route_in_dispatch": routed, "ours_fused_combine": fused, "ours_fused_combine_bulk": fused_bulk, "library": lib, "max_rel_err_ours_vs_library": max_err,

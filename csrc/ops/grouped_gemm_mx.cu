@@ -27,7 +27,8 @@
 // execute in issue order, so a copy cannot overtake the MMAs that still read the previous group.
 // Optional `trace` (int64 [64][8]): SM clock of CTA 0 per tile: 0 the MMA issuer got the accumulator,
 // 5 it has issued the first K block, 1 the last; 6 the first epilogue warp starts waiting, 2 sees
-// the sums, 3 has them in registers, 4 has stored the tile.
+// the sums, 3 has them in registers, 4 has stored the tile; 7 the issuer's waits of the tile, for
+// operands in the low word and for scale words in the high word.
 // No TMA multicast anywhere. Every wait is bounded and sets error_flag (1 producer, 2 MMA issuer,
 // 3 epilogue, 4 scale warp).
 //
@@ -225,6 +226,7 @@ __device__ __forceinline__ void grouped_fp8_gemm_mx_body(const KernelArgs& a) {
       bool ok = true;
       for (int t = pair; t < total_tiles && ok; t += num_pairs, ++tile_i) {
         const bool stamp = a.trace != nullptr && blockIdx.x == 0 && lane == 0 && tile_i < kTraceTiles;
+        long long waited_full = 0, waited_sf = 0;
         for (int kb = 0; kb < nkb && ok; ++kb, ++it) {
           if (__shfl_sync(0xffffffffu, *reinterpret_cast<volatile uint32_t*>(&s_failed), 0) != 0) {
             ok = false;
@@ -234,10 +236,16 @@ __device__ __forceinline__ void grouped_fp8_gemm_mx_body(const KernelArgs& a) {
           const uint32_t sub = static_cast<uint32_t>(kb) & 3u;   // which byte of the scale words
           const bool last_of_group = sub == 3u || kb == nkb - 1;
           const uint32_t slot = sf_it % kSfSlots;
+          const long long w0 = stamp ? clock64() : 0;
           ok = __all_sync(0xffffffffu, mbar_wait_timed(&full_bar[s], (it / kStagesMx) & 1u, kWaitNs));
+          const long long w1 = stamp ? clock64() : 0;
           if (ok && sub == 0u) {
             ok = __all_sync(0xffffffffu,
                             mbar_wait_timed_acquire_cluster(&sf_full_bar[slot], (sf_it / kSfSlots) & 1u, kWaitNs));
+          }
+          if (stamp) {   // low word: cycles spent waiting for operands, high word: for scale words
+            waited_full += w1 - w0;
+            waited_sf += clock64() - w1;
           }
           if (!ok) break;
           fence_after_thread_sync();
@@ -284,7 +292,10 @@ __device__ __forceinline__ void grouped_fp8_gemm_mx_body(const KernelArgs& a) {
           if (last_of_group) ++sf_it;
           if (stamp && kb == 0) a.trace[tile_i * 8 + 5] = clock64();
         }
-        if (stamp) a.trace[tile_i * 8 + 1] = clock64();
+        if (stamp) {
+          a.trace[tile_i * 8 + 1] = clock64();
+          a.trace[tile_i * 8 + 7] = (waited_sf << 32) | (waited_full & 0xffffffffll);
+        }
       }
       if (!ok && lane == 0) {
         s_failed = 1;
@@ -387,7 +398,11 @@ __device__ __forceinline__ void grouped_fp8_gemm_mx_body(const KernelArgs& a) {
         *reinterpret_cast<uint4*>(sf + kSfaBytes + 512 + lane * 16) = second;
         fence_proxy_async_smem();   // tcgen05.cp reads shared memory through the async proxy
         __syncwarp();
-        if (lane == 0) mbar_arrive_release_cluster(sf_full_leader + slot * 8u);
+        // Default (CTA-scope) release on purpose: a cluster-scope release would first wait for this
+        // thread's cp.async copies in flight, one memory round trip per group. The words are in this
+        // CTA's shared memory and fenced for the async proxy above; the copy into tensor memory
+        // that the leader triggers reads them on this SM.
+        if (lane == 0) mbar_arrive_cluster(sf_full_leader + slot * 8u);
         ++sf_it;
       }
       cp_async_wait<0>();   // nothing of this thread's may still be landing when the CTA leaves
