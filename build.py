@@ -68,7 +68,22 @@ def _has_header(name: str) -> bool:
     return any((Path(d) / name).exists() for d in ("/usr/include", "/usr/local/include"))
 
 
-def write_ninja(verbose: bool) -> Path:
+def _sanitizer_compiler(sanitize: str) -> str:
+    """A g++ that can link -fsanitize=<sanitize> (the runtime library is not part of every install)."""
+    import tempfile
+
+    for cxx in dict.fromkeys([os.environ.get("CXX", "g++"), "/usr/bin/g++", "g++"]):
+        with tempfile.TemporaryDirectory(dir=BUILD) as tmp:
+            src = Path(tmp) / "probe.cpp"
+            src.write_text("int main() { return 0; }\n")
+            probe = subprocess.run([cxx, f"-fsanitize={sanitize}", str(src), "-o", str(Path(tmp) / "probe")],
+                                   capture_output=True)
+            if probe.returncode == 0:
+                return cxx
+    raise RuntimeError(f"no g++ here can link -fsanitize={sanitize}")
+
+
+def write_ninja(verbose: bool, sanitize: str | None = None) -> Path:
     BUILD.mkdir(exist_ok=True)
     py_inc = sysconfig.get_paths()["include"]
     ext_suffix = sysconfig.get_config_var("EXT_SUFFIX")
@@ -109,6 +124,24 @@ def write_ninja(verbose: bool) -> Path:
         "  description = LINK $out",
         "",
     ]
+    if sanitize:
+        # The host code once more with a sanitizer (address, thread or undefined), for the native
+        # unit tests only: kernels and CUDA runtime calls are not instrumented.
+        san = ["-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", f"-fsanitize={sanitize}", "-fPIC", "-Wall",
+               "-Wno-unused-function", "-pthread"] + defines
+        lines += [
+            f"sancxx = {_sanitizer_compiler(sanitize)}",
+            f"sanflags = {' '.join(san + common_inc)}",
+            "rule cxx_san",
+            "  command = $sancxx -MMD -MF $out.d $sanflags -c $in -o $out",
+            "  depfile = $out.d",
+            "  deps = gcc",
+            "  description = CXX($sanitize) $in".replace("$sanitize", sanitize),
+            "rule link_san",
+            f"  command = $sancxx -fsanitize={sanitize} -o $out $in $ldflags",
+            "  description = LINK $out",
+            "",
+        ]
     groups = _sources()
 
     def compile_group(paths: list[Path], tag: str) -> list[str]:
@@ -151,16 +184,31 @@ def write_ninja(verbose: bool) -> Path:
             (ROOT / "bin").mkdir(exist_ok=True)
             lines.append(f"build {out}: link_exe {' '.join(objs + core_objs)}")
             targets.append(str(out))
+    if sanitize and groups["core_tests"]:
+        san_objs = []
+        for src in [p for p in groups["ext"] if "bindings" not in p.relative_to(CSRC).parts] + groups["core_tests"]:
+            rel = src.relative_to(CSRC)
+            if src.suffix == ".cu":
+                # device code and its host stubs as built above
+                san_objs.append(str((BUILD / "ext" / rel.with_suffix(rel.suffix + ".o")).relative_to(ROOT)))
+                continue
+            obj = (BUILD / f"san-{sanitize}" / rel.with_suffix(rel.suffix + ".o"))
+            obj.parent.mkdir(parents=True, exist_ok=True)
+            lines.append(f"build {obj.relative_to(ROOT)}: cxx_san {src.relative_to(ROOT)}")
+            san_objs.append(str(obj.relative_to(ROOT)))
+        out = Path("bin") / f"pplx-core-tests-{sanitize}"
+        lines.append(f"build {out}: link_san {' '.join(san_objs)}")
+        targets.append(str(out))
     lines.append(f"default {' '.join(targets)}")
     ninja = BUILD / "build.ninja"
     ninja.write_text("\n".join(lines) + "\n")
     return ninja
 
 
-def build(verbose: bool = False, jobs: int | None = None, clean: bool = False) -> None:
+def build(verbose: bool = False, jobs: int | None = None, clean: bool = False, sanitize: str | None = None) -> None:
     if clean and BUILD.exists():
         shutil.rmtree(BUILD)
-    ninja = write_ninja(verbose)
+    ninja = write_ninja(verbose, sanitize)
     cmd = ["ninja", "-f", str(ninja)]
     if jobs:
         cmd += ["-j", str(jobs)]
@@ -174,8 +222,11 @@ def main() -> None:
     ap.add_argument("--verbose", action="store_true", help="show commands and ptxas resource usage")
     ap.add_argument("--clean", action="store_true")
     ap.add_argument("--jobs", type=int, default=None)
+    ap.add_argument("--sanitize", choices=["address", "thread", "undefined"], default=None,
+                    help="also build bin/pplx-core-tests-<sanitizer>: the host code and its native unit tests "
+                         "(engine threads, imm counters, sharding, ...) under that sanitizer")
     args = ap.parse_args()
-    build(args.verbose, args.jobs, args.clean)
+    build(args.verbose, args.jobs, args.clean, args.sanitize)
 
 
 if __name__ == "__main__":

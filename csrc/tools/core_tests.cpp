@@ -2,9 +2,11 @@
 // unit tests: cuda-lib/src/test_driver.rs, fabric-lib's imm_count / utils modules). No GPU is
 // needed. Exit code 0 when every check passes; each failure prints its expression and line.
 #include <atomic>
+#include <chrono>
 #include <cstdio>
 #include <cstring>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include "../core/error.h"
@@ -12,7 +14,9 @@
 #include "../fabric/host_buffer.h"
 #include "../fabric/imm_count.h"
 #include "../fabric/shard.h"
+#include "../fabric/faulty_domain.h"
 #include "../fabric/topo.h"
+#include "../fabric/transfer_engine.h"
 #include "../fabric/util.h"
 #include "../unigram/json.h"
 
@@ -183,6 +187,98 @@ void test_json_numbers() {
   CHECK(threw);
 }
 
+// Two engines on host memory (no GPU), four submitting threads each way, callbacks and counters
+// coming back on the engines' own threads, immediates counted at the receiver, a delayed and
+// reordered domain under one of them, then shutdown while the last completions arrive. Its job is
+// to give the thread and address sanitizer builds (python build.py --sanitize thread|address)
+// something that exercises the engine's locking and object lifetimes; the assertions are the
+// same a plain build checks.
+void test_engine_threads() {
+  GpuDomainSpec spec;
+  spec.cuda_device = -1;
+  spec.domains = {DomainInfo{"host0", 1, "local"}, DomainInfo{"host1", 1, "local"}};
+  std::vector<uint8_t> src(1 << 16), dst_a(1 << 16), dst_b(1 << 16);
+  for (size_t i = 0; i < src.size(); ++i) src[i] = static_cast<uint8_t>(i * 7);
+  {
+    TransferEngine a({spec}), b({spec});
+    const auto a_src = a.register_memory(reinterpret_cast<uint64_t>(src.data()), src.size(), -1);
+    const auto b_dst = b.register_memory(reinterpret_cast<uint64_t>(dst_b.data()), dst_b.size(), -1);
+    const auto b_src = b.register_memory(reinterpret_cast<uint64_t>(src.data()), src.size(), -1);
+    const auto a_dst = a.register_memory(reinterpret_cast<uint64_t>(dst_a.data()), dst_a.size(), -1);
+    if (auto* d = dynamic_cast<FaultyDomain*>(a.debug_domain(-1, 1))) {
+      d->inject(FaultKind::kDelayWrites, 1);
+      d->inject(FaultKind::kReorderWrites, 2);
+    }
+    std::atomic<int> imm_seen{0}, reached{0}, done_cb{0}, err_cb{0};
+    b.set_imm_callback([&](uint32_t) { imm_seen.fetch_add(1); });
+    a.set_imm_count_expected(7, 64, [&] { reached.fetch_add(1); });
+    auto done = std::make_shared<std::atomic<int64_t>>(0);
+    auto errors = std::make_shared<std::atomic<int64_t>>(0);
+    const TransferCounter counter(done, errors);
+    constexpr int kThreads = 4, kPerThread = 32;
+    std::vector<std::thread> threads;
+    for (int t = 0; t < kThreads; ++t) {
+      threads.emplace_back([&, t] {
+        for (int i = 0; i < kPerThread; ++i) {
+          const uint64_t off = static_cast<uint64_t>(t * kPerThread + i) * 256;
+          SingleTransferRequest r;
+          r.src_mr = a_src.first;
+          r.src_offset = off;
+          r.length = 256;
+          r.dst_mr = b_dst.second;
+          r.dst_offset = off;
+          r.imm_data = (i % 2 == 0) ? std::optional<uint32_t>(1000 + i) : std::nullopt;
+          r.domain = DomainGroupRouting::sharded(2);
+          if (i % 4 == 0) {
+            a.submit_transfer_atomic(TransferRequest(std::move(r)), counter);
+          } else {
+            a.submit_transfer(TransferRequest(std::move(r)), [&] { done_cb.fetch_add(1); },
+                              [&](const std::string&) { err_cb.fetch_add(1); });
+          }
+          // and the other way, with an immediate that the first engine counts
+          if (i % 2 == 0) {
+            SingleTransferRequest back;
+            back.src_mr = b_src.first;
+            back.src_offset = off;
+            back.length = 128;
+            back.dst_mr = a_dst.second;
+            back.dst_offset = off;
+            back.imm_data = 7;
+            back.domain = DomainGroupRouting::pinned(static_cast<uint8_t>(i % 2));
+            b.submit_transfer(TransferRequest(std::move(back)), [&] { done_cb.fetch_add(1); },
+                              [&](const std::string&) { err_cb.fetch_add(1); });
+          }
+        }
+      });
+    }
+    for (auto& th : threads) th.join();
+    const int want_cb = kThreads * kPerThread * 3 / 4 + kThreads * kPerThread / 2;
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(20);
+    while ((done_cb.load() < want_cb || done->load() < kThreads * kPerThread / 4 || reached.load() < 1 ||
+            imm_seen.load() < kThreads * kPerThread) &&
+           std::chrono::steady_clock::now() < deadline) {
+      std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    }
+    CHECK(done_cb.load() == want_cb);
+    CHECK(err_cb.load() == 0 && errors->load() == 0);
+    CHECK(done->load() == kThreads * kPerThread / 4);
+    CHECK(imm_seen.load() == kThreads * kPerThread);   // two shards per write, each carries the immediate
+    CHECK(reached.load() == 1);
+    CHECK(std::memcmp(src.data(), dst_b.data(), kThreads * kPerThread * 256) == 0);
+    // a last burst that is still in flight when the engines are stopped and destroyed
+    for (int i = 0; i < 16; ++i) {
+      SingleTransferRequest r;
+      r.src_mr = a_src.first;
+      r.length = 4096;
+      r.dst_mr = b_dst.second;
+      r.domain = DomainGroupRouting::sharded(2);
+      a.submit_transfer(TransferRequest(std::move(r)), [] {}, [](const std::string&) {});
+    }
+    a.stop();
+    b.stop();
+  }
+}
+
 }  // namespace
 
 int main() {
@@ -193,6 +289,7 @@ int main() {
   test_host_buffers();
   test_addresses_and_topology_helpers();
   test_json_numbers();
+  test_engine_threads();
   std::printf("%d checks, %d failed\n", g_checks, g_failures);
   return g_failures == 0 ? 0 : 1;
 }

@@ -175,6 +175,18 @@ class P2PAllToAll(AllToAllKernel):
         )
         self._layout = layout
         self.max_recv_rows: int = layout["max_recv_rows"]
+        # Every rank writes into its peers' buffers with its own idea of the layout: the wire format
+        # (which an environment variable can override per process), strides and offsets must be
+        # the same everywhere, or a receiver would wait for lines that never come.
+        if global_group is not None and world_size > 1:
+            shape_keys = sorted(k for k in layout if k not in ("num_blocks", "node_mask", "wait_limit_ns"))
+            mine_shape = tuple((k, layout[k]) for k in shape_keys)
+            for peer, theirs in enumerate(global_group.all_gather_object(mine_shape)):
+                if theirs != mine_shape:
+                    diff = [k for (k, v), (_, w) in zip(mine_shape, theirs) if v != w]
+                    raise ValueError(
+                        f"rank {rank} and rank {peer} disagree about the all-to-all layout ({', '.join(diff)}); "
+                        "check PPLX_A2A_WIRE and the constructor arguments on every rank")
 
         torch.cuda.set_device(device)
         handle_kind = CUMemHandleKind.FileDescriptor
