@@ -301,7 +301,8 @@ __device__ __forceinline__ void grouped_fp8_gemm_body(const KernelArgs& a) {
       const int nb0 = swiglu ? n_tile : n_tile * 2 + h;
       const int nb1 = swiglu ? I / 128 + n_tile : nb0;
       TileScales ts;
-      ts.a_row = a.a_scale + static_cast<int64_t>(valid ? row : 0) * a.a_scale_stride_row;
+      // rows past the count read their own (clamped) row's scales: one shared fallback row would be a hot line in L2
+      ts.a_row = a.a_scale + static_cast<int64_t>(min(row, a.max_rows - 1)) * a.a_scale_stride_row;
       ts.b0 = a.b_scale + (static_cast<int64_t>(e) * nb_per_expert + nb0) * nkb_scale;
       ts.b1 = a.b_scale + (static_cast<int64_t>(e) * nb_per_expert + nb1) * nkb_scale;
       return ts;
