@@ -21,7 +21,9 @@ Extensions (keyword-only, all optional): ``combine_mode="pre_reduce"`` makes the
 ranks apply the routing weights given at dispatch time and send one partial sum per
 (token, expert rank) instead of one row per route; passing bf16 ``dp_x`` to a context
 whose ``in_dtype`` is ``float8_e4m3fn`` with ``hidden_dim_scale = hidden_dim // 128`` and
-``dp_x_scale=None`` quantises on the fly (one fp32 scale per 1x128 block); ``wire`` picks
+``dp_x_scale=None`` quantises on the fly (one fp32 scale per 1x128 block; with
+``pow2_scales=True`` every scale is rounded up to a power of two, which the block-scaled expert
+GEMM, ``grouped_fp8_gemm(scale_format="pow2")``, needs); ``wire`` picks
 the format on the wire: ``"ll"`` (128-byte lines that carry their own arrival flag, no fences,
 one eighth more bytes: best for decode-sized calls), ``"plain"`` (contiguous records announced
 by release stores: best for prefill-sized calls) or ``None`` (``"ll"`` up to 512 tokens per

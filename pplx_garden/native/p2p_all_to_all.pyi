@@ -78,7 +78,7 @@ class AllToAllContext:
         weights_stride: int,
         bound_m_ptr: int | None,
         stream: int,
-        quantize: bool = False,
+        quantize: int = 0,  # 0 no, 1 bf16 -> e4m3 with fp32 1x128 scales, 2 the same with power-of-two scales
         logits_ptr: int | None = None,
         logits_stride: int = 0,
         logits_bf16: bool = False,
