@@ -3,9 +3,12 @@
 layer (hidden 2048, intermediate 768, 16 local experts, ~1024 rows per expert) and of a
 DeepSeek-V3-like layer, device-timed with CUDA events after warm-up, inputs larger than L2
 rotated between iterations. Reports TFLOP/s and the fraction of the measured cuBLAS bf16 peak
-doubled for fp8 (MEASURED_PEAKS.json if present).
+doubled for fp8 (MEASURED_PEAKS.json if present). `--scales pow2` (default) quantises with
+power-of-two scales and runs the kernel whose tensor cores apply them; `--scales fp32` runs the
+kernel that folds arbitrary scales in per K block and also reports where its pipeline waits.
 
-    python -m benchmarks.bench_grouped_gemm [--rows-per-expert 1024] [--experts 16]
+    python -m benchmarks.bench_grouped_gemm [--rows-per-expert 1024] [--experts 16] [--scales pow2|fp32]
+    python -m benchmarks.bench_grouped_gemm --experts 8 --hidden 7168 --intermediate 2048    # DeepSeek-V3-like
 """
 
 from __future__ import annotations
