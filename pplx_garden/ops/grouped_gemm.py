@@ -123,6 +123,8 @@ def grouped_fp8_gemm(
         assert out is None and scatter is not None
     else:
         assert out.dtype == torch.bfloat16 and out.shape == (rows, n)
+    if _SCALE_FORMATS[scale_format] == SCALES_POW2 and (wait_cycles is not None or debug_skip != 0):
+        raise ValueError("wait_cycles and debug_skip belong to the fp32-scale kernel; the pow2 kernel has trace= only")
     if error_flag is None:
         error_flag = torch.zeros(1, dtype=torch.int32, device=a.device)
     _native.grouped_fp8_gemm(
