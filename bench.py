@@ -498,7 +498,8 @@ def main() -> None:
             # The same step as a serving loop launches it: captured once per staging buffer in a
             # CUDA graph (copy in, dispatch, combine, copy out) and replayed. Epochs and cursors
             # live on the device, so a replay is a step like any other.
-            # Across ranks the replay has only been exercised on one GPU so far: there it is off
+            # Across ranks the replay bought nothing (EP8, host clock: 209.1 us replayed against
+            # 203.6 us eager) and its device-timed form has only run on one GPU: there it is off
             # unless PPLX_BENCH_GRAPH=1 asks for it, and the eager figure stands.
             if args.impl == "ours" and (world == 1 or os.environ.get("PPLX_BENCH_GRAPH") == "1"):
                 try:
