@@ -17,6 +17,16 @@ using fabric::TransferCounter;
 using fabric::TransferRequest;
 
 namespace {
+// The words come from the kernels (system-scope release stores into pinned host memory) or, in
+// host-only tests, from another thread: the phase words are read with acquire, what they publish
+// after that with plain atomic loads.
+uint32_t load_acquire(const volatile uint32_t* p) {
+  return __atomic_load_n(const_cast<const uint32_t*>(p), __ATOMIC_ACQUIRE);
+}
+uint32_t load_relaxed(const volatile uint32_t* p) {
+  return __atomic_load_n(const_cast<const uint32_t*>(p), __ATOMIC_RELAXED);
+}
+
 uint64_t flag_offset(int row, int src_rank) {
   return static_cast<uint64_t>(row * kMaxRanks + src_rank) * kFlagStrideWords * sizeof(uint32_t);
 }
@@ -91,17 +101,15 @@ void A2AProxy::loop() {
   while (!stop_.load(std::memory_order_acquire)) {
     bool worked = false;
     // the kernels write the tag of the phase that has just finished (tags count up from 1)
-    const uint32_t d = buf_.proxy_words[kProxyDispatchSent];
+    const uint32_t d = load_acquire(&buf_.proxy_words[kProxyDispatchSent]);
     if (static_cast<int32_t>(d - next_dispatch) >= 0) {
-      std::atomic_thread_fence(std::memory_order_acquire);
       serve_dispatch(next_dispatch);
       ++next_dispatch;
       dispatches_.fetch_add(1);
       worked = true;
     }
-    const uint32_t c = buf_.proxy_words[kProxyCombineSent];
+    const uint32_t c = load_acquire(&buf_.proxy_words[kProxyCombineSent]);
     if (static_cast<int32_t>(c - next_combine) >= 0) {
-      std::atomic_thread_fence(std::memory_order_acquire);
       serve_combine(next_combine);
       ++next_combine;
       combines_.fetch_add(1);
@@ -148,8 +156,7 @@ bool A2AProxy::run(std::vector<TransferRequest> requests, const char* what) {
 bool A2AProxy::send_flags(int row, uint32_t tag, const char* what) {
   // one word per (row, tag parity) so that a flag in flight is never overwritten by the next
   const int word = row * 2 + static_cast<int>(tag & 1u);
-  buf_.flag_source_host[word] = tag;
-  std::atomic_thread_fence(std::memory_order_release);
+  __atomic_store_n(const_cast<uint32_t*>(&buf_.flag_source_host[word]), tag, __ATOMIC_RELEASE);
   std::vector<TransferRequest> requests;
   for (const A2AProxyPeer& p : peers_) {
     SingleTransferRequest r;
@@ -183,7 +190,7 @@ void A2AProxy::serve_dispatch(uint32_t tag) {
     c.dst_offset = counts_off;
     c.domain = DomainGroupRouting::pinned(0);
     requests.emplace_back(std::move(c));
-    const uint64_t records = buf_.proxy_words[kProxyRecords + p.rank];
+    const uint64_t records = load_relaxed(&buf_.proxy_words[kProxyRecords + p.rank]);
     if (records == 0) continue;
     if (records > static_cast<uint64_t>(cfg_.max_num_tokens)) {
       fail("dispatch: the kernel reported more records than a region holds");
@@ -209,9 +216,9 @@ void A2AProxy::serve_combine(uint32_t tag) {
   std::vector<TransferRequest> requests;
   for (const A2AProxyPeer& p : peers_) {
     const int g = p.rank / cfg_.dp_size;   // rows go to every member of the origin's dp group
-    const uint32_t rows = buf_.proxy_words[kProxyRows + g];
+    const uint32_t rows = load_relaxed(&buf_.proxy_words[kProxyRows + g]);
     if (rows == 0) continue;
-    const uint32_t first = buf_.proxy_words[kProxyRowBase + g];
+    const uint32_t first = load_relaxed(&buf_.proxy_words[kProxyRowBase + g]);
     if (static_cast<uint64_t>(first) + rows > cfg_.max_recv_rows) {
       fail("combine: the kernel reported more staged rows than the staging buffer holds");
       return;
@@ -221,7 +228,7 @@ void A2AProxy::serve_combine(uint32_t tag) {
     const uint64_t slots = static_cast<uint64_t>(cfg_.max_num_tokens) * cfg_.c_records_per_token;
     for (uint32_t i = 0; i < rows; ++i) {
       (*src_pages)[i] = first + i;
-      const uint32_t slot = buf_.stage_slot[first + i];
+      const uint32_t slot = load_relaxed(&buf_.stage_slot[first + i]);
       if (slot >= slots) {
         fail("combine: a staged row names a slot outside the receive buffer");
         return;

@@ -19,6 +19,27 @@
 namespace pplx::fabric {
 
 namespace {
+// A one-sided write into host memory that another thread may be polling (a flag word after the
+// data it announces): words are stored with release semantics, so that everything this thread
+// copied before is visible to a reader that sees the word, also on weakly ordered CPUs; anything
+// else is a plain copy.
+void host_write(void* dst, const void* src, size_t n) {
+  const uintptr_t d = reinterpret_cast<uintptr_t>(dst);
+  if (n == 4 && d % 4 == 0) {
+    uint32_t v;
+    std::memcpy(&v, src, 4);
+    __atomic_store_n(static_cast<uint32_t*>(dst), v, __ATOMIC_RELEASE);
+  } else if (n == 8 && d % 8 == 0) {
+    uint64_t v;
+    std::memcpy(&v, src, 8);
+    __atomic_store_n(static_cast<uint64_t*>(dst), v, __ATOMIC_RELEASE);
+  } else {
+    std::memcpy(dst, src, n);
+  }
+}
+}  // namespace
+
+namespace {
 
 enum MsgType : uint32_t {
   kMsgSend = 1,
@@ -466,7 +487,7 @@ void LocalDomain::handle(Message& msg, std::vector<DomainCompletion>* out) {
       if (it != by_rkey_.end()) {
         const Region& r = regions_[it->second];
         if (r.device < 0 && msg.b + msg.payload.size() <= r.len) {
-          std::memcpy(reinterpret_cast<void*>(r.ptr + msg.b), msg.payload.data(), msg.payload.size());
+          host_write(reinterpret_cast<void*>(r.ptr + msg.b), msg.payload.data(), msg.payload.size());
           ok = true;
         }
       }
@@ -722,8 +743,8 @@ void LocalDomain::run_write(const PendingWrite& w, RemoteRegion& rr, std::vector
   if (!dst_dev && !src_dev) {
     if (rr.same_process) {
       for (size_t i = 0; i < num_pages; ++i) {
-        std::memcpy(rr.mapped + dst_page(i) * dst_stride + dst_offset,
-                    reinterpret_cast<const void*>(src_base + src_page(i) * src_stride + src_offset), length);
+        host_write(rr.mapped + dst_page(i) * dst_stride + dst_offset,
+                   reinterpret_cast<const void*>(src_base + src_page(i) * src_stride + src_offset), length);
       }
       finish_now();
       return;

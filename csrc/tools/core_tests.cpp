@@ -9,6 +9,8 @@
 #include <thread>
 #include <vector>
 
+#include "../a2a/a2a_context.h"
+#include "../a2a/a2a_proxy.h"
 #include "../core/error.h"
 #include "../fabric/api.h"
 #include "../fabric/host_buffer.h"
@@ -98,7 +100,7 @@ void test_imm_counts() {
   CHECK(map.inc(7) == ImmIncResult::kNotReached);
   CHECK(map.inc(7) == ImmIncResult::kReached);
   CHECK(map.inc(7) == ImmIncResult::kVacant);   // fired once; surplus arrivals see no counter
-  auto prev = map.set_expected(7, 2);
+  [[maybe_unused]] auto prev = map.set_expected(7, 2);
   CHECK(map.inc(7, 2) == ImmIncResult::kReached);
   auto free_cell = map.set_free(9);
   map.inc(9);
@@ -279,6 +281,130 @@ void test_engine_threads() {
   }
 }
 
+// The all-to-all's host proxy between two one-rank "nodes" over host memory: this test plays the
+// kernels (it fills the stand-in buffers and raises the words they would raise) and checks that
+// counts, records and combine rows land where the remote kernels expect them, and that a flag
+// never arrives before its data. Mainly here so that the proxy thread, the engine's threads and
+// the words they share run under the sanitizers.
+void test_proxy_between_two_nodes() {
+  A2AParams p;
+  p.world = 2;
+  p.num_experts = 4;
+  p.topk = 2;
+  p.max_num_tokens = 8;
+  p.hidden_dim = 64;
+  p.in_elemsize = 2;
+  p.out_elemsize = 2;
+  p.wire = kWirePlain;
+  p.wait_limit_ms = 3000;
+  struct Side {
+    A2AConfig cfg;
+    std::vector<uint8_t> sync, recv, shadow_sync, shadow_recv, stage, flag_source;
+    std::vector<uint32_t> words, slots;
+    std::unique_ptr<TransferEngine> engine;
+    MemoryRegionDescriptor sync_desc, recv_desc;
+    std::unique_ptr<A2AProxy> proxy;
+  };
+  GpuDomainSpec spec;
+  spec.cuda_device = -1;
+  spec.domains = {DomainInfo{"host0", 1, "local"}};
+  Side side[2];
+  for (int r = 0; r < 2; ++r) {
+    Side& s = side[r];
+    p.node_mask = 1u << r;
+    s.cfg = a2a_make_config(p, 148, 1);
+    s.sync.assign(s.cfg.sync_bytes, 0);
+    s.recv.assign(s.cfg.recv_bytes, 0);
+    s.shadow_sync.assign(s.cfg.sync_bytes, 0);
+    s.shadow_recv.assign(s.cfg.drecv_group_stride, 0);
+    s.stage.assign(static_cast<size_t>(s.cfg.max_recv_rows) * s.cfg.c_stride, 0);
+    s.flag_source.assign(4096, 0);
+    s.words.assign(kProxyWords, 0);
+    s.slots.assign(s.cfg.max_recv_rows, 0);
+    s.engine = std::make_unique<TransferEngine>(std::vector<GpuDomainSpec>{spec});
+    auto reg = [&](std::vector<uint8_t>& v) {
+      return s.engine->register_memory(reinterpret_cast<uint64_t>(v.data()), v.size(), -1).second;
+    };
+    s.sync_desc = reg(s.sync);
+    s.recv_desc = reg(s.recv);
+    reg(s.shadow_sync);
+    reg(s.shadow_recv);
+    reg(s.stage);
+    reg(s.flag_source);
+  }
+  for (int r = 0; r < 2; ++r) {
+    Side& s = side[r];
+    Side& o = side[1 - r];
+    A2AProxyPeer peer;
+    peer.rank = 1 - r;
+    peer.sync_desc = o.sync_desc;
+    peer.recv_desc = o.recv_desc;
+    A2AProxyBuffers buf;
+    buf.shadow_sync[1 - r] = reinterpret_cast<uint64_t>(s.shadow_sync.data());
+    buf.shadow_recv[1 - r] = reinterpret_cast<uint64_t>(s.shadow_recv.data());
+    buf.stage = reinterpret_cast<uint64_t>(s.stage.data());
+    buf.flag_source = reinterpret_cast<uint64_t>(s.flag_source.data());
+    buf.flag_source_host = reinterpret_cast<volatile uint32_t*>(s.flag_source.data());
+    buf.proxy_words = reinterpret_cast<volatile uint32_t*>(s.words.data());
+    buf.stage_slot = reinterpret_cast<const volatile uint32_t*>(s.slots.data());
+    s.proxy = std::make_unique<A2AProxy>(s.cfg, r, s.engine.get(), std::vector<A2AProxyPeer>{peer}, buf, -1);
+  }
+  Side& a = side[0];
+  Side& b = side[1];
+  const A2AConfig& c = a.cfg;
+  auto flag_at = [&](Side& s, int row, int src) {
+    const size_t off = static_cast<size_t>(row * kMaxRanks + src) * kFlagStrideWords * sizeof(uint32_t);
+    return __atomic_load_n(reinterpret_cast<uint32_t*>(s.sync.data() + off), __ATOMIC_ACQUIRE);
+  };
+  auto raise = [&](Side& s, int word, uint32_t value) {
+    __atomic_store_n(&s.words[word], value, __ATOMIC_RELEASE);
+  };
+  auto wait_for = [&](auto cond) {
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(10);
+    while (!cond() && std::chrono::steady_clock::now() < deadline) std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    return cond();
+  };
+  // dispatch 1 from rank 0: three records and the counts message
+  for (size_t i = 0; i < 3u * c.d_stride; ++i) a.shadow_recv[i] = static_cast<uint8_t>(1 + i % 251);
+  const size_t counts_off = c.off_counts;   // bank 0, source group 0
+  for (uint32_t i = 0; i < c.counts_stride; ++i) {
+    const uint32_t v = i + 1;
+    std::memcpy(a.shadow_sync.data() + counts_off + 4 * i, &v, 4);
+  }
+  a.words[kProxyRecords + 1] = 3;
+  raise(a, kProxyDispatchSent, 1);
+  CHECK(wait_for([&] { return flag_at(b, kFlagDispatchStarted, 0) == 1u; }));
+  CHECK(std::memcmp(b.recv.data() + c.off_drecv, a.shadow_recv.data(), 3u * c.d_stride) == 0);
+  CHECK(std::memcmp(b.sync.data() + counts_off, a.shadow_sync.data() + counts_off, 4u * c.counts_stride) == 0);
+  // the proxy counts a phase when its own write of the flag has completed, which is after the flag is visible
+  CHECK(wait_for([&] { return a.proxy->dispatches() == 1u; }) && !a.proxy->failed());
+  // combine 1: four rows for rank 1, staged behind five rows that stay here
+  const uint32_t slots[4] = {7, 0, 12, 3};
+  for (int i = 0; i < 4; ++i) {
+    a.slots[5 + i] = slots[i];
+    std::memset(a.stage.data() + static_cast<size_t>(5 + i) * c.c_stride, 0x40 + i, c.c_stride);
+  }
+  a.words[kProxyRowBase + 1] = 5;
+  a.words[kProxyRows + 1] = 4;
+  raise(a, kProxyCombineSent, 1);
+  CHECK(wait_for([&] { return flag_at(b, kFlagRemoteCombine, 0) == 1u; }));
+  for (int i = 0; i < 4; ++i) {
+    const uint8_t* row = b.recv.data() + c.off_crecv + static_cast<size_t>(slots[i]) * c.c_stride;
+    CHECK(row[0] == 0x40 + i && row[c.c_stride - 1] == 0x40 + i);
+  }
+  CHECK(wait_for([&] { return a.proxy->combines() == 1u; }));
+  // the other direction at the same time as a second dispatch from rank 0
+  b.words[kProxyRecords + 0] = 0;
+  raise(b, kProxyDispatchSent, 1);
+  a.words[kProxyRecords + 1] = 0;
+  raise(a, kProxyDispatchSent, 2);
+  CHECK(wait_for([&] { return flag_at(a, kFlagDispatchStarted, 1) == 1u && flag_at(b, kFlagDispatchStarted, 0) == 2u; }));
+  for (Side& s : side) {
+    s.proxy.reset();
+    s.engine->stop();
+  }
+}
+
 }  // namespace
 
 int main() {
@@ -290,6 +416,7 @@ int main() {
   test_addresses_and_topology_helpers();
   test_json_numbers();
   test_engine_threads();
+  test_proxy_between_two_nodes();
   std::printf("%d checks, %d failed\n", g_checks, g_failures);
   return g_failures == 0 ? 0 : 1;
 }

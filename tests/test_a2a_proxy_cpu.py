@@ -102,7 +102,8 @@ def test_proxy_forwards_dispatch_then_combine(ranks) -> None:
     assert torch.equal(b.recv[dst:dst + 3 * d_stride], records)
     assert int(b.recv[dst + 3 * d_stride:dst + 4 * d_stride].count_nonzero()) == 0
     assert torch.equal(b.sync[counts_off:counts_off + 4 * L["counts_stride"]].view(torch.int32), counts)
-    assert a.probe.counters() == (1, 0)
+    # the proxy counts a phase once its own write of the flag has completed: just after the flag is visible
+    assert _wait(lambda: a.probe.counters() == (1, 0))
 
     # ---- combine 1: rows for origin group 1 sit in the second segment of the staging buffer ----
     first, rows = 5, 4                # five rows of group 0 come first (they stay on this rank)
@@ -119,7 +120,7 @@ def test_proxy_forwards_dispatch_then_combine(ranks) -> None:
         assert torch.equal(crecv[slot], payload[i])
     untouched = [s for s in range(TOKENS * TOPK) if s not in slots]
     assert int(crecv[untouched].count_nonzero()) == 0
-    assert a.probe.counters() == (1, 1) and not a.probe.failed()
+    assert _wait(lambda: a.probe.counters() == (1, 1)) and not a.probe.failed()
 
     # ---- a second dispatch with nothing for rank 1: the flag still travels ----
     a.words[RECORDS + 1] = 0
