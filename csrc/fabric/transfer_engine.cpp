@@ -604,7 +604,9 @@ void TransferEngine::uvm_loop() {
       for (size_t i = 0; i < kWatchSlots; ++i) {
         WatchSlot& s = watch_slots_[i];
         if (!s.used) continue;
-        const uint64_t now = reinterpret_cast<volatile uint64_t*>(watch_page_)[i];
+        // written by a kernel (or, in host-only use, by another thread): an acquire load, so that a
+        // callback sees what the writer published before the word
+        const uint64_t now = __atomic_load_n(&watch_page_[i], __ATOMIC_ACQUIRE);
         if (now != s.last) {
           TransferCompletionEntry e{};
           e.kind = TransferCompletionEntry::Kind::kUvmWatch;

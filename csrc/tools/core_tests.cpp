@@ -267,6 +267,33 @@ void test_engine_threads() {
     CHECK(imm_seen.load() == kThreads * kPerThread);   // two shards per write, each carries the immediate
     CHECK(reached.load() == 1);
     CHECK(std::memcmp(src.data(), dst_b.data(), kThreads * kPerThread * 256) == 0);
+    // two-sided messages into bouncing receives, and a watched word changed from another thread
+    std::atomic<int> received{0}, sent{0}, watched{0};
+    std::atomic<uint64_t> last_seen{0};
+    b.submit_bouncing_recvs(2, 256, [&](const std::string& data) { if (data.rfind("message ", 0) == 0) received.fetch_add(1); },
+                            [&](const std::string&) { err_cb.fetch_add(1); });
+    for (int i = 0; i < 8; ++i) {
+      a.submit_send(b.main_address(), "message " + std::to_string(i), [&] { sent.fetch_add(1); },
+                    [&](const std::string&) { err_cb.fetch_add(1); });
+    }
+    const UvmWatcher watcher = a.alloc_scalar_watcher([&](uint64_t, uint64_t now) {
+      last_seen.store(now);
+      watched.fetch_add(1);
+      return true;
+    });
+    std::thread poker([&] {
+      for (uint64_t v = 1; v <= 5; ++v) {
+        __atomic_store_n(reinterpret_cast<uint64_t*>(watcher.ptr()), v, __ATOMIC_RELEASE);
+        std::this_thread::sleep_for(std::chrono::milliseconds(2));
+      }
+    });
+    poker.join();
+    const auto deadline2 = std::chrono::steady_clock::now() + std::chrono::seconds(20);
+    while ((received.load() < 8 || sent.load() < 8 || last_seen.load() != 5) && std::chrono::steady_clock::now() < deadline2) {
+      std::this_thread::sleep_for(std::chrono::milliseconds(1));
+    }
+    CHECK(received.load() == 8 && sent.load() == 8);
+    CHECK(last_seen.load() == 5 && watched.load() >= 1 && err_cb.load() == 0);
     // a last burst that is still in flight when the engines are stopped and destroyed
     for (int i = 0; i < 16; ++i) {
       SingleTransferRequest r;
