@@ -1,6 +1,9 @@
 // Native unit tests of the host-side building blocks (the counterpart of the reference's Rust
 // unit tests: cuda-lib/src/test_driver.rs, fabric-lib's imm_count / utils modules). No GPU is
 // needed. Exit code 0 when every check passes; each failure prints its expression and line.
+#include <sys/mman.h>
+#include <unistd.h>
+
 #include <atomic>
 #include <chrono>
 #include <cstdio>
@@ -12,6 +15,7 @@
 #include "../a2a/a2a_context.h"
 #include "../a2a/a2a_proxy.h"
 #include "../core/error.h"
+#include "../cumem/cumem.h"
 #include "../fabric/api.h"
 #include "../fabric/host_buffer.h"
 #include "../fabric/imm_count.h"
@@ -432,6 +436,61 @@ void test_proxy_between_two_nodes() {
   }
 }
 
+// The descriptor server (the SCM_RIGHTS route by which CUDA virtual-memory allocations travel
+// between processes): four threads fetch a registered descriptor over the socket while another
+// is registered and unregistered; a wrong token and an unregistered number are refused.
+void test_fd_server_threads() {
+  const int fd = memfd_create("pplx-core-test", MFD_CLOEXEC);
+  CHECK(fd >= 0);
+  const char text[] = "descriptor contents";
+  CHECK(write(fd, text, sizeof(text)) == static_cast<ssize_t>(sizeof(text)));
+  const int other = memfd_create("pplx-core-test-2", MFD_CLOEXEC);
+  const std::string name = fd_server_name();
+  fd_server_register(fd);
+  fd_fetch_set_mode("socket");
+  std::atomic<int> good{0}, refused{0};
+  std::vector<std::thread> threads;
+  for (int t = 0; t < 4; ++t) {
+    threads.emplace_back([&] {
+      for (int i = 0; i < 8; ++i) {
+        try {
+          const int got = fd_fetch(getpid(), fd, name);
+          char buf[sizeof(text)] = {};
+          if (pread(got, buf, sizeof(buf), 0) == static_cast<ssize_t>(sizeof(buf)) && std::memcmp(buf, text, sizeof(buf)) == 0) {
+            good.fetch_add(1);
+          }
+          close(got);
+        } catch (const std::exception&) {
+        }
+        try {
+          close(fd_fetch(getpid(), fd + 1000, name));   // never registered
+        } catch (const std::exception&) {
+          refused.fetch_add(1);
+        }
+      }
+    });
+  }
+  for (int i = 0; i < 16; ++i) {
+    fd_server_register(other);
+    fd_server_unregister(other);
+  }
+  for (auto& th : threads) th.join();
+  CHECK(good.load() == 32);
+  CHECK(refused.load() == 32);
+  bool threw = false;
+  try {
+    const size_t colon = name.find(':');
+    close(fd_fetch(getpid(), fd, name.substr(0, colon) + ":0000000000000000"));   // right socket, wrong token
+  } catch (const std::exception&) {
+    threw = true;
+  }
+  CHECK(threw);
+  fd_fetch_set_mode("auto");
+  fd_server_unregister(fd);
+  close(fd);
+  close(other);
+}
+
 }  // namespace
 
 int main() {
@@ -444,6 +503,7 @@ int main() {
   test_json_numbers();
   test_engine_threads();
   test_proxy_between_two_nodes();
+  test_fd_server_threads();
   std::printf("%d checks, %d failed\n", g_checks, g_failures);
   return g_failures == 0 ? 0 : 1;
 }
