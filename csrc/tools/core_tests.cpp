@@ -24,6 +24,7 @@
 #include "../fabric/topo.h"
 #include "../fabric/transfer_engine.h"
 #include "../fabric/util.h"
+#include "../unigram/engine.h"
 #include "../unigram/json.h"
 
 namespace {
@@ -491,6 +492,38 @@ void test_fd_server_threads() {
   close(other);
 }
 
+// The tokenizer's batch encoder: a small model (empty charsmap, nine pieces), 400 documents, one
+// thread against six; the threads share the engine and keep their own states and word caches.
+void test_unigram_batch_threads() {
+  const std::string spec =
+      "{\"version\": \"1.0\", \"added_tokens\": [], \"normalizer\": {\"type\": \"Precompiled\", "
+      "\"precompiled_charsmap\": \"AAAAAA==\"}, \"pre_tokenizer\": {\"type\": \"Metaspace\", \"replacement\": \"\u2581\", "
+      "\"prepend_scheme\": \"always\", \"split\": true}, \"post_processor\": null, \"decoder\": {\"type\": \"Metaspace\", "
+      "\"replacement\": \"\u2581\", \"prepend_scheme\": \"always\", \"split\": true}, \"model\": {\"type\": \"Unigram\", "
+      "\"unk_id\": 0, \"vocab\": [[\"<unk>\", 0.0], [\"\u2581\", -2.0], [\"\u2581a\", -1.0], [\"a\", -3.0], [\"b\", -3.0], "
+      "[\"ab\", -2.5], [\"\u2581ab\", -1.5], [\"c\", -4.0], [\"\u2581abc\", -1.2]], \"byte_fallback\": false}}";
+  const auto engine = pplx::unigram::Engine::from_hf_json_bytes(spec);
+  CHECK(engine->vocab_size() == 9);
+  std::vector<std::string> docs;
+  uint32_t x = 12345;
+  for (int d = 0; d < 400; ++d) {
+    std::string text;
+    for (int w = 0; w < 200; ++w) {
+      x = x * 1664525u + 1013904223u;
+      static const char* words[] = {"ab", "abc", "a", "cab", "zz", "abcabc", "b", "ca"};
+      text += words[(x >> 24) & 7];
+      text += ' ';
+    }
+    docs.push_back(std::move(text));
+  }
+  std::vector<std::string_view> views(docs.begin(), docs.end());
+  const auto one = engine->encode_batch(views, 1);
+  const auto six = engine->encode_batch(views, 6);
+  CHECK(one.size() == 400 && one == six);
+  const std::vector<pplx::unigram::TokenId> want = {6, 8, 2, 1, 7, 5};
+  CHECK(engine->encode_batch({std::string_view("ab abc a cab")}, 2)[0] == want);
+}
+
 }  // namespace
 
 int main() {
@@ -504,6 +537,7 @@ int main() {
   test_engine_threads();
   test_proxy_between_two_nodes();
   test_fd_server_threads();
+  test_unigram_batch_threads();
   std::printf("%d checks, %d failed\n", g_checks, g_failures);
   return g_failures == 0 ? 0 : 1;
 }

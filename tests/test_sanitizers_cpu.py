@@ -1,7 +1,9 @@
 """The host code under the address, thread and undefined-behaviour sanitizers: builds the native
 unit tests (csrc/tools/core_tests.cpp: error type, deferred calls and pools, imm counters, sharding,
-host buffers, topology helpers, JSON numbers, and two transfer engines driven from four threads
-with a delayed and reordered domain) with -fsanitize=<x> and runs them. The kernels themselves are
+host buffers, topology helpers, JSON numbers; two transfer engines driven from four threads with a
+delayed and reordered domain, two-sided messages and a watched word; the all-to-all host proxy
+between two one-rank nodes; the descriptor server under four fetching threads; the tokenizer's
+batch encoder on six threads) with -fsanitize=<x> and runs them. The kernels themselves are
 not covered: device-side checking is the epoch tags, the bounded waits and the status words."""
 
 from __future__ import annotations
