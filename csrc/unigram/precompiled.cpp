@@ -48,7 +48,7 @@ PrecompiledNormalizer::PrecompiledNormalizer(const std::vector<uint8_t>& blob) {
     throw std::runtime_error("precompiled charsmap: bad trie size");
   }
   units_.resize(trie_bytes / 4);
-  std::memcpy(units_.data(), blob.data() + 4, trie_bytes);
+  if (trie_bytes > 0) std::memcpy(units_.data(), blob.data() + 4, trie_bytes);   // an empty charsmap has no trie
   normalized_.assign(reinterpret_cast<const char*>(blob.data()) + 4 + trie_bytes,
                      blob.size() - 4 - trie_bytes);
   // ASCII bytes that no charsmap key starts with pass through unchanged whenever they
