@@ -150,7 +150,8 @@ struct A2AConfig {
   uint64_t sync_bytes;
   uint64_t off_counts;          // inside the sync region; two banks of counts_bank_words
   uint64_t off_tok_arrive;      // inside the sync region; [max_num_tokens] u32
-  uint32_t counts_bank_words;   // num_groups * counts_stride
+  uint32_t counts_bank_words;   // counts_stride x the number of senders of a counts message: the source
+                                // groups, or every source rank in the flagged-line format
   uint32_t pad0_;
   uint64_t recv_bytes;
   uint64_t off_drecv;           // inside the recv region

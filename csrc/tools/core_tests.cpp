@@ -524,6 +524,68 @@ void test_unigram_batch_threads() {
   CHECK(engine->encode_batch({std::string_view("ab abc a cab")}, 2)[0] == want);
 }
 
+// The symmetric layout of the all-to-all for a grid of shapes: strides are multiples of 16 bytes
+// (128 for the flagged-line format), the regions inside the sync and receive areas do not
+// overlap and fit, and the receive area holds a worst-case dispatch and combine.
+void test_a2a_layout_invariants() {
+  int configs = 0;
+  for (int world : {1, 2, 4, 8}) {
+    for (int dp : {1, 2}) {
+      if (world % dp != 0) continue;
+      for (int tokens : {1, 8, 128, 4096}) {
+        for (int hidden : {16, 64, 7168}) {
+          for (int with_scale : {0, 1}) {
+            if (with_scale && hidden % 128 != 0) continue;
+            for (int wire : {static_cast<int>(kWirePlain), static_cast<int>(kWireLL)}) {
+              for (int mode : {static_cast<int>(kCombinePerRoute), static_cast<int>(kCombinePreReduce)}) {
+                A2AParams p;
+                p.world = world;
+                p.dp_size = dp;
+                p.num_experts = 8 * world;
+                p.topk = 4;
+                p.max_num_tokens = tokens;
+                p.hidden_dim = hidden;
+                p.hidden_dim_scale = with_scale ? hidden / 128 : 0;
+                p.in_elemsize = with_scale ? 1 : 2;
+                p.out_elemsize = 2;
+                p.wire = wire;
+                p.combine_mode = mode;
+                const A2AConfig c = a2a_make_config(p, 148, 1);
+                ++configs;
+                const uint32_t unit = c.wire == kWireLL ? 128u : 16u;
+                bool ok = c.d_stride % unit == 0 && c.c_stride % unit == 0 && c.d_stride > 0 && c.c_stride > 0;
+                ok = ok && c.num_groups == world / dp && c.experts_per_rank == 8;
+                ok = ok && c.d_header_bytes % 16 == 0 && c.d_header_bytes >= 4u * (2 + 2 * 4);
+                ok = ok && c.d_payload_bytes >= static_cast<uint32_t>(hidden * p.in_elemsize);
+                // sync area: two banks of counts, then the per-token arrival words
+                // one counts message per source group, or per source rank in the flagged-line format
+                ok = ok && c.counts_bank_words == static_cast<uint32_t>(c.wire == kWireLL ? world : c.num_groups) * c.counts_stride;
+                ok = ok && c.off_counts % 16 == 0 && c.off_counts + 8ull * c.counts_bank_words <= c.sync_bytes;
+                ok = ok && c.off_tok_arrive % 16 == 0 && c.off_tok_arrive + 4ull * tokens <= c.sync_bytes;
+                ok = ok && (c.off_tok_arrive >= c.off_counts + 8ull * c.counts_bank_words ||
+                            c.off_counts >= c.off_tok_arrive + 4ull * tokens);
+                // receive area: every source group's worst case of records, then the combine slots
+                ok = ok && c.drecv_group_stride >= static_cast<uint64_t>(tokens) * c.d_stride;
+                ok = ok && c.off_drecv % unit == 0 && c.off_crecv % unit == 0;
+                ok = ok && c.off_drecv + c.num_groups * c.drecv_group_stride <= c.off_crecv;
+                ok = ok && c.c_records_per_token == static_cast<uint32_t>(mode == kCombinePerRoute ? 4 : world);
+                ok = ok && c.off_crecv + static_cast<uint64_t>(tokens) * c.c_records_per_token * c.c_stride <= c.recv_bytes;
+                ok = ok && c.max_recv_rows >= static_cast<uint32_t>(tokens) * 4u * static_cast<uint32_t>(c.num_groups);
+                if (!ok) {
+                  std::fprintf(stderr, "layout: world %d dp %d tokens %d hidden %d scale %d wire %d mode %d\n", world, dp, tokens,
+                               hidden, with_scale, wire, mode);
+                }
+                CHECK(ok);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  CHECK(configs > 300);
+}
+
 }  // namespace
 
 int main() {
@@ -538,6 +600,7 @@ int main() {
   test_proxy_between_two_nodes();
   test_fd_server_threads();
   test_unigram_batch_threads();
+  test_a2a_layout_invariants();
   std::printf("%d checks, %d failed\n", g_checks, g_failures);
   return g_failures == 0 ? 0 : 1;
 }
