@@ -74,6 +74,20 @@ def _sig(t: Optional[torch.Tensor]):
     return (t.data_ptr(), t.shape, t.stride(), t.dtype)
 
 
+def check_layout_agreement(group: ParallelGroup, rank: int, layout: dict) -> None:
+    """Collective over ``group``: raises ValueError on every rank that finds a peer whose layout
+    (wire format, strides, offsets, sizes) differs from its own. Launch shape (``num_blocks``), the
+    NVLink-domain mask and the wait limit may differ."""
+    shape_keys = sorted(k for k in layout if k not in ("num_blocks", "node_mask", "wait_limit_ns"))
+    mine = tuple((k, layout[k]) for k in shape_keys)
+    for peer, theirs in enumerate(group.all_gather_object(mine)):
+        if theirs != mine:
+            diff = [k for (k, v), (_, w) in zip(mine, theirs) if v != w]
+            raise ValueError(
+                f"rank {rank} and rank {peer} disagree about the all-to-all layout ({', '.join(diff)}); "
+                "check PPLX_A2A_WIRE and the constructor arguments on every rank")
+
+
 class P2PAllToAll(AllToAllKernel):
     def __init__(
         self,
@@ -181,14 +195,7 @@ class P2PAllToAll(AllToAllKernel):
         # (which an environment variable can override per process), strides and offsets must be
         # the same everywhere, or a receiver would wait for lines that never come.
         if global_group is not None and world_size > 1:
-            shape_keys = sorted(k for k in layout if k not in ("num_blocks", "node_mask", "wait_limit_ns"))
-            mine_shape = tuple((k, layout[k]) for k in shape_keys)
-            for peer, theirs in enumerate(global_group.all_gather_object(mine_shape)):
-                if theirs != mine_shape:
-                    diff = [k for (k, v), (_, w) in zip(mine_shape, theirs) if v != w]
-                    raise ValueError(
-                        f"rank {rank} and rank {peer} disagree about the all-to-all layout ({', '.join(diff)}); "
-                        "check PPLX_A2A_WIRE and the constructor arguments on every rank")
+            check_layout_agreement(global_group, rank, layout)
 
         torch.cuda.set_device(device)
         handle_kind = CUMemHandleKind.FileDescriptor

@@ -51,3 +51,27 @@ def _worker(device, dp_group, global_group, cfg):
 @pytest.mark.parametrize("cfg", [(16, 8, 32, 2, 1, None), (9, 12, 16, 3, 4, 2)])
 def test_baseline_matches_oracle(world: int, cfg) -> None:
     assert all(ParallelLaunch(world_size=world).run(_worker, cfg))
+
+
+def _layout_worker(device, dp_group, global_group, mismatch):
+    """Every rank computes the all-to-all layout and compares it with its peers' (the check that
+    P2PAllToAll makes before any rank writes into another's buffers)."""
+    from pplx_garden.kernels.p2p_all_to_all import check_layout_agreement
+    from pplx_garden.native.p2p_all_to_all import AllToAllContext
+
+    rank, world = global_group.rank, global_group.size
+    wire = "plain" if (mismatch and rank == 1) else "ll"
+    layout = AllToAllContext.layout(hidden_dim=256, in_elemsize=2, out_elemsize=2, max_num_tokens=16,
+                                    num_experts=8, num_experts_per_token=2, world_size=world, wire=wire,
+                                    num_blocks=16 + rank)   # the launch shape may differ
+    try:
+        check_layout_agreement(global_group, rank, layout)
+    except ValueError as e:
+        return str(e)
+    return "agreed"
+
+
+def test_ranks_compare_their_all_to_all_layouts() -> None:
+    assert ParallelLaunch(world_size=2).run(_layout_worker, False) == ["agreed", "agreed"]
+    messages = ParallelLaunch(world_size=2).run(_layout_worker, True)
+    assert all("disagree about the all-to-all layout" in m and "wire" in m for m in messages), messages
