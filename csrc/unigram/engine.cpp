@@ -301,12 +301,13 @@ void Engine::encode_segment(std::string_view text, EncodeState* st) const {
   if (text.empty()) return;
   if (add_prefix_space_ && text.front() != ' ') prep.append(replacement_);
   size_t run = 0;
-  for (size_t i = 0; i < text.size(); ++i) {
-    if (text[i] == ' ') {
-      prep.append(text.data() + run, i - run);
-      prep.append(replacement_);
-      run = i + 1;
-    }
+  while (run < text.size()) {
+    const void* hit = std::memchr(text.data() + run, ' ', text.size() - run);
+    if (hit == nullptr) break;
+    const size_t i = static_cast<size_t>(static_cast<const char*>(hit) - text.data());
+    prep.append(text.data() + run, i - run);
+    prep.append(replacement_);
+    run = i + 1;
   }
   prep.append(text.data() + run, text.size() - run);
 

@@ -1,5 +1,7 @@
 #include "precompiled.h"
 
+#include <algorithm>
+
 #include <cstring>
 #include <stdexcept>
 
@@ -56,7 +58,7 @@ PrecompiledNormalizer::PrecompiledNormalizer(const std::vector<uint8_t>& blob) {
   for (int c = 0; c < 128; ++c) {
     const uint8_t b = static_cast<uint8_t>(c);
     size_t len = 0;
-    ascii_passthrough_[c] = c != 0 && transform(&b, 1, &len) == nullptr;
+    ascii_passthrough_[c] = c != 0 && c != '\r' && transform(&b, 1, &len) == nullptr;
   }
 }
 
@@ -104,42 +106,62 @@ const char* PrecompiledNormalizer::transform(const uint8_t* chunk, size_t n, siz
 
 namespace {
 
+// Appends to a string through a raw pointer (no capacity check per byte) and collapses runs of
+// spaces into one, which is the Replace(" {2,}" -> " ") step that follows the charsmap.
 struct Collapser {
   std::string* out;
+  size_t used = 0;
   bool prev_space = false;
+  // room for n more bytes
+  inline char* reserve(size_t n) {
+    if (used + n > out->size()) out->resize(std::max(out->size() * 2, used + n + 64));
+    return out->data() + used;
+  }
   inline void push_bytes(const char* p, size_t n) {
+    char* w = reserve(n);
+    char* const w0 = w;
+    bool ps = prev_space;
     for (size_t i = 0; i < n; ++i) {
       const char c = p[i];
-      if (c == ' ') {
-        if (!prev_space) out->push_back(' ');
-        prev_space = true;
-      } else {
-        out->push_back(c);
-        prev_space = false;
-      }
+      const bool sp = c == ' ';
+      *w = c;
+      w += (sp && ps) ? 0 : 1;
+      ps = sp;
     }
+    prev_space = ps;
+    used += static_cast<size_t>(w - w0);
   }
+  inline void finish() { out->resize(used); }
 };
 
 }  // namespace
 
 void PrecompiledNormalizer::normalize_into(std::string_view input, std::string* out) const {
   out->clear();
-  out->reserve(input.size());
+  out->resize(input.size() + 64);
   const uint8_t* s = reinterpret_cast<const uint8_t*>(input.data());
   const size_t n = input.size();
   Collapser sink{out};
   size_t pos = 0;
   while (pos < n) {
-    // Fast path: an unmapped ASCII byte followed by another ASCII byte is a cluster of
-    // its own (CR LF is the one ASCII pair that joins, and CR is never followed here
-    // without the check).
-    const uint8_t c0 = s[pos];
-    if (c0 < 0x80 && ascii_passthrough_[c0] && pos + 1 < n && s[pos + 1] < 0x80 &&
-        !(c0 == '\r' && s[pos + 1] == '\n')) {
-      const char ch = static_cast<char>(c0);
-      sink.push_bytes(&ch, 1);
-      ++pos;
+    // Fast path: an unmapped ASCII byte followed by another ASCII byte is a cluster of its own
+    // (CR LF is the one ASCII pair that joins; CR always takes the slow path). A run of such
+    // bytes is copied in one pass, runs of spaces collapsing into one on the way.
+    if (pos + 1 < n && ascii_passthrough_[s[pos]] && s[pos + 1] < 0x80) {
+      char* w = sink.reserve(n - pos);
+      char* const w0 = w;
+      bool ps = sink.prev_space;
+      uint8_t c0 = s[pos];
+      do {
+        const bool sp = c0 == ' ';
+        *w = static_cast<char>(c0);
+        w += (sp && ps) ? 0 : 1;
+        ps = sp;
+        ++pos;
+        c0 = s[pos];
+      } while (pos + 1 < n && ascii_passthrough_[c0] && s[pos + 1] < 0x80);
+      sink.prev_space = ps;
+      sink.used += static_cast<size_t>(w - w0);
       continue;
     }
     const size_t end = unicode::grapheme_end(s, n, pos);
@@ -173,6 +195,7 @@ void PrecompiledNormalizer::normalize_into(std::string_view input, std::string* 
     }
     pos = end;
   }
+  sink.finish();
 }
 
 }  // namespace pplx::unigram

@@ -33,7 +33,7 @@ class PrecompiledNormalizer {
  private:
   std::vector<uint32_t> units_;
   std::string normalized_;
-  bool ascii_passthrough_[128] = {};
+  bool ascii_passthrough_[256] = {};   // false from 0x80 up and for CR (CR LF is one cluster)
 };
 
 }  // namespace pplx::unigram
